@@ -1,0 +1,330 @@
+#!/usr/bin/env python
+"""Benchmark of the Llama decode hot path: decode tokens/s, TinyLlama-1.1B shape, batch 1.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--dtype f32|bf16] [--impl lumen|reference]
+
+One "step" is one teacher-forced decode token (one pass over all the weights).  Synthetic data:
+weights N(0, 0.02) from seed 0 with RMSNorm gains 1.0, a 32-token prompt and the forced ids from
+seed 1 (BASELINE config 1); the static KV cache is sized to max_seq_len 2048.
+
+Own arm (default): prints ONE JSON line with
+  value     device-resident throughput (ids and logits stay in HBM), CUDA events on the library's stream
+  e2e       the same metric through the public host API: per step the token id is copied host->device
+            and the logits [vocab] device->host, inside the timed region
+  roofline  algorithmic HBM bytes per step / measured step time against the measured copy bandwidth
+  cpu_baseline  the CPU restatement of the reference's Rayon path, timed on this box's host cores on a
+            bounded sample of the same workload (rank 0, N = 1 only)
+With N > 1 (launched by torchrun, one rank per GPU) the model is tensor-parallel over the N GPUs with an
+NCCL allreduce after the o/down projections ("scaling": "strong": the work per token is fixed).
+
+Reference arm (--impl reference): the reference is Rust and cannot be built on this box, so the arm
+times its CPU restatement (oracle/) with all host threads on the same workload and prints the same
+line with "impl": "reference".
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+PROMPT_LEN = 32
+METRIC = "decode_tokens_per_s"
+UNIT = "tokens/s"
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_hbm_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    try:
+        return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU through NVML (read-only) every few ms."""
+
+    def __init__(self, index: int, period_s: float = 0.004):
+        super().__init__(daemon=True)
+        self.index, self.period = index, period_s
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._halt = threading.Event()
+        self.active = False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def run(self):
+        if self.nv is None:
+            return
+        nv = self.nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4),
+            "hw_power_brake": getattr(nv, "nvmlClocksThrottleReasonHwPowerBrakeSlowdown", 0x80),
+        }
+        while not self._halt.is_set():
+            if self.active:
+                try:
+                    self.samples.append(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
+                    r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+                    self.reasons.update(n for n, bit in names.items() if r & bit)
+                except Exception:
+                    pass
+            time.sleep(self.period)
+
+    def stop(self):
+        self._halt.set()
+
+    def summary(self):
+        return {"sm_mhz": (statistics.median(self.samples) if self.samples else None), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def tinyllama_cfg(dtype: str, max_seq: int):
+    from lumen_b200 import synth
+    cfg = dict(synth.TINYLLAMA)
+    cfg["max_seq_len"] = max_seq
+    return cfg
+
+
+def gen_params(cfg: dict, dtype: str):
+    from lumen_b200 import synth
+    from lumen_b200.llama import LlamaConfig
+    return synth.iter_params(LlamaConfig(**cfg), 0, std=0.02, round_bf16=(dtype == "bf16"))
+
+
+def algorithmic_bytes_per_step(cfg: dict, weight_bytes: int, ctx_len_mean: float, tp: int) -> float:
+    """Weights of this rank once + K/V rows of the context once per KV head + the embedding row + logits."""
+    d = cfg["hidden_size"] // cfg["num_attention_heads"]
+    hkv_local = max(1, cfg["num_key_value_heads"] // tp)
+    kv = cfg["num_hidden_layers"] * 2 * hkv_local * d * 4 * (ctx_len_mean + 1)
+    return weight_bytes + kv + cfg["hidden_size"] * 4 + cfg["vocab_size"] * 4 / tp
+
+
+def cpu_decode(cfg: dict, params: dict, ids: np.ndarray, budget_s: float, max_steps: int):
+    """Times the CPU restatement on a bounded sample: full 32-token prefill, then decode steps until the
+    budget is spent.  Returns (tokens/s over the decode steps, steps, threads, logits of those steps)."""
+    from oracle import binding as O
+    model = O.Llama(cfg, params, "f32")
+    caches = model.init_kv_caches(1)
+    model.forward(ids[None, :PROMPT_LEN], caches)
+    logits = []
+    t0 = time.perf_counter()
+    steps = 0
+    while steps < max_steps:
+        logits.append(model.forward(ids[None, PROMPT_LEN + steps:PROMPT_LEN + steps + 1], caches)[0, 0])
+        steps += 1
+        if time.perf_counter() - t0 > budget_s:
+            break
+    dt = time.perf_counter() - t0
+    return steps / dt, steps, O.num_threads(), np.stack(logits)
+
+
+def run_reference(args):
+    """--impl reference: the reference's CPU path (restated in C; the Rust crate cannot be built here)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    cfg = tinyllama_cfg(args.dtype, 2048)
+    params = dict(gen_params(cfg, args.dtype))
+    from lumen_b200 import synth
+    ids = synth.token_ids(1, PROMPT_LEN + args.warmup + args.steps + 1, cfg["vocab_size"])
+    budget = 90.0
+    tps, steps, threads, _ = cpu_decode(cfg, params, ids, budget, max(1, args.steps))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": 0, "ms_per_step": 1000.0 / tps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"tinyllama_1.1b_{args.dtype}_batch1_decode", "prompt_len": PROMPT_LEN, "max_seq_len": 2048,
+                   "note": "Rust reference cannot be built here (no rustc); this times its C/OpenMP restatement"},
+        "cpu_baseline": {"value": tps, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": f"{PROMPT_LEN}-token prefill (untimed) + {steps} decode steps, <= {budget:.0f} s"},
+        "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--dtype", choices=["f32", "bf16"], default="f32")
+    ap.add_argument("--impl", choices=["lumen", "reference"], default="lumen")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-budget-s", type=float, default=12.0)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        return run_reference(args)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus N > 1 must be launched with torchrun (one rank per GPU)")
+    import torch
+    import torch.distributed as dist
+
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    import lumen_b200 as L
+    from lumen_b200 import synth
+
+    total = PROMPT_LEN + args.warmup + args.steps
+    max_seq = 2048
+    if total > max_seq:
+        raise SystemExit(f"prompt + warmup + steps = {total} exceeds max_seq_len {max_seq}")
+    cfg = tinyllama_cfg(args.dtype, max_seq)
+
+    nccl_id = None
+    if world > 1:
+        box = [L.Context.nccl_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        nccl_id = box[0]
+    ctx = L.Context(local_rank, rank, world, nccl_id)
+    model = L.LlamaModel(L.LlamaConfig(**cfg, weight_dtype=args.dtype), ctx)
+    keep_params = (rank == 0 and world == 1 and not args.no_cpu_baseline)
+    params = {}
+    for name, w in gen_params(cfg, args.dtype):
+        model.set_param(name, w)
+        if keep_params:
+            params[name] = w
+    ids = synth.token_ids(1, total + 1, cfg["vocab_size"])
+    weight_bytes = model.weight_bytes_per_step
+    stream = torch.cuda.ExternalStream(ctx.stream, device=torch.device("cuda", local_rank))
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+
+    def barrier():
+        ctx.synchronize()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    caches = model.init_kv_caches(1)
+    d_ids = L.Tensor.from_array_no_grad(ids, ctx)
+    d_logits = L.Tensor.from_array_no_grad(np.zeros(cfg["vocab_size"], np.float32), ctx)
+
+    def prefill():
+        model.reset_kv_caches(caches)
+        with L.no_grad():
+            model.forward(ids[None, :PROMPT_LEN], caches, 0, last_only=True)
+
+    # ---- device-resident throughput --------------------------------------------------------------------
+    with L.no_grad():
+        prefill()
+        pos = PROMPT_LEN
+        for _ in range(args.warmup):
+            model.forward_device(d_ids.data_ptr + 4 * pos, 1, 1, caches, d_logits.data_ptr)
+            pos += 1
+        barrier()
+        launches0 = ctx.launch_count
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        sampler.active = True
+        e0.record(stream)
+        for _ in range(args.steps):
+            model.forward_device(d_ids.data_ptr + 4 * pos, 1, 1, caches, d_logits.data_ptr)
+            pos += 1
+        e1.record(stream)
+        barrier()
+        sampler.active = False
+        dev_ms = max_over_ranks(e0.elapsed_time(e1))
+        launches = ctx.launch_count - launches0
+
+        # ---- end to end through the host API: id in (pinned staging inside the library), logits out -------
+        prefill()
+        pos = PROMPT_LEN
+        host_logits = []
+        for _ in range(args.warmup):
+            model.forward(ids[None, pos:pos + 1], caches)
+            pos += 1
+        barrier()
+        t0 = time.perf_counter()
+        e0.record(stream)
+        for _ in range(args.steps):
+            lg = model.forward(ids[None, pos:pos + 1], caches)
+            if len(host_logits) < 4:
+                host_logits.append(lg[0, 0].copy())
+            pos += 1
+        e1.record(stream)
+        barrier()
+        e2e_wall_ms = (time.perf_counter() - t0) * 1000.0
+        e2e_ms = max_over_ranks(max(e0.elapsed_time(e1), e2e_wall_ms))
+    sampler.stop()
+
+    tps = args.steps / (dev_ms / 1000.0)
+    e2e_tps = args.steps / (e2e_ms / 1000.0)
+    ctx_mean = PROMPT_LEN + args.warmup + (args.steps - 1) / 2.0
+    bytes_step = algorithmic_bytes_per_step(cfg, weight_bytes, ctx_mean, world)
+    peak, peak_kind = measured_hbm_peak()
+    achieved = bytes_step / (dev_ms / args.steps / 1000.0) / 1e9
+    line = {
+        "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"tinyllama_1.1b_{args.dtype}_batch1_decode", "weights": args.dtype, "batch": 1,
+                   "prompt_len": PROMPT_LEN, "max_seq_len": max_seq, "parallelism": f"tp{world}",
+                   "l2": "inputs larger than L2: every step streams %.2f GB of weights" % (weight_bytes / 1e9)},
+        "e2e": {"value": e2e_tps, "unit": UNIT, "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4 * cfg["vocab_size"],
+                "ms_per_step": e2e_ms / args.steps},
+        "gpu_launches": int(launches),
+        "clocks": sampler.summary(),
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
+                     "kernel": "whole decode step (CUDA graph of %d kernels)" % (launches // max(args.steps, 1)),
+                     "algorithmic_bytes_per_step": bytes_step},
+    }
+    if keep_params:
+        tps_cpu, n, threads, cpu_logits = cpu_decode(cfg, params, ids[:PROMPT_LEN + args.warmup + 4 + 64], args.cpu_budget_s,
+                                                     args.warmup + 4)
+        line["cpu_baseline"] = {"value": tps_cpu, "unit": UNIT, "cores": threads, "kind": "port",
+                                "sample": f"{PROMPT_LEN}-token prefill (untimed) + {n} decode steps of the same workload"}
+        # the CPU steps cover the warm-up positions and then the first timed ones: compare where they overlap
+        k = min(len(host_logits), n - args.warmup)
+        if k > 0:
+            errs = [float(np.abs(host_logits[i] - cpu_logits[args.warmup + i]).max() / np.abs(cpu_logits[args.warmup + i]).max())
+                    for i in range(k)]
+            line["parity_vs_cpu"] = {"steps_compared": k, "max_rel_err": max(errs),
+                                     "argmax_equal": all(int(host_logits[i].argmax()) == int(cpu_logits[args.warmup + i].argmax())
+                                                         for i in range(k))}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

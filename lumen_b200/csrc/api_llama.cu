@@ -1,0 +1,603 @@
+// C ABI: LlamaModel (src/models/llama.rs of the reference) on one GPU or one tensor-parallel rank.
+//
+// Memory: one device slab holds every weight of the rank (q/k/v rows of a layer are stored back to
+// back so the three projections are one vector-matrix launch), one slab holds the KV caches of all
+// layers, one workspace holds the activations of the largest batch seen.  A decode step allocates
+// nothing.  Decode steps (S == 1) are captured once per batch size into a CUDA graph and replayed;
+// the context length is read from device memory so the same graph serves every position.
+//
+// Tensor parallelism (new; the reference is single-process): q/k/v/gate/up are split by output row
+// (whole heads per rank, KV heads replicated when there are fewer than ranks), o/down by input
+// column with a sum-allreduce after each, lm_head by vocabulary row with an allgather.
+#include <algorithm>
+#include <cmath>
+#include <map>
+#include <tuple>
+
+#include "common.cuh"
+
+using namespace lumen;
+
+namespace {
+
+struct LayerW {
+    char *wqkv = nullptr;  // [(qd_l + 2*kvd_l), H]
+    char *wo = nullptr;    // [H, qd_l]
+    char *wgate = nullptr; // [I_l, H]
+    char *wup = nullptr;   // [I_l, H]
+    char *wdown = nullptr; // [H, I_l]
+    float *norm1 = nullptr, *norm2 = nullptr, *qn = nullptr, *kn = nullptr;
+};
+
+struct Workspace {
+    size_t M = 0;
+    char *base = nullptr;
+    float *x = nullptr, *nx = nullptr, *qkv = nullptr, *att = nullptr, *act = nullptr, *gate = nullptr, *up = nullptr;
+    float *logits = nullptr, *logits_local = nullptr, *last_x = nullptr, *part = nullptr, *ids = nullptr;
+    size_t part_bytes = 0;
+    float *h_ids = nullptr;     // pinned
+    float *h_logits = nullptr;  // pinned
+    size_t h_logits_elems = 0;
+};
+
+constexpr int kMaxSplits = 64;
+
+__global__ void f32_to_bf16_kernel(const float *in, __nv_bfloat16 *out, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = __float2bfloat16_rn(in[i]);
+}
+__global__ void bf16_to_f32_kernel2(const __nv_bfloat16 *in, float *out, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = __bfloat162float(in[i]);
+}
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace
+
+struct lumen_llama {
+    lumen_ctx *ctx = nullptr;
+    lumen_llama_config cfg{};
+    size_t D = 0, H = 0, V = 0, I = 0, L = 0;
+    size_t hq_l = 0, hkv_l = 0, qd_l = 0, kvd_l = 0, inter_l = 0, vocab_l = 0, qkv_rows = 0;
+    size_t kv_head0 = 0, q_head0 = 0;  // first global head owned by this rank
+    size_t esz = 4;
+    char *wslab = nullptr;
+    size_t wbytes = 0, stream_bytes = 0;
+    std::vector<LayerW> layers;
+    char *embed = nullptr, *lm_head = nullptr;
+    float *final_norm = nullptr;
+    float *cos_t = nullptr, *sin_t = nullptr;
+    std::map<std::string, bool> is_set;
+    size_t n_expected = 0;
+    Workspace ws;
+    // decode graphs keyed by (batch, splits, first cache's k pointer)
+    std::map<std::tuple<size_t, int, const void *>, cudaGraphExec_t> graphs;
+    std::map<std::tuple<size_t, int, const void *>, int> eager_runs;
+    std::map<std::tuple<size_t, int, const void *>, unsigned long long> graph_nodes;
+    bool use_graph = true;
+};
+
+namespace {
+
+void drop_graphs(lumen_llama *m) {
+    for (auto &kv : m->graphs) cudaGraphExecDestroy(kv.second);
+    m->graphs.clear();
+    m->eager_runs.clear();
+}
+
+int ensure_workspace(lumen_llama *m, size_t M) {
+    Workspace &w = m->ws;
+    if (M <= w.M) return LUMEN_OK;
+    lumen_ctx *ctx = m->ctx;
+    LUMEN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    drop_graphs(m);
+    if (w.base) cudaFree(w.base);
+    if (w.h_ids) cudaFreeHost(w.h_ids);
+    if (w.h_logits) cudaFreeHost(w.h_logits);
+    w = Workspace();
+    const size_t T = ctx->tp_size;
+    const size_t qkvd = m->qkv_rows;
+    // Decode batches never exceed M; the attention scratch is sized for the largest split count.
+    w.part_bytes = attn_decode_scratch_bytes(M, m->hq_l, m->D, kMaxSplits);
+    size_t off = 0;
+    auto take = [&](size_t elems) {
+        size_t o = off;
+        off += align_up(elems * sizeof(float), 256);
+        return o;
+    };
+    size_t o_x = take(M * m->H), o_nx = take(M * m->H), o_qkv = take(M * qkvd), o_att = take(M * m->qd_l);
+    size_t o_act = take(M * m->inter_l), o_gate = take(M * m->inter_l), o_up = take(M * m->inter_l);
+    size_t o_logits = take(M * m->V), o_ll = take(T > 1 ? T * M * m->vocab_l : 0), o_last = take(M * m->H);
+    size_t o_part = take(w.part_bytes / sizeof(float)), o_ids = take(M);
+    LUMEN_CUDA(ctx, cudaMalloc(&w.base, off));
+    auto at = [&](size_t o) { return reinterpret_cast<float *>(w.base + o); };
+    w.x = at(o_x); w.nx = at(o_nx); w.qkv = at(o_qkv); w.att = at(o_att); w.act = at(o_act); w.gate = at(o_gate);
+    w.up = at(o_up); w.logits = at(o_logits); w.logits_local = at(o_ll); w.last_x = at(o_last); w.part = at(o_part);
+    w.ids = at(o_ids);
+    LUMEN_CUDA(ctx, cudaMallocHost(&w.h_ids, std::max<size_t>(M, 1) * sizeof(float)));
+    w.h_logits_elems = std::min<size_t>(M * m->V, (size_t)16 << 20);  // pinned staging up to 64 MB
+    LUMEN_CUDA(ctx, cudaMallocHost(&w.h_logits, std::max<size_t>(w.h_logits_elems, 1) * sizeof(float)));
+    w.M = M;
+    return LUMEN_OK;
+}
+
+// Copies the [rows x ncols] block starting at column col0 of a row-major host matrix with `cols_total`
+// columns into a dense device matrix of dtype dst_dt, converting between f32 and bf16 when needed.
+int upload_block(lumen_ctx *ctx, void *dst, lumen_dtype dst_dt, const void *src_host, lumen_dtype src_dt, size_t rows,
+                 size_t cols_total, size_t col0, size_t ncols) {
+    if (rows == 0 || ncols == 0) return LUMEN_OK;
+    const size_t se = src_dt == LUMEN_F32 ? 4 : 2;
+    const char *src = static_cast<const char *>(src_host) + col0 * se;
+    cudaStream_t s = ctx->stream;
+    if (src_dt == dst_dt) {
+        LUMEN_CUDA(ctx, cudaMemcpy2DAsync(dst, ncols * se, src, cols_total * se, ncols * se, rows, cudaMemcpyHostToDevice, s));
+        LUMEN_CUDA(ctx, cudaStreamSynchronize(s));
+        return LUMEN_OK;
+    }
+    // Convert in row chunks to bound the staging buffer.
+    const size_t chunk_rows = std::max<size_t>(1, ((size_t)64 << 20) / (ncols * se));
+    void *tmp = nullptr;
+    LUMEN_CUDA(ctx, cudaMalloc(&tmp, std::min(rows, chunk_rows) * ncols * se));
+    const size_t de = dst_dt == LUMEN_F32 ? 4 : 2;
+    int rc = LUMEN_OK;
+    for (size_t r0 = 0; r0 < rows && rc == LUMEN_OK; r0 += chunk_rows) {
+        const size_t nr = std::min(chunk_rows, rows - r0), n = nr * ncols;
+        cudaError_t e = cudaMemcpy2DAsync(tmp, ncols * se, src + r0 * cols_total * se, cols_total * se, ncols * se, nr,
+                                          cudaMemcpyHostToDevice, s);
+        if (e != cudaSuccess) { rc = cuda_fail(ctx, e, "cudaMemcpy2DAsync"); break; }
+        char *d = static_cast<char *>(dst) + r0 * ncols * de;
+        if (dst_dt == LUMEN_BF16)
+            f32_to_bf16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>((const float *)tmp, (__nv_bfloat16 *)d, n);
+        else
+            bf16_to_f32_kernel2<<<(unsigned)((n + 255) / 256), 256, 0, s>>>((const __nv_bfloat16 *)tmp, (float *)d, n);
+        e = cudaStreamSynchronize(s);
+        if (e != cudaSuccess) rc = cuda_fail(ctx, e, "convert upload");
+    }
+    cudaFree(tmp);
+    return rc;
+}
+
+struct StepPlan {
+    size_t B, S, M;
+    bool decode;
+    int nsplit;
+};
+
+// Enqueues one forward pass over ws.ids[M] on the context stream.  `last_only` restricts the final norm
+// and lm_head to the last position of each sequence.  Logits land in ws.logits ([M,V] or [B,V]).
+int enqueue_forward(lumen_llama *m, const StepPlan &p, lumen_kv_cache **caches, bool last_only) {
+    lumen_ctx *ctx = m->ctx;
+    cudaStream_t s = ctx->stream;
+    Workspace &w = m->ws;
+    const size_t M = p.M, H = m->H, qkvd = m->qkv_rows;
+    const lumen_dtype wdt = m->cfg.weight_dtype;
+    const bool vec = M <= 8 && M * std::max(H, std::max(m->inter_l, m->qd_l)) * 4 <= 200 * 1024;
+    const bool tp = ctx->tp_size > 1;
+    const float eps = m->cfg.rms_norm_eps;
+    const float scale = 1.0f / sqrtf((float)m->D);  // (head_dim as f32).sqrt().recip(), self_attention.rs:89
+    const float *res_x = (!tp || ctx->tp_rank == 0) ? w.x : nullptr;
+
+    LUMEN_TRY(launch_embedding(ctx, w.ids, m->embed, wdt, w.x, M, m->V, H, s));
+    for (size_t l = 0; l < m->L; ++l) {
+        const LayerW &lw = m->layers[l];
+        lumen_kv_cache *c = caches[l];
+        // h = x + Attention(Norm(x))                                   llama.rs:107-110
+        if (vec) {
+            GemvArgs g;
+            g.x = w.x; g.w = lw.wqkv; g.wdt = wdt; g.y = w.qkv; g.M = (int)M; g.K = H; g.N = qkvd; g.ldy = qkvd;
+            g.norm_w = lw.norm1; g.norm_eps = eps;
+            LUMEN_TRY(launch_gemv_nk(ctx, g, s));
+        } else {
+            LUMEN_TRY(launch_rmsnorm(ctx, w.x, lw.norm1, eps, w.nx, M, H, s));
+            LUMEN_TRY(launch_gemm_nk(ctx, w.nx, lw.wqkv, wdt, w.qkv, M, H, qkvd, nullptr, s));
+        }
+        if (p.decode) {
+            AttnDecodeArgs a;
+            a.q = w.qkv; a.k_new = w.qkv + m->qd_l; a.v_new = w.qkv + m->qd_l + m->kvd_l;
+            a.q_stride = qkvd; a.kv_stride = qkvd;
+            a.k_cache = c->k; a.v_cache = c->v; a.d_len = c->d_len;
+            a.B = p.B; a.Hq = m->hq_l; a.Hkv = m->hkv_l; a.D = m->D; a.max_seq = c->max_seq;
+            a.cos_t = m->cos_t; a.sin_t = m->sin_t;
+            a.q_norm = lw.qn; a.k_norm = lw.kn; a.norm_eps = eps;
+            a.scale = scale; a.out = w.att; a.part = w.part; a.max_splits = p.nsplit;
+            LUMEN_TRY(launch_attn_decode(ctx, a, s));
+        } else {
+            AttnPrefillArgs a;
+            a.q = w.qkv; a.k = w.qkv + m->qd_l; a.v = w.qkv + m->qd_l + m->kvd_l;
+            a.q_stride = qkvd; a.kv_stride = qkvd;
+            a.k_cache = c->k; a.v_cache = c->v;
+            a.past = c->len; a.S = p.S; a.B = p.B; a.Hq = m->hq_l; a.Hkv = m->hkv_l; a.D = m->D; a.max_seq = c->max_seq;
+            a.cos_t = m->cos_t; a.sin_t = m->sin_t;
+            a.q_norm = lw.qn; a.k_norm = lw.kn; a.norm_eps = eps;
+            a.scale = scale; a.causal = 1; a.out = w.att;
+            LUMEN_TRY(launch_attn_prefill(ctx, a, s));
+            LUMEN_TRY(launch_bump_len(ctx, c->d_len, (int)p.S, s));
+        }
+        LUMEN_TRY(matmul_dispatch(ctx, w.att, lw.wo, wdt, w.x, M, m->qd_l, H, res_x, s));
+        if (tp) LUMEN_TRY(tp_allreduce_sum(ctx, w.x, M * H, s));
+        // out = h + MLP(Norm(h))                                       llama.rs:113-115, :59-65
+        if (vec) {
+            LUMEN_TRY(launch_gemv_gate_up(ctx, w.x, lw.wgate, lw.wup, wdt, w.act, (int)M, H, m->inter_l, lw.norm2, eps, s));
+        } else {
+            LUMEN_TRY(launch_rmsnorm(ctx, w.x, lw.norm2, eps, w.nx, M, H, s));
+            LUMEN_TRY(launch_gemm_nk(ctx, w.nx, lw.wgate, wdt, w.gate, M, H, m->inter_l, nullptr, s));
+            LUMEN_TRY(launch_gemm_nk(ctx, w.nx, lw.wup, wdt, w.up, M, H, m->inter_l, nullptr, s));
+            LUMEN_TRY(launch_silu_mul(ctx, w.gate, w.up, w.act, M * m->inter_l, s));
+        }
+        LUMEN_TRY(matmul_dispatch(ctx, w.act, lw.wdown, wdt, w.x, M, m->inter_l, H, res_x, s));
+        if (tp) LUMEN_TRY(tp_allreduce_sum(ctx, w.x, M * H, s));
+    }
+    // Final norm + lm_head                                             llama.rs:202-205
+    const float *xin = w.x;
+    size_t rows = M;
+    if (last_only && p.S > 1) {
+        LUMEN_CUDA(ctx, cudaMemcpy2DAsync(w.last_x, H * 4, w.x + (p.S - 1) * H, p.S * H * 4, H * 4, p.B, cudaMemcpyDeviceToDevice, s));
+        xin = w.last_x;
+        rows = p.B;
+    }
+    float *lg = tp ? w.logits_local + (size_t)ctx->tp_rank * rows * m->vocab_l : w.logits;
+    if (rows <= 8 && rows * H * 4 <= 200 * 1024) {
+        GemvArgs g;
+        g.x = xin; g.w = m->lm_head; g.wdt = wdt; g.y = lg; g.M = (int)rows; g.K = H; g.N = m->vocab_l; g.ldy = m->vocab_l;
+        g.norm_w = m->final_norm; g.norm_eps = eps;
+        LUMEN_TRY(launch_gemv_nk(ctx, g, s));
+    } else {
+        LUMEN_TRY(launch_rmsnorm(ctx, xin, m->final_norm, eps, w.nx, rows, H, s));
+        LUMEN_TRY(launch_gemm_nk(ctx, w.nx, m->lm_head, wdt, lg, rows, H, m->vocab_l, nullptr, s));
+    }
+    if (tp) {
+        LUMEN_TRY(tp_allgather(ctx, lg, w.logits_local, rows * m->vocab_l, s));
+        for (int r = 0; r < ctx->tp_size; ++r)
+            LUMEN_CUDA(ctx, cudaMemcpy2DAsync(w.logits + (size_t)r * m->vocab_l, m->V * 4, w.logits_local + (size_t)r * rows * m->vocab_l,
+                                              m->vocab_l * 4, m->vocab_l * 4, rows, cudaMemcpyDeviceToDevice, s));
+    }
+    return LUMEN_OK;
+}
+
+int pick_decode_splits(const lumen_llama *m, size_t B, size_t len) {
+    // Power-of-two buckets so that a handful of graphs cover every context length.
+    int want = attn_decode_pick_splits(B, m->hkv_l, len, m->ctx->num_sms);
+    int n = 1;
+    while (n < want && n < kMaxSplits) n <<= 1;
+    return n;
+}
+
+int check_caches(lumen_llama *m, size_t b, size_t s, lumen_kv_cache **caches, size_t n_caches) {
+    lumen_ctx *ctx = m->ctx;
+    if (n_caches != m->L || !caches)
+        return set_error(ctx, LUMEN_ERR_CACHE_COUNT, "KV cache count mismatch: got %zu, expected %zu", n_caches, m->L);
+    for (size_t l = 0; l < m->L; ++l) {
+        lumen_kv_cache *c = caches[l];
+        if (!c) return set_error(ctx, LUMEN_ERR_INVALID, "null KV cache for layer %zu", l);
+        if (c->b != b || c->h_kv != m->hkv_l || c->d != m->D)
+            return set_error(ctx, LUMEN_ERR_SHAPE, "KV cache %zu geometry [%zu,%zu,%zu,%zu] does not match batch %zu / model", l, c->b, c->h_kv, c->max_seq, c->d, b);
+        if (c->len != caches[0]->len) return set_error(ctx, LUMEN_ERR_INVALID, "KV caches have different lengths");
+        if (s == 1) {  // decode asserts overflow before touching RoPE (self_attention.rs:144-149)
+            if (c->len + 1 > c->max_seq) return set_error(ctx, LUMEN_ERR_KV_OVERFLOW, "KV cache overflow: new_len=%zu > max_seq=%zu", c->len + 1, c->max_seq);
+            if (c->len >= m->cfg.max_seq_len) return set_error(ctx, LUMEN_ERR_ROPE_RANGE, "RoPE index out of range: pos %zu >= max %zu", c->len, m->cfg.max_seq_len);
+        } else {       // prefill rotates first (self_attention.rs:334-346)
+            if (c->len + s > m->cfg.max_seq_len) return set_error(ctx, LUMEN_ERR_ROPE_RANGE, "RoPE index out of range: offset %zu + len %zu > max %zu", c->len, s, m->cfg.max_seq_len);
+            if (c->len + s > c->max_seq) return set_error(ctx, LUMEN_ERR_KV_OVERFLOW, "KV cache overflow: new_len=%zu > max_seq=%zu", c->len + s, c->max_seq);
+        }
+    }
+    return LUMEN_OK;
+}
+
+// Runs one forward over ws.ids; decode steps go through a captured graph after the first call.
+int run_forward(lumen_llama *m, size_t b, size_t s, lumen_kv_cache **caches, bool last_only) {
+    lumen_ctx *ctx = m->ctx;
+    StepPlan p{b, s, b * s, s == 1, 1};
+    if (p.decode) p.nsplit = pick_decode_splits(m, b, caches[0]->len + 1);
+    int rc = LUMEN_OK;
+    if (p.decode && m->use_graph) {
+        auto key = std::make_tuple(b, p.nsplit, (const void *)caches[0]->k);
+        auto it = m->graphs.find(key);
+        if (it == m->graphs.end() && m->eager_runs[key]++ >= 1) {
+            cudaGraph_t graph = nullptr;
+            const unsigned long long before = ctx->launches;
+            LUMEN_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+            rc = enqueue_forward(m, p, caches, last_only);
+            cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
+            m->graph_nodes[key] = ctx->launches - before;  // captured, not run
+            ctx->launches = before;
+            if (rc != LUMEN_OK) {
+                if (graph) cudaGraphDestroy(graph);
+                return rc;
+            }
+            if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaStreamEndCapture");
+            cudaGraphExec_t exec = nullptr;
+            e = cudaGraphInstantiate(&exec, graph, 0);
+            cudaGraphDestroy(graph);
+            if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaGraphInstantiate");
+            it = m->graphs.emplace(key, exec).first;
+        }
+        if (it != m->graphs.end()) {
+            LUMEN_CUDA(ctx, cudaGraphLaunch(it->second, ctx->stream));
+            ctx->launches += m->graph_nodes[key];
+        } else {
+            rc = enqueue_forward(m, p, caches, last_only);
+        }
+    } else {
+        rc = enqueue_forward(m, p, caches, last_only);
+    }
+    if (rc == LUMEN_OK)
+        for (size_t l = 0; l < m->L; ++l) caches[l]->len += s;
+    return rc;
+}
+
+int forward_host(lumen_llama *m, const float *ids_host, size_t b, size_t s, lumen_kv_cache **caches, size_t n_caches,
+                 float *logits_host, bool last_only) {
+    if (!m || !ids_host || !logits_host) return LUMEN_ERR_INVALID;
+    lumen_ctx *ctx = m->ctx;
+    if (m->is_set.size() < m->n_expected) return set_error(ctx, LUMEN_ERR_MISSING_PARAM, "%zu of %zu parameters set", m->is_set.size(), m->n_expected);
+    const size_t M = b * s;
+    if (M == 0) return LUMEN_OK;
+    LUMEN_TRY(check_caches(m, b, s, caches, n_caches));
+    // Embedding range check on the host (src/layers/basic/embedding.rs:50-56) before anything is launched.
+    for (size_t i = 0; i < M; ++i) {
+        const float f = ids_host[i];
+        if (f >= (float)m->V && f == f) return set_error(ctx, LUMEN_ERR_EMBED_RANGE, "Embedding index out of bounds: %.0f >= %zu", (double)f, m->V);
+    }
+    LUMEN_TRY(ensure_workspace(m, M));
+    Workspace &w = m->ws;
+    // The pinned staging buffers are reused every step: wait for the previous step's copies first.
+    LUMEN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    memcpy(w.h_ids, ids_host, M * sizeof(float));
+    LUMEN_CUDA(ctx, cudaMemcpyAsync(w.ids, w.h_ids, M * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+    LUMEN_TRY(run_forward(m, b, s, caches, last_only));
+    const size_t rows = (last_only && s > 1) ? b : M;
+    const size_t n = rows * m->V;
+    if (n <= w.h_logits_elems) {
+        LUMEN_CUDA(ctx, cudaMemcpyAsync(w.h_logits, w.logits, n * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        LUMEN_TRY(check_device_status(ctx));
+        memcpy(logits_host, w.h_logits, n * 4);
+    } else {
+        LUMEN_CUDA(ctx, cudaMemcpyAsync(logits_host, w.logits, n * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        LUMEN_TRY(check_device_status(ctx));
+    }
+    return LUMEN_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int lumen_llama_new(lumen_ctx *ctx, const lumen_llama_config *cfg, lumen_llama **out) {
+    if (!ctx || !cfg || !out) return set_error(ctx, LUMEN_ERR_INVALID, "llama_new: null argument");
+    if (cfg->weight_dtype != LUMEN_F32 && cfg->weight_dtype != LUMEN_BF16) return set_error(ctx, LUMEN_ERR_DTYPE, "weight_dtype %d", (int)cfg->weight_dtype);
+    if (!cfg->num_attention_heads || !cfg->num_key_value_heads || cfg->num_attention_heads % cfg->num_key_value_heads)
+        return set_error(ctx, LUMEN_ERR_SHAPE, "num_attention_heads must be a positive multiple of num_key_value_heads");
+    if (!cfg->head_dim && cfg->hidden_size % cfg->num_attention_heads) return set_error(ctx, LUMEN_ERR_SHAPE, "Embed dim must be divisible by n_head");
+    auto *m = new lumen_llama();
+    m->ctx = ctx;
+    m->cfg = *cfg;
+    m->H = cfg->hidden_size; m->V = cfg->vocab_size; m->I = cfg->intermediate_size; m->L = cfg->num_hidden_layers;
+    m->D = cfg->head_dim ? cfg->head_dim : cfg->hidden_size / cfg->num_attention_heads;
+    m->esz = cfg->weight_dtype == LUMEN_F32 ? 4 : 2;
+    const size_t T = ctx->tp_size, r = ctx->tp_rank, Hq = cfg->num_attention_heads, Hkv = cfg->num_key_value_heads;
+    if (m->D == 0 || (m->D & 1) || m->D > 256) { delete m; return set_error(ctx, LUMEN_ERR_UNSUPPORTED, "head_dim %zu (need even, <= 256)", m->D); }
+    if (Hq % T || m->I % T || m->V % T) { delete m; return set_error(ctx, LUMEN_ERR_UNSUPPORTED, "heads/intermediate/vocab not divisible by tp_size %zu", T); }
+    m->hq_l = Hq / T;
+    m->q_head0 = r * m->hq_l;
+    if (Hkv % T == 0) {
+        m->hkv_l = Hkv / T;
+        m->kv_head0 = r * m->hkv_l;
+    } else if (T % Hkv == 0) {  // fewer KV heads than ranks: each KV head is replicated on T/Hkv ranks
+        m->hkv_l = 1;
+        m->kv_head0 = r / (T / Hkv);
+    } else {
+        delete m;
+        return set_error(ctx, LUMEN_ERR_UNSUPPORTED, "kv heads %zu vs tp_size %zu", Hkv, T);
+    }
+    m->qd_l = m->hq_l * m->D; m->kvd_l = m->hkv_l * m->D; m->inter_l = m->I / T; m->vocab_l = m->V / T;
+    m->qkv_rows = m->qd_l + 2 * m->kvd_l;
+    if (m->hq_l % m->hkv_l) { delete m; return set_error(ctx, LUMEN_ERR_UNSUPPORTED, "local q heads %zu not a multiple of local kv heads %zu", m->hq_l, m->hkv_l); }
+
+    // Slab layout.
+    const size_t e = m->esz, H = m->H;
+    size_t off = 0;
+    auto take = [&](size_t bytes) { size_t o = off; off += align_up(bytes, 256); return o; };
+    struct Off { size_t qkv, o, g, u, d, n1, n2, qn, kn; };
+    std::vector<Off> lo(m->L);
+    size_t o_embed = take(m->V * H * e);
+    for (size_t l = 0; l < m->L; ++l) {
+        lo[l].n1 = take(H * 4);
+        lo[l].qkv = take(m->qkv_rows * H * e);
+        lo[l].qn = take(cfg->qk_norm ? m->D * 4 : 0);
+        lo[l].kn = take(cfg->qk_norm ? m->D * 4 : 0);
+        lo[l].o = take(H * m->qd_l * e);
+        lo[l].n2 = take(H * 4);
+        lo[l].g = take(m->inter_l * H * e);
+        lo[l].u = take(m->inter_l * H * e);
+        lo[l].d = take(H * m->inter_l * e);
+    }
+    size_t o_fn = take(H * 4), o_lm = take(m->vocab_l * H * e);
+    const size_t half = m->D / 2;
+    size_t o_cos = take(cfg->max_seq_len * half * 4), o_sin = take(cfg->max_seq_len * half * 4);
+    m->wbytes = off;
+    cudaError_t ce = cudaMalloc(&m->wslab, std::max<size_t>(off, 256));
+    if (ce != cudaSuccess) { delete m; return cuda_fail(ctx, ce, "cudaMalloc(weight slab)"); }
+    m->embed = m->wslab + o_embed;
+    m->layers.resize(m->L);
+    for (size_t l = 0; l < m->L; ++l) {
+        LayerW &w = m->layers[l];
+        w.wqkv = m->wslab + lo[l].qkv; w.wo = m->wslab + lo[l].o; w.wgate = m->wslab + lo[l].g;
+        w.wup = m->wslab + lo[l].u; w.wdown = m->wslab + lo[l].d;
+        w.norm1 = (float *)(m->wslab + lo[l].n1); w.norm2 = (float *)(m->wslab + lo[l].n2);
+        if (cfg->qk_norm) { w.qn = (float *)(m->wslab + lo[l].qn); w.kn = (float *)(m->wslab + lo[l].kn); }
+    }
+    m->final_norm = (float *)(m->wslab + o_fn);
+    m->lm_head = m->wslab + o_lm;
+    m->cos_t = (float *)(m->wslab + o_cos);
+    m->sin_t = (float *)(m->wslab + o_sin);
+    std::vector<float> ch, sh;
+    rope_tables_host(m->D, cfg->max_seq_len, cfg->rope_theta, ch, sh);
+    if (!ch.empty()) {
+        cudaMemcpy(m->cos_t, ch.data(), ch.size() * 4, cudaMemcpyHostToDevice);
+        cudaMemcpy(m->sin_t, sh.data(), sh.size() * 4, cudaMemcpyHostToDevice);
+    }
+    m->n_expected = 3 + m->L * (cfg->qk_norm ? 11 : 9);
+    // Weights one decode step reads on this rank (the embedding contributes one row per token).
+    m->stream_bytes = m->L * ((m->qkv_rows * H + H * m->qd_l + 3 * m->inter_l * H) * e + 2 * H * 4 + (cfg->qk_norm ? 2 * m->D * 4 : 0)) +
+                      H * 4 + m->vocab_l * H * e;
+    const char *ng = getenv("LUMEN_NO_GRAPH");
+    m->use_graph = !(ng && ng[0] == '1');
+    *out = m;
+    return LUMEN_OK;
+}
+
+int lumen_llama_set_param(lumen_llama *m, const char *name, const void *host_data, const size_t *shape, int ndim, lumen_dtype dtype) {
+    if (!m || !name || !host_data || !shape) return LUMEN_ERR_INVALID;
+    lumen_ctx *ctx = m->ctx;
+    if (dtype != LUMEN_F32 && dtype != LUMEN_BF16) return set_error(ctx, LUMEN_ERR_DTYPE, "set_param: dtype %d", (int)dtype);
+    const size_t H = m->H, D = m->D, T = ctx->tp_size, r = ctx->tp_rank;
+    const size_t Hq = m->cfg.num_attention_heads, Hkv = m->cfg.num_key_value_heads;
+    const lumen_dtype wdt = m->cfg.weight_dtype;
+    const size_t se = dtype == LUMEN_F32 ? 4 : 2;
+    auto expect = [&](size_t r0, size_t c0) -> int {
+        if (c0 == 0) {
+            if (ndim != 1 || shape[0] != r0) return set_error(ctx, LUMEN_ERR_SHAPE, "%s: expected [%zu]", name, r0);
+        } else if (ndim != 2 || shape[0] != r0 || shape[1] != c0) {
+            return set_error(ctx, LUMEN_ERR_SHAPE, "%s: expected [%zu,%zu]", name, r0, c0);
+        }
+        return LUMEN_OK;
+    };
+    auto rows_at = [&](size_t row0, size_t cols) { return static_cast<const char *>(host_data) + row0 * cols * se; };
+    int rc = LUMEN_ERR_PARAM_NAME;
+    if (!strcmp(name, "model.embed_tokens.weight")) {
+        LUMEN_TRY(expect(m->V, H));
+        rc = upload_block(ctx, m->embed, wdt, host_data, dtype, m->V, H, 0, H);
+    } else if (!strcmp(name, "model.norm.weight")) {
+        LUMEN_TRY(expect(H, 0));
+        rc = upload_block(ctx, m->final_norm, LUMEN_F32, host_data, dtype, 1, H, 0, H);
+    } else if (!strcmp(name, "lm_head.weight")) {
+        LUMEN_TRY(expect(m->V, H));
+        rc = upload_block(ctx, m->lm_head, wdt, rows_at(r * m->vocab_l, H), dtype, m->vocab_l, H, 0, H);
+    } else {
+        long li = -1;
+        char rest[128];
+        if (sscanf(name, "model.layers.%ld.%127s", &li, rest) != 2 || li < 0 || (size_t)li >= m->L)
+            return set_error(ctx, LUMEN_ERR_PARAM_NAME, "unknown parameter '%s'", name);
+        LayerW &w = m->layers[li];
+        const size_t e = m->esz;
+        if (!strcmp(rest, "self_attn.q_proj.weight")) {
+            LUMEN_TRY(expect(Hq * D, H));
+            rc = upload_block(ctx, w.wqkv, wdt, rows_at(m->q_head0 * D, H), dtype, m->qd_l, H, 0, H);
+        } else if (!strcmp(rest, "self_attn.k_proj.weight")) {
+            LUMEN_TRY(expect(Hkv * D, H));
+            rc = upload_block(ctx, w.wqkv + m->qd_l * H * e, wdt, rows_at(m->kv_head0 * D, H), dtype, m->kvd_l, H, 0, H);
+        } else if (!strcmp(rest, "self_attn.v_proj.weight")) {
+            LUMEN_TRY(expect(Hkv * D, H));
+            rc = upload_block(ctx, w.wqkv + (m->qd_l + m->kvd_l) * H * e, wdt, rows_at(m->kv_head0 * D, H), dtype, m->kvd_l, H, 0, H);
+        } else if (!strcmp(rest, "self_attn.o_proj.weight")) {
+            LUMEN_TRY(expect(H, Hq * D));
+            rc = upload_block(ctx, w.wo, wdt, host_data, dtype, H, Hq * D, m->q_head0 * D, m->qd_l);
+        } else if (!strcmp(rest, "mlp.gate_proj.weight")) {
+            LUMEN_TRY(expect(m->I, H));
+            rc = upload_block(ctx, w.wgate, wdt, rows_at(r * m->inter_l, H), dtype, m->inter_l, H, 0, H);
+        } else if (!strcmp(rest, "mlp.up_proj.weight")) {
+            LUMEN_TRY(expect(m->I, H));
+            rc = upload_block(ctx, w.wup, wdt, rows_at(r * m->inter_l, H), dtype, m->inter_l, H, 0, H);
+        } else if (!strcmp(rest, "mlp.down_proj.weight")) {
+            LUMEN_TRY(expect(H, m->I));
+            rc = upload_block(ctx, w.wdown, wdt, host_data, dtype, H, m->I, r * m->inter_l, m->inter_l);
+        } else if (!strcmp(rest, "input_layernorm.weight")) {
+            LUMEN_TRY(expect(H, 0));
+            rc = upload_block(ctx, w.norm1, LUMEN_F32, host_data, dtype, 1, H, 0, H);
+        } else if (!strcmp(rest, "post_attention_layernorm.weight")) {
+            LUMEN_TRY(expect(H, 0));
+            rc = upload_block(ctx, w.norm2, LUMEN_F32, host_data, dtype, 1, H, 0, H);
+        } else if (m->cfg.qk_norm && !strcmp(rest, "self_attn.q_norm.weight")) {
+            LUMEN_TRY(expect(D, 0));
+            rc = upload_block(ctx, w.qn, LUMEN_F32, host_data, dtype, 1, D, 0, D);
+        } else if (m->cfg.qk_norm && !strcmp(rest, "self_attn.k_norm.weight")) {
+            LUMEN_TRY(expect(D, 0));
+            rc = upload_block(ctx, w.kn, LUMEN_F32, host_data, dtype, 1, D, 0, D);
+        } else {
+            return set_error(ctx, LUMEN_ERR_PARAM_NAME, "unknown parameter '%s'", name);
+        }
+        (void)T;
+    }
+    if (rc == LUMEN_ERR_PARAM_NAME) return set_error(ctx, rc, "unknown parameter '%s'", name);
+    if (rc == LUMEN_OK) m->is_set[name] = true;
+    return rc;
+}
+
+int lumen_llama_init_kv_caches(lumen_llama *m, size_t batch, lumen_kv_cache **caches_out) {
+    if (!m || !caches_out) return LUMEN_ERR_INVALID;
+    lumen_ctx *ctx = m->ctx;
+    const size_t per = batch * m->hkv_l * m->cfg.max_seq_len * m->D;  // floats per k (or v) slab of a layer
+    const size_t bytes = m->L * 2 * per * sizeof(float) + align_up(m->L * sizeof(int), 256);
+    auto *slab = new lumen_storage();
+    slab->ctx = ctx;
+    slab->bytes = bytes;
+    slab->refs = 0;
+    cudaError_t e = cudaMalloc(&slab->ptr, std::max<size_t>(bytes, 256));
+    if (e != cudaSuccess) { delete slab; return cuda_fail(ctx, e, "cudaMalloc(kv slab)"); }
+    LUMEN_CUDA(ctx, cudaMemsetAsync(slab->ptr, 0, bytes, ctx->stream));  // Array4::zeros, self_attention.rs:35-36
+    float *base = static_cast<float *>(slab->ptr);
+    int *lens = reinterpret_cast<int *>(base + m->L * 2 * per);
+    for (size_t l = 0; l < m->L; ++l) {
+        auto *c = new lumen_kv_cache();
+        c->ctx = ctx; c->b = batch; c->h_kv = m->hkv_l; c->max_seq = m->cfg.max_seq_len; c->d = m->D;
+        c->k = base + (2 * l) * per;
+        c->v = base + (2 * l + 1) * per;
+        c->d_len = lens + l;
+        c->owns_slab = false;
+        c->slab = slab;
+        slab->refs += 1;
+        caches_out[l] = c;
+    }
+    if (m->L == 0) { cudaFree(slab->ptr); delete slab; }
+    return LUMEN_OK;
+}
+
+int lumen_llama_reset_kv_caches(lumen_llama *m, lumen_kv_cache **caches, size_t n_caches) {
+    if (!m || (!caches && n_caches)) return LUMEN_ERR_INVALID;
+    for (size_t i = 0; i < n_caches; ++i) LUMEN_TRY(lumen_kv_reset(caches[i]));
+    return LUMEN_OK;
+}
+
+int lumen_llama_forward(lumen_llama *m, const float *ids_host, size_t b, size_t s, lumen_kv_cache **caches, size_t n_caches,
+                        size_t pos, float *logits_host) {
+    (void)pos;  // `_pos` is ignored by the reference too (llama.rs:180-181)
+    return forward_host(m, ids_host, b, s, caches, n_caches, logits_host, false);
+}
+
+int lumen_llama_forward_last(lumen_llama *m, const float *ids_host, size_t b, size_t s, lumen_kv_cache **caches, size_t n_caches,
+                             size_t pos, float *logits_host) {
+    (void)pos;
+    return forward_host(m, ids_host, b, s, caches, n_caches, logits_host, true);
+}
+
+int lumen_llama_forward_device(lumen_llama *m, const float *ids_dev, size_t b, size_t s, lumen_kv_cache **caches, size_t n_caches,
+                               float *logits_dev) {
+    if (!m || !ids_dev || !logits_dev) return LUMEN_ERR_INVALID;
+    lumen_ctx *ctx = m->ctx;
+    if (m->is_set.size() < m->n_expected) return set_error(ctx, LUMEN_ERR_MISSING_PARAM, "%zu of %zu parameters set", m->is_set.size(), m->n_expected);
+    const size_t M = b * s;
+    if (M == 0) return LUMEN_OK;
+    LUMEN_TRY(check_caches(m, b, s, caches, n_caches));
+    LUMEN_TRY(ensure_workspace(m, M));
+    LUMEN_CUDA(ctx, cudaMemcpyAsync(m->ws.ids, ids_dev, M * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
+    LUMEN_TRY(run_forward(m, b, s, caches, false));
+    LUMEN_CUDA(ctx, cudaMemcpyAsync(logits_dev, m->ws.logits, M * m->V * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
+    return LUMEN_OK;
+}
+
+size_t lumen_llama_weight_bytes(const lumen_llama *m) { return m ? m->stream_bytes : 0; }
+
+int lumen_llama_free(lumen_llama *m) {
+    if (!m) return LUMEN_ERR_INVALID;
+    cudaStreamSynchronize(m->ctx->stream);
+    drop_graphs(m);
+    if (m->ws.base) cudaFree(m->ws.base);
+    if (m->ws.h_ids) cudaFreeHost(m->ws.h_ids);
+    if (m->ws.h_logits) cudaFreeHost(m->ws.h_logits);
+    if (m->wslab) cudaFree(m->wslab);
+    delete m;
+    return LUMEN_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,103 @@
+// Tensor-parallel plumbing: one context = one rank = one GPU; collectives go through NCCL over
+// NVLink.  NCCL is bound at run time with dlopen("libnccl.so.2") so that the library carries no
+// link-time dependency and shares the NCCL already loaded by the host process when there is one.
+// The reference has no multi-device code; the sharding layout (row-split q/k/v/gate/up, column-split
+// o/down, one sum-allreduce after each) is described where the model applies it.
+#include <dlfcn.h>
+
+#include "common.cuh"
+
+namespace lumen {
+namespace {
+
+struct NcclId {
+    char bytes[LUMEN_NCCL_ID_BYTES];
+};
+typedef int (*fn_get_unique_id)(NcclId *);
+typedef int (*fn_comm_init_rank)(void **, int, NcclId, int);
+typedef int (*fn_comm_destroy)(void *);
+typedef int (*fn_all_reduce)(const void *, void *, size_t, int, int, void *, cudaStream_t);
+typedef int (*fn_all_gather)(const void *, void *, size_t, int, void *, cudaStream_t);
+typedef const char *(*fn_error_string)(int);
+
+struct NcclApi {
+    void *handle = nullptr;
+    fn_get_unique_id get_unique_id = nullptr;
+    fn_comm_init_rank comm_init_rank = nullptr;
+    fn_comm_destroy comm_destroy = nullptr;
+    fn_all_reduce all_reduce = nullptr;
+    fn_all_gather all_gather = nullptr;
+    fn_error_string error_string = nullptr;
+    bool ok = false;
+};
+
+NcclApi &api() {
+    static NcclApi a;
+    if (a.handle) return a;
+    a.handle = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!a.handle) a.handle = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+    if (!a.handle) return a;
+    a.get_unique_id = (fn_get_unique_id)dlsym(a.handle, "ncclGetUniqueId");
+    a.comm_init_rank = (fn_comm_init_rank)dlsym(a.handle, "ncclCommInitRank");
+    a.comm_destroy = (fn_comm_destroy)dlsym(a.handle, "ncclCommDestroy");
+    a.all_reduce = (fn_all_reduce)dlsym(a.handle, "ncclAllReduce");
+    a.all_gather = (fn_all_gather)dlsym(a.handle, "ncclAllGather");
+    a.error_string = (fn_error_string)dlsym(a.handle, "ncclGetErrorString");
+    a.ok = a.get_unique_id && a.comm_init_rank && a.comm_destroy && a.all_reduce && a.all_gather && a.error_string;
+    return a;
+}
+
+constexpr int kNcclFloat32 = 7;  // ncclFloat32 in nccl.h's ncclDataType_t
+constexpr int kNcclSum = 0;      // ncclSum in ncclRedOp_t
+
+int nccl_fail(lumen_ctx *ctx, int rc, const char *what) {
+    return set_error(ctx, LUMEN_ERR_NCCL, "NCCL error %d (%s) in %s", rc, api().error_string ? api().error_string(rc) : "?", what);
+}
+
+}  // namespace
+
+int tp_init(lumen_ctx *ctx, const void *unique_id) {
+    if (!unique_id) return set_error(ctx, LUMEN_ERR_INVALID, "tp_size > 1 needs an NCCL unique id");
+    NcclApi &a = api();
+    if (!a.ok) return set_error(ctx, LUMEN_ERR_NCCL, "libnccl.so.2 could not be loaded: %s", dlerror());
+    NcclId id;
+    memcpy(id.bytes, unique_id, sizeof(id.bytes));
+    int rc = a.comm_init_rank(&ctx->nccl_comm, ctx->tp_size, id, ctx->tp_rank);
+    if (rc != 0) return nccl_fail(ctx, rc, "ncclCommInitRank");
+    return LUMEN_OK;
+}
+
+void tp_shutdown(lumen_ctx *ctx) {
+    if (ctx->nccl_comm && api().ok) api().comm_destroy(ctx->nccl_comm);
+    ctx->nccl_comm = nullptr;
+}
+
+int tp_allreduce_sum(lumen_ctx *ctx, float *buf, size_t n, cudaStream_t s) {
+    if (ctx->tp_size == 1) return LUMEN_OK;
+    int rc = api().all_reduce(buf, buf, n, kNcclFloat32, kNcclSum, ctx->nccl_comm, s);
+    if (rc != 0) return nccl_fail(ctx, rc, "ncclAllReduce");
+    return LUMEN_OK;
+}
+
+int tp_allgather(lumen_ctx *ctx, const float *send, float *recv, size_t n_per_rank, cudaStream_t s) {
+    if (ctx->tp_size == 1) {
+        if (send != recv) LUMEN_CUDA(ctx, cudaMemcpyAsync(recv, send, n_per_rank * 4, cudaMemcpyDeviceToDevice, s));
+        return LUMEN_OK;
+    }
+    int rc = api().all_gather(send, recv, n_per_rank, kNcclFloat32, ctx->nccl_comm, s);
+    if (rc != 0) return nccl_fail(ctx, rc, "ncclAllGather");
+    return LUMEN_OK;
+}
+
+}  // namespace lumen
+
+extern "C" int lumen_nccl_unique_id(void *id_out_128_bytes) {
+    if (!id_out_128_bytes) return LUMEN_ERR_INVALID;
+    auto &a = lumen::api();
+    if (!a.ok) return LUMEN_ERR_NCCL;
+    lumen::NcclId id;
+    int rc = a.get_unique_id(&id);
+    if (rc != 0) return LUMEN_ERR_NCCL;
+    memcpy(id_out_128_bytes, id.bytes, sizeof(id.bytes));
+    return LUMEN_OK;
+}

@@ -1,0 +1,44 @@
+"""Seeded synthetic weights and token ids with the shapes of the benchmark configurations.
+
+The reference publishes no weights-free benchmark data; the configurations name architectures
+only, so weights are N(0, 0.02) draws and prompts are uniform token ids.  One numpy PCG64 stream
+per seed, parameters drawn in sorted-name order, RMSNorm gains fixed at 1.0 (not drawn).
+"""
+from __future__ import annotations
+
+import numpy as np
+
+from .llama import LlamaConfig
+from .tensor import bf16_bits_to_f32, f32_to_bf16_bits
+
+TINYLLAMA = dict(vocab_size=32000, hidden_size=2048, intermediate_size=5632, num_hidden_layers=22,
+                 num_attention_heads=32, num_key_value_heads=4, rms_norm_eps=1e-5, max_seq_len=2048,
+                 rope_theta=10000.0)
+LLAMA2_7B = dict(vocab_size=32000, hidden_size=4096, intermediate_size=11008, num_hidden_layers=32,
+                 num_attention_heads=32, num_key_value_heads=32, rms_norm_eps=1e-5, max_seq_len=1024,
+                 rope_theta=10000.0)
+QWEN3_8B = dict(vocab_size=151936, hidden_size=4096, intermediate_size=12288, num_hidden_layers=36,
+                num_attention_heads=32, num_key_value_heads=8, rms_norm_eps=1e-6, max_seq_len=4352,
+                rope_theta=1e6, head_dim=128, qk_norm=True)
+
+
+def iter_params(cfg: LlamaConfig, seed: int, std: float = 0.02, round_bf16: bool = False):
+    """Yield (name, f32 array) for every parameter of `cfg`, deterministically from `seed`.
+
+    With `round_bf16` the matrices are rounded to bf16 (nearest even) and widened back, i.e. the
+    values a bf16 checkpoint holds after the reference loader's upcast (src/loader.rs:50-64).
+    """
+    rng = np.random.default_rng(seed)
+    for name, shape in sorted(cfg.param_shapes().items()):
+        if len(shape) == 1:
+            yield name, np.ones(shape, np.float32)
+            continue
+        w = rng.standard_normal(shape, dtype=np.float32)
+        w *= np.float32(std)
+        if round_bf16:
+            w = bf16_bits_to_f32(f32_to_bf16_bits(w)).reshape(shape)
+        yield name, w
+
+
+def token_ids(seed: int, n: int, vocab: int) -> np.ndarray:
+    return np.random.default_rng(seed).integers(0, vocab, size=n).astype(np.float32)

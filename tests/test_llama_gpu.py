@@ -1,0 +1,176 @@
+"""GPU parity tests of LlamaModel::forward (prefill + teacher-forced decode) against the CPU oracle
+and the committed fixtures.  Tolerances are the north star's: per-step logits within rel 1e-4 for
+f32 weights, 1e-2 for bf16 weights (rel = max|a-b| / max|b| over one logits vector), and identical
+argmax token ids under teacher forcing."""
+import os
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from helpers import TOL_BF16, TOL_F32, cfg_obj, make_params, rel_err, small_cfg
+
+pytestmark = pytest.mark.gpu
+GOLD = Path(__file__).resolve().parent / "golden"
+
+
+def _gpu_run(L, cfg, params, ids, prompt_len, weight_dtype="f32", last_only=False):
+    model = L.LlamaModel(cfg_obj(L, cfg, weight_dtype))
+    model.load_state(params)
+    caches = model.init_kv_caches(ids.shape[0])
+    outs = []
+    with L.no_grad():
+        lg = model.forward(ids[:, :prompt_len], caches, 0, last_only=last_only)
+        outs.append(lg[:, None] if last_only else lg)
+        for t in range(prompt_len, ids.shape[1]):
+            outs.append(model.forward(ids[:, t:t + 1], caches, 0))
+    assert all(c.len == ids.shape[1] for c in caches)
+    return np.concatenate(outs, axis=1), model, caches
+
+
+def _oracle_run(oracle, cfg, params, ids, prompt_len, prec="f32"):
+    m = oracle.Llama(cfg, params, prec)
+    caches = m.init_kv_caches(ids.shape[0])
+    outs = [m.forward(ids[:, :prompt_len], caches)]
+    for t in range(prompt_len, ids.shape[1]):
+        outs.append(m.forward(ids[:, t:t + 1], caches))
+    return np.concatenate(outs, axis=1), caches
+
+
+@pytest.mark.parametrize("name", ["llama_small_gqa", "llama_small_b3", "llama_small_qknorm"])
+def test_golden_fixtures(L, name):
+    g = np.load(GOLD / f"{name}.npz")
+    cfg = {k[4:]: g[k].item() for k in g.files if k.startswith("cfg_")}
+    params = make_params(L, cfg, int(g["seed"]), std=float(g["std"]), random_norms=True)
+    pl = int(g["prompt_len"])
+    got, _, _ = _gpu_run(L, cfg, params, g["ids"], pl)
+    got = got[:, pl - 1:]
+    want = g["logits"]
+    for t in range(want.shape[1]):
+        assert rel_err(got[:, t], want[:, t]) < TOL_F32, (name, t)
+    assert np.array_equal(got.argmax(-1), want.argmax(-1))
+
+
+@pytest.mark.parametrize("over,batch,prompt", [
+    (dict(), 1, 5), (dict(num_key_value_heads=4), 2, 1), (dict(num_key_value_heads=1), 3, 7),
+    (dict(hidden_size=128, num_attention_heads=2, intermediate_size=200, vocab_size=301), 9, 3),
+    (dict(head_dim=32, qk_norm=True, rope_theta=1e6), 2, 4),
+])
+@pytest.mark.parametrize("wdt", ["f32", "bf16"])
+def test_small_models_vs_oracle(L, oracle, over, batch, prompt, wdt):
+    """Covers batch sizes on both sides of the vector-matrix / GEMM switch (M <= 8 vs M > 8)."""
+    cfg = small_cfg(**over)
+    params = make_params(L, cfg, 21, std=0.08, round_bf16=(wdt == "bf16"), random_norms=True)
+    ids = np.random.default_rng(22).integers(0, cfg["vocab_size"], size=(batch, prompt + 6)).astype(np.float32)
+    got, _, gc = _gpu_run(L, cfg, params, ids, prompt, wdt)
+    want, oc = _oracle_run(oracle, cfg, params, ids, prompt, "f64")
+    tol = TOL_BF16 if wdt == "bf16" else TOL_F32
+    for t in range(ids.shape[1]):
+        assert rel_err(got[:, t], want[:, t]) < tol, t
+    # bf16-rounded weights are exactly representable, so the bf16 model is as close as the f32 one
+    assert rel_err(got, want) < TOL_F32
+    # KV cache contents (rotated keys, values) agree with the oracle's
+    for l in range(cfg["num_hidden_layers"]):
+        k, v = gc[l].read()
+        assert rel_err(k, oc[l].k) < 1e-5 and rel_err(v, oc[l].v) < 1e-5
+
+
+def test_forward_last_and_device_entry_points(L, oracle):
+    cfg = small_cfg()
+    params = make_params(L, cfg, 31, std=0.08)
+    ids = np.random.default_rng(32).integers(0, cfg["vocab_size"], size=(2, 6)).astype(np.float32)
+    full, _, _ = _gpu_run(L, cfg, params, ids, 4)
+    last, _, _ = _gpu_run(L, cfg, params, ids, 4, last_only=True)
+    assert np.array_equal(last[:, 0], full[:, 3]) and np.array_equal(last[:, 1:], full[:, 4:])
+    # device-resident ids / logits
+    model = L.LlamaModel(cfg_obj(L, cfg))
+    model.load_state(params)
+    caches = model.init_kv_caches(2)
+    d_out = L.Tensor.from_array_no_grad(np.zeros((2, 4, cfg["vocab_size"]), np.float32))
+    d_ids4 = L.Tensor.from_array_no_grad(np.ascontiguousarray(ids[:, :4]))
+    with L.no_grad():
+        model.forward_device(d_ids4.data_ptr, 2, 4, caches, d_out.data_ptr)
+    model.ctx.synchronize()
+    assert np.array_equal(d_out.data(), full[:, :4])
+
+
+def test_graph_replay_equals_eager(L, monkeypatch):
+    """Decode steps replay a captured CUDA graph from the third call on; results are identical to the
+    eager launches and the context length advances on the device."""
+    cfg = small_cfg(max_seq_len=300)
+    params = make_params(L, cfg, 41, std=0.08)
+    ids = np.random.default_rng(42).integers(0, cfg["vocab_size"], size=(1, 280)).astype(np.float32)
+    graph, _, _ = _gpu_run(L, cfg, params, ids, 3)
+    monkeypatch.setenv("LUMEN_NO_GRAPH", "1")
+    eager, _, _ = _gpu_run(L, cfg, params, ids, 3)
+    assert np.array_equal(graph, eager)
+
+
+def test_reset_and_reuse_caches(L):
+    cfg = small_cfg()
+    params = make_params(L, cfg, 51, std=0.08)
+    ids = np.random.default_rng(52).integers(0, cfg["vocab_size"], size=(1, 9)).astype(np.float32)
+    first, model, caches = _gpu_run(L, cfg, params, ids, 4)
+    model.reset_kv_caches(caches)  # len = 0, slab contents kept (llama.rs:172-176)
+    assert all(c.len == 0 for c in caches)
+    with L.no_grad():
+        again = [model.forward(ids[:, :4], caches)] + [model.forward(ids[:, t:t + 1], caches) for t in range(4, 9)]
+    assert np.array_equal(first, np.concatenate(again, axis=1))
+
+
+def test_error_conditions(L):
+    cfg = small_cfg(max_seq_len=6)
+    model = L.LlamaModel(cfg_obj(L, cfg))
+    caches = model.init_kv_caches(1)
+    one = np.zeros((1, 1), np.float32)
+    with pytest.raises(NotImplementedError):
+        model.forward(one, caches)  # outside no_grad: training path is out of scope
+    with L.no_grad():
+        with pytest.raises(L.LumenError) as e:
+            model.forward(one, caches)
+        assert e.value.code == L._lib.ERR_MISSING_PARAM
+        model.load_state(make_params(L, cfg, 1))
+        with pytest.raises(L.LumenError) as e:
+            model.set_param("model.layers.9.mlp.up_proj.weight", np.zeros((160, 64), np.float32))
+        assert e.value.code == L._lib.ERR_PARAM_NAME
+        with pytest.raises(L.LumenError) as e:
+            model.set_param("lm_head.weight", np.zeros((5, 5), np.float32))
+        assert e.value.code == L._lib.ERR_SHAPE
+        with pytest.raises(L.LumenError) as e:  # llama.rs:182-188
+            model.forward(one, caches[:1])
+        assert e.value.code == L._lib.ERR_CACHE_COUNT
+        with pytest.raises(L.LumenError) as e:  # embedding.rs:55
+            model.forward(np.full((1, 1), 97.0, np.float32), caches)
+        assert e.value.code == L._lib.ERR_EMBED_RANGE
+        assert caches[0].len == 0  # nothing ran
+        with pytest.raises(L.LumenError) as e:  # prefill longer than the RoPE table
+            model.forward(np.zeros((1, 7), np.float32), caches)
+        assert e.value.code == L._lib.ERR_ROPE_RANGE
+        model.forward(np.zeros((1, 5), np.float32), caches)
+        model.forward(one, caches)
+        with pytest.raises(L.LumenError) as e:  # self_attention.rs:144-149
+            model.forward(one, caches)
+        assert e.value.code == L._lib.ERR_KV_OVERFLOW
+        assert caches[0].len == 6
+        wrong = L.LlamaModel(cfg_obj(L, small_cfg(max_seq_len=6, num_key_value_heads=4)))
+        with pytest.raises(L.LumenError) as e:
+            model.forward(one, wrong.init_kv_caches(1))
+        assert e.value.code == L._lib.ERR_SHAPE
+
+
+@pytest.mark.parametrize("wdt,prompt,steps", [("f32", 32, 128), ("bf16", 32, 24)])
+def test_tinyllama_config1_teacher_forced(L, oracle, wdt, prompt, steps):
+    """BASELINE config 1 at full size: TinyLlama-1.1B shape, weights N(0,0.02) seed 0 (gains 1.0), 32
+    prompt ids from seed 1 and teacher-forced decode steps at batch 1, cache sized to 2048.  The bf16
+    variant rounds the same weights to bf16 and runs fewer steps to bound the CPU oracle's time."""
+    from lumen_b200 import synth
+    cfg = dict(synth.TINYLLAMA)
+    params = make_params(L, cfg, 0, std=0.02, round_bf16=(wdt == "bf16"))
+    ids = synth.token_ids(1, prompt + steps, cfg["vocab_size"])[None, :]
+    got, _, _ = _gpu_run(L, cfg, params, ids, prompt, wdt)
+    want, _ = _oracle_run(oracle, cfg, params, ids, prompt, "f32")
+    tol = TOL_BF16 if wdt == "bf16" else TOL_F32
+    errs = [rel_err(got[0, t], want[0, t]) for t in range(prompt - 1, prompt + steps)]
+    print(f"\nconfig1 {wdt}: max rel err over {len(errs)} steps = {max(errs):.3e}")
+    assert max(errs) < tol
+    assert np.array_equal(got[0, prompt - 1:].argmax(-1), want[0, prompt - 1:].argmax(-1))
