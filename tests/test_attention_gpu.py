@@ -18,9 +18,11 @@ def _decode_case(L, oracle, ctx, b, hq, hkv, d, ctx_len, max_seq, seed, steps=1,
     gc = L.KVCacheInner(b, hkv, max_seq, d)
     gc.write(k, v, past)
     oc = oracle.KVCache(b, hkv, max_seq, d, "f64")
-    oc.k[...] = k
-    oc.v[...] = v
-    oc.len = past
+    oc32 = oracle.KVCache(b, hkv, max_seq, d, "f32")
+    for c in (oc, oc32):
+        c.k[...] = k
+        c.v[...] = v
+        c.len = past
     rope = L.RotaryEmbedding(d, max_seq, theta)
     worst = 0.0
     for _ in range(steps):
@@ -28,17 +30,21 @@ def _decode_case(L, oracle, ctx, b, hq, hkv, d, ctx_len, max_seq, seed, steps=1,
         kn = rng.standard_normal((b, 1, hkv * d), dtype=np.float32)
         vn = rng.standard_normal((b, 1, hkv * d), dtype=np.float32)
         want = oracle.attention(q, kn, vn, oc, hq, theta, max_seq)  # [B,1,Hq,D] float64
+        want32 = oracle.attention(q, kn, vn, oc32, hq, theta, max_seq)
         tq, tk, tv = (L.Tensor.from_array_no_grad(a) for a in (q, kn, vn))
         out = L.Tensor.from_array_no_grad(np.zeros((b, hq * d), np.float32))
         L.attention_decode(ctx, tq.data_ptr, tk.data_ptr, tv.data_ptr, hq, gc, rope, out.data_ptr)
         got = out.data().reshape(b, 1, hq, d)
-        worst = max(worst, rel_err(got, want))
+        # the f64 shadow also evaluates the RoPE angles in f64, which moves far positions by ~pos*6e-8 rad;
+        # the f32 oracle shares the reference's f32 table recipe
+        worst = max(worst, min(rel_err(got, want), rel_err(got, want32)))
+        assert rel_err(got, want) < 1e-3
         assert gc.len == oc.len
-    # the appended rows must match the oracle's cache (rotated k: same table, unfused f32 ops)
+    # the appended rows are bit-identical to the f32 oracle's (same f32 table, unfused f32 mul/add/sub)
     gk, gv = gc.read()
     n = gc.len
-    assert rel_err(gk[:, :, :n], oc.k[:, :, :n]) < 1e-6
-    assert np.array_equal(gv[:, :, :n], oc.v[:, :, :n].astype(np.float32))
+    assert np.array_equal(gk[:, :, :n], oc32.k[:, :, :n])
+    assert np.array_equal(gv[:, :, :n], oc32.v[:, :, :n])
     assert np.all(gk[:, :, n:] == 0)
     return worst
 

@@ -124,7 +124,8 @@ def test_rmsnorm(L, oracle, rows, dim):
     w = (1 + 0.1 * rng.standard_normal(dim)).astype(np.float32)
     got = L.RMSNorm(dim, 1e-5, weight=L.Tensor.from_array_no_grad(w)).forward(L.Tensor.from_array_no_grad(x)).data()
     assert rel_err(got, oracle.rmsnorm(x, w, 1e-5, "f64")) < 1e-6
-    assert rel_err(got, oracle.rmsnorm(x, w, 1e-5, "f32")) < 1e-6
+    # the f32 oracle's sequential sum of squares is the less accurate side for long rows
+    assert rel_err(got, oracle.rmsnorm(x, w, 1e-5, "f32")) < 5e-6
 
 
 def test_elementwise_bit_exact(L, oracle):
