@@ -208,6 +208,13 @@ int lumen_llama_forward_device(lumen_llama *m, const float *ids_dev, size_t b, s
 int lumen_llama_free(lumen_llama *m);
 /* Bytes of weights one decode step streams on this rank (for roofline accounting). */
 size_t lumen_llama_weight_bytes(const lumen_llama *m);
+/* Tracing (no counterpart in the reference, which has no timers): when the environment variable
+ * LUMEN_DECODE_TRACE=1 was set at lumen_llama_new, the persistent batch-1 decode kernel stores, for CTA 0,
+ * a nanosecond timestamp at the start of each phase, after its prologue and after its last weight tile
+ * (3 per phase; phases per layer: qkv, attention, o_proj, gate/up, down; then lm_head), plus one at the
+ * end, followed by one stamp per phase taken when the producer issued the phase's first weight tile.
+ * Copies up to `capacity` stamps of the last step to the host. */
+int lumen_llama_decode_trace(lumen_llama *m, uint64_t *out, size_t capacity, size_t *n_out);
 
 #ifdef __cplusplus
 }

@@ -95,6 +95,7 @@ PROTOTYPES = {
     "lumen_llama_forward_device": (_I, [_P, _FP, _SZ, _SZ, _PP, _SZ, _FP]),
     "lumen_llama_free": (_I, [_P]),
     "lumen_llama_weight_bytes": (_SZ, [_P]),
+    "lumen_llama_decode_trace": (_I, [_P, C.POINTER(C.c_uint64), _SZ, _SZP]),
 }
 
 _lib = None

@@ -62,6 +62,9 @@ int check_device_status(lumen_ctx *ctx) {
     if (ctx->h_status->code != 0) {
         int code = ctx->h_status->code, d0 = ctx->h_status->detail0, d1 = ctx->h_status->detail1;
         LUMEN_CUDA(ctx, cudaMemsetAsync(ctx->d_status, 0, sizeof(DeviceStatus), ctx->stream));
+        // A persistent decode kernel that gave up leaves its barrier counter mid-way: start over.
+        LUMEN_CUDA(ctx, cudaMemsetAsync(ctx->d_mega_sync, 0, 16, ctx->stream));
+        ctx->mega_bar_base = 0;
         if (code == LUMEN_ERR_EMBED_RANGE) return set_error(ctx, code, "Embedding index out of bounds: id %d at position %d", d1, d0);
         if (code == LUMEN_ERR_TIMEOUT) return set_error(ctx, code, "device-side wait gave up (site %d, value %d)", d0, d1);
         return set_error(ctx, code, "device status %d (%d, %d)", code, d0, d1);
@@ -134,6 +137,8 @@ int lumen_ctx_create(int device, int tp_rank, int tp_size, const void *nccl_uniq
     if ((e = cudaMalloc(&ctx->d_status, sizeof(DeviceStatus))) != cudaSuccess) return fail(e, "cudaMalloc(status)");
     if ((e = cudaMemset(ctx->d_status, 0, sizeof(DeviceStatus))) != cudaSuccess) return fail(e, "cudaMemset(status)");
     if ((e = cudaMallocHost(&ctx->h_status, sizeof(DeviceStatus))) != cudaSuccess) return fail(e, "cudaMallocHost(status)");
+    if ((e = cudaMalloc(&ctx->d_mega_sync, 16)) != cudaSuccess) return fail(e, "cudaMalloc(barrier)");
+    if ((e = cudaMemset(ctx->d_mega_sync, 0, 16)) != cudaSuccess) return fail(e, "cudaMemset(barrier)");
     if (tp_size > 1) {
         int rc = tp_init(ctx, nccl_unique_id);
         if (rc != LUMEN_OK) {
@@ -154,6 +159,7 @@ int lumen_ctx_destroy(lumen_ctx *ctx) {
         tp_shutdown(ctx);
     }
     if (ctx->d_status) cudaFree(ctx->d_status);
+    if (ctx->d_mega_sync) cudaFree(ctx->d_mega_sync);
     if (ctx->h_status) cudaFreeHost(ctx->h_status);
     if (ctx->stream) cudaStreamDestroy(ctx->stream);
     delete ctx;

@@ -15,6 +15,7 @@
 #include <tuple>
 
 #include "common.cuh"
+#include "decode_mega.cuh"
 
 using namespace lumen;
 
@@ -76,6 +77,11 @@ struct lumen_llama {
     std::map<std::tuple<size_t, int, const void *>, int> eager_runs;
     std::map<std::tuple<size_t, int, const void *>, unsigned long long> graph_nodes;
     bool use_graph = true;
+    // persistent whole-step decode kernel (batch 1)
+    bool use_mega = true;
+    MegaLayer *d_mega_layers = nullptr;
+    const void *mega_key = nullptr;  // first cache's k pointer the layer table was built for
+    unsigned long long *d_trace = nullptr;  // phase timestamps of the last persistent step (LUMEN_DECODE_TRACE=1)
 };
 
 namespace {
@@ -284,9 +290,68 @@ int check_caches(lumen_llama *m, size_t b, size_t s, lumen_kv_cache **caches, si
     return LUMEN_OK;
 }
 
-// Runs one forward over ws.ids; decode steps go through a captured graph after the first call.
+// Batch-1 decode through the persistent kernel: one launch per token.
+int run_mega(lumen_llama *m, lumen_kv_cache **caches) {
+    lumen_ctx *ctx = m->ctx;
+    if (m->mega_key != (const void *)caches[0]->k || !m->d_mega_layers) {
+        std::vector<MegaLayer> host(m->L);
+        for (size_t l = 0; l < m->L; ++l) {
+            const LayerW &w = m->layers[l];
+            host[l] = MegaLayer{w.wqkv, w.wo, w.wgate, w.wup, w.wdown, w.norm1, w.norm2, w.qn, w.kn,
+                                caches[l]->k, caches[l]->v, caches[l]->d_len};
+        }
+        if (!m->d_mega_layers) LUMEN_CUDA(ctx, cudaMalloc(&m->d_mega_layers, std::max<size_t>(m->L, 1) * sizeof(MegaLayer)));
+        LUMEN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // earlier launches may still read the table
+        LUMEN_CUDA(ctx, cudaMemcpy(m->d_mega_layers, host.data(), m->L * sizeof(MegaLayer), cudaMemcpyHostToDevice));
+        m->mega_key = caches[0]->k;
+    }
+    Workspace &w = m->ws;
+    MegaParams p{};
+    p.layers = m->d_mega_layers;
+    p.L = (int)m->L; p.H = (int)m->H; p.I = (int)m->inter_l; p.V = (int)m->vocab_l; p.vocab = (int)m->V;
+    p.Hq = (int)m->hq_l; p.Hkv = (int)m->hkv_l; p.D = (int)m->D;
+    p.qkv_rows = (int)m->qkv_rows; p.qd = (int)m->qd_l; p.kvd = (int)m->kvd_l; p.max_seq = (int)caches[0]->max_seq;
+    p.wbf16 = m->cfg.weight_dtype == LUMEN_BF16;
+    p.embed = m->embed; p.final_norm = m->final_norm; p.lm_head = m->lm_head;
+    p.cos_t = m->cos_t; p.sin_t = m->sin_t;
+    p.eps = m->cfg.rms_norm_eps;
+    p.scale = 1.0f / sqrtf((float)m->D);
+    p.ids = w.ids; p.x = w.x; p.qkv = w.qkv; p.act = w.act; p.logits = w.logits;
+    // Attention work items = heads x splits, about one per SM, with at least 32 rows per split.
+    const size_t len = caches[0]->len + 1;
+    int nsplit = std::max(1, std::min(decode_mega_max_splits(), ctx->num_sms / std::max(1, p.Hq)));
+    nsplit = (int)std::max<size_t>(1, std::min<size_t>(nsplit, len / 32));
+    p.nsplit = nsplit;
+    const size_t rows = (size_t)p.Hq * nsplit;
+    p.part_m = w.part; p.part_l = w.part + rows; p.part_ctx = w.part + 2 * rows;
+    p.bar_counter = ctx->d_mega_sync;
+    p.bar_base = ctx->mega_bar_base;
+    p.abort_flag = reinterpret_cast<int *>(ctx->d_mega_sync + 1);
+    p.status = ctx->d_status;
+    p.trace = m->d_trace;
+    LUMEN_TRY(launch_decode_mega(ctx, p, ctx->stream));
+    ctx->mega_bar_base += (unsigned long long)decode_mega_barriers_per_launch(p.L) * (unsigned long long)ctx->num_sms;
+    return LUMEN_OK;
+}
+
+bool mega_usable(lumen_llama *m, size_t b, size_t s) {
+    if (!m->use_mega || b != 1 || s != 1 || m->ctx->tp_size != 1 || m->L == 0) return false;
+    MegaParams p{};
+    p.H = (int)m->H; p.I = (int)m->inter_l; p.qd = (int)m->qd_l; p.D = (int)m->D;
+    p.wbf16 = m->cfg.weight_dtype == LUMEN_BF16;
+    char why[128];
+    return decode_mega_supported(p, why, sizeof(why)) != 0;
+}
+
+// Runs one forward over ws.ids; batch-1 decode steps take the persistent kernel, other decode steps go
+// through a captured graph after the first call.
 int run_forward(lumen_llama *m, size_t b, size_t s, lumen_kv_cache **caches, bool last_only) {
     lumen_ctx *ctx = m->ctx;
+    if (mega_usable(m, b, s)) {
+        LUMEN_TRY(run_mega(m, caches));
+        for (size_t l = 0; l < m->L; ++l) caches[l]->len += 1;
+        return LUMEN_OK;
+    }
     StepPlan p{b, s, b * s, s == 1, 1};
     if (p.decode) p.nsplit = pick_decode_splits(m, b, caches[0]->len + 1);
     int rc = LUMEN_OK;
@@ -443,6 +508,14 @@ int lumen_llama_new(lumen_ctx *ctx, const lumen_llama_config *cfg, lumen_llama *
                       H * 4 + m->vocab_l * H * e;
     const char *ng = getenv("LUMEN_NO_GRAPH");
     m->use_graph = !(ng && ng[0] == '1');
+    const char *nm = getenv("LUMEN_NO_MEGA");
+    m->use_mega = !(nm && nm[0] == '1');
+    const char *tr = getenv("LUMEN_DECODE_TRACE");
+    if (tr && tr[0] == '1') {
+        const size_t n = 4 * (5 * m->L + 1) + 1;
+        if (cudaMalloc(&m->d_trace, n * sizeof(unsigned long long)) == cudaSuccess) cudaMemset(m->d_trace, 0, n * sizeof(unsigned long long));
+        else m->d_trace = nullptr;
+    }
     *out = m;
     return LUMEN_OK;
 }
@@ -588,10 +661,23 @@ int lumen_llama_forward_device(lumen_llama *m, const float *ids_dev, size_t b, s
 
 size_t lumen_llama_weight_bytes(const lumen_llama *m) { return m ? m->stream_bytes : 0; }
 
+int lumen_llama_decode_trace(lumen_llama *m, uint64_t *out, size_t capacity, size_t *n_out) {
+    if (!m || !out || !n_out) return LUMEN_ERR_INVALID;
+    lumen_ctx *ctx = m->ctx;
+    if (!m->d_trace) return set_error(ctx, LUMEN_ERR_UNSUPPORTED, "decode trace is off (set LUMEN_DECODE_TRACE=1 before creating the model)");
+    const size_t n = std::min<size_t>(capacity, 4 * (5 * m->L + 1) + 1);
+    LUMEN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    LUMEN_CUDA(ctx, cudaMemcpy(out, m->d_trace, n * sizeof(uint64_t), cudaMemcpyDeviceToHost));
+    *n_out = n;
+    return LUMEN_OK;
+}
+
 int lumen_llama_free(lumen_llama *m) {
     if (!m) return LUMEN_ERR_INVALID;
     cudaStreamSynchronize(m->ctx->stream);
     drop_graphs(m);
+    if (m->d_mega_layers) cudaFree(m->d_mega_layers);
+    if (m->d_trace) cudaFree(m->d_trace);
     if (m->ws.base) cudaFree(m->ws.base);
     if (m->ws.h_ids) cudaFreeHost(m->ws.h_ids);
     if (m->ws.h_logits) cudaFreeHost(m->ws.h_logits);

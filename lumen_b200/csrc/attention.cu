@@ -1,240 +1,38 @@
-// GQA attention over the static KV cache.
+// GQA attention over the static KV cache: stand-alone decode kernels (split over the context, then a
+// merge) and the prefill path.
 //
-// Decode (S == 1) restates src/layers/attention/self_attention.rs:141-297 of the reference: rotate the
-// new k into cache row `len`, copy v, rotate q, then softmax(q.K^T * scale).V over rows 0..=len with
-// the `1/(l + 1e-9)` normalisation.  The reference walks the rows serially per (b,h) with a
-// branching online softmax; here the rows are split over CTAs and warps (flash-decoding), each keeps
-// a running (max, sum, ctx) and the pieces are merged with the usual log-sum-exp rescale, so results
-// agree to rounding.  One CTA serves all query heads of its KV head, so K/V rows are read once per
-// KV head instead of once per query head.
+// Decode (S == 1): see attn_decode.cuh.  One CTA serves all query heads of its KV head (up to 8), so
+// K/V rows are read once per KV head instead of once per query head.
 //
-// Prefill (S > 1) restates :308-426, :519-535, :621-678: rotate q/k at positions past..past+S, slab
-// write, causal mask j > past+i, softmax with `1/(sum + 1e-9)`, P.V, output in [B,S,H,D] order.
-#include "common.cuh"
+// Prefill (S > 1) restates src/layers/attention/self_attention.rs:308-426, :519-535, :621-678 of the
+// reference: rotate q/k at positions past..past+S, slab write, causal mask j > past+i, softmax with
+// `1/(sum + 1e-9)`, P.V, output in [B,S,H,D] order.
+#include "attn_decode.cuh"
 
 namespace lumen {
 namespace {
 
-constexpr int kThreads = 256;
-constexpr int kWarps = kThreads / 32;
+constexpr int kThreads = kAttnThreads;
+constexpr int kWarps = kAttnWarps;
 
-__device__ __forceinline__ float warp_sum(float v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    return v;
-}
-
-// Normalise (optional) and rotate one head vector held in shared memory `buf[D]` in place.
-// Called by one warp.  RoPE as encoding.rs:195-203: dst[j] = x1*c - x2*s; dst[j+half] = x2*c + x1*s.
-__device__ void head_norm_rope(float *buf, int D, const float *norm_w, float eps, const float *cos_row,
-                               const float *sin_row, int lane) {
-    if (norm_w) {
-        float ss = 0.f;
-        for (int i = lane; i < D; i += 32) ss = fmaf(buf[i], buf[i], ss);
-        ss = warp_sum(ss);
-        float inv = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(ss, (float)D), eps)));
-        for (int i = lane; i < D; i += 32) buf[i] = __fmul_rn(__fmul_rn(buf[i], inv), norm_w[i]);
-        __syncwarp();
-    }
-    if (cos_row) {
-        const int half = D / 2;
-        for (int j = lane; j < half; j += 32) {
-            float x1 = buf[j], x2 = buf[j + half];
-            float c = cos_row[j], s = sin_row[j];
-            buf[j] = __fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, s));
-            buf[j + half] = __fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, s));
-        }
-        __syncwarp();
-    }
-}
-
-struct DecodeParams {
-    const float *q, *k_new, *v_new;
-    size_t q_stride, kv_stride;
-    float *k_cache, *v_cache;
-    const int *d_len;
-    int Hq, Hkv, D, max_seq;
-    const float *cos_t, *sin_t, *q_norm, *k_norm;
-    float norm_eps, scale;
-    float *part_m, *part_l, *part_ctx;  // [B,Hq,nsplit], [B,Hq,nsplit], [B,Hq,nsplit,D]
-    int nsplit;
+struct SyncThreads {
+    __device__ __forceinline__ void operator()() const { __syncthreads(); }
 };
 
-// grid (nsplit, Hkv * (G/GT), B).  GT query heads per CTA, NI = ceil(D/32) elements per lane.
+// grid (nsplit, Hkv * (G/GT), B)
 template <int GT, int NI>
 __global__ void __launch_bounds__(kThreads) attn_decode_kernel(DecodeParams p) {
     extern __shared__ __align__(16) float smem[];
-    const int D = p.D;
-    float *qs = smem;                       // [GT][D]
-    float *knew = qs + GT * D;              // [D]
-    float *wm = knew + D;                   // [kWarps][GT]
-    float *wl = wm + kWarps * GT;           // [kWarps][GT]
-    float *wctx = wl + kWarps * GT;         // [kWarps][GT][D]
-
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int G = p.Hq / p.Hkv;
-    const int groups_per_kv = G / GT;
-    const int hk = blockIdx.y / groups_per_kv;
-    const int h0 = hk * G + (blockIdx.y % groups_per_kv) * GT;
-    const int b = blockIdx.z;
-    const int split = blockIdx.x;
-
-    const int past = *p.d_len;
-    const int total = past + 1;
-    const int chunk = (total + p.nsplit - 1) / p.nsplit;
-    const int j0 = split * chunk;
-    const int j1 = min(total, j0 + chunk);
-    const int half = D / 2;
-    const float *cos_row = p.cos_t ? p.cos_t + (size_t)past * half : nullptr;
-    const float *sin_row = p.sin_t ? p.sin_t + (size_t)past * half : nullptr;
-
-    // Stage and rotate the GT query heads (one warp per head, round robin).
-    for (int g = warp; g < GT; g += kWarps) {
-        const float *src = p.q + (size_t)b * p.q_stride + (size_t)(h0 + g) * D;
-        for (int i = lane; i < D; i += 32) qs[g * D + i] = src[i];
-        __syncwarp();
-        head_norm_rope(qs + g * D, D, p.q_norm, p.norm_eps, cos_row, sin_row, lane);
-    }
-    // The CTA whose range holds row `past` appends the new k (rotated) and v to the cache.
-    // Only the first head group of a KV head writes; the others read what it wrote?  No: they would
-    // race.  Every group whose range holds `past` keeps the new row in shared memory and uses that
-    // copy, so nobody reads the freshly written global row inside this kernel.
-    const bool owns_new = (past >= j0 && past < j1);
-    float *k_row_cache = p.k_cache + (((size_t)b * p.Hkv + hk) * p.max_seq + past) * D;
-    float *v_row_cache = p.v_cache + (((size_t)b * p.Hkv + hk) * p.max_seq + past) * D;
-    if (owns_new && warp == kWarps - 1) {
-        const float *ksrc = p.k_new + (size_t)b * p.kv_stride + (size_t)hk * D;
-        for (int i = lane; i < D; i += 32) knew[i] = ksrc[i];
-        __syncwarp();
-        head_norm_rope(knew, D, p.k_norm, p.norm_eps, cos_row, sin_row, lane);
-        if (blockIdx.y % groups_per_kv == 0) {
-            const float *vsrc = p.v_new + (size_t)b * p.kv_stride + (size_t)hk * D;
-            for (int i = lane; i < D; i += 32) {
-                k_row_cache[i] = knew[i];
-                v_row_cache[i] = vsrc[i];
-            }
-        }
-    }
-    __syncthreads();
-
-    float q[GT][NI], ctx[GT][NI], m[GT], l[GT];
-#pragma unroll
-    for (int g = 0; g < GT; ++g) {
-        m[g] = -INFINITY;
-        l[g] = 0.f;
-#pragma unroll
-        for (int i = 0; i < NI; ++i) {
-            int e = lane + 32 * i;
-            q[g][i] = (e < D) ? qs[g * D + e] : 0.f;
-            ctx[g][i] = 0.f;
-        }
-    }
-
-    const float *kbase = p.k_cache + ((size_t)b * p.Hkv + hk) * p.max_seq * D;
-    const float *vbase = p.v_cache + ((size_t)b * p.Hkv + hk) * p.max_seq * D;
-    const float *vnew_src = p.v_new + (size_t)b * p.kv_stride + (size_t)hk * D;
-    constexpr int UN = 4;
-    for (int jb = j0 + warp * UN; jb < j1; jb += kWarps * UN) {
-        float kr[UN][NI], vr[UN][NI];
-#pragma unroll
-        for (int u = 0; u < UN; ++u) {
-            const int j = jb + u;
-#pragma unroll
-            for (int i = 0; i < NI; ++i) {
-                const int e = lane + 32 * i;
-                float kv = 0.f, vv = 0.f;
-                if (j < j1 && e < D) {
-                    if (j == past) {  // the row appended by this step: use the staged copy
-                        kv = knew[e];
-                        vv = vnew_src[e];
-                    } else {
-                        kv = __ldcg(kbase + (size_t)j * D + e);
-                        vv = __ldcg(vbase + (size_t)j * D + e);
-                    }
-                }
-                kr[u][i] = kv;
-                vr[u][i] = vv;
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < UN; ++u) {
-            if (jb + u >= j1) break;
-#pragma unroll
-            for (int g = 0; g < GT; ++g) {
-                float dot = 0.f;
-#pragma unroll
-                for (int i = 0; i < NI; ++i) dot = fmaf(q[g][i], kr[u][i], dot);
-                dot = warp_sum(dot);
-                const float sc = __fmul_rn(dot, p.scale);
-                const float mn = fmaxf(m[g], sc);
-                const float r = expf(m[g] - mn);  // exp(-inf) = 0 on the first row
-                const float w = expf(sc - mn);
-                l[g] = fmaf(l[g], r, w);
-#pragma unroll
-                for (int i = 0; i < NI; ++i) ctx[g][i] = fmaf(w, vr[u][i], ctx[g][i] * r);
-                m[g] = mn;
-            }
-        }
-    }
-
-    // Merge the warps of this CTA.
-#pragma unroll
-    for (int g = 0; g < GT; ++g) {
-        if (lane == 0) {
-            wm[warp * GT + g] = m[g];
-            wl[warp * GT + g] = l[g];
-        }
-#pragma unroll
-        for (int i = 0; i < NI; ++i) {
-            int e = lane + 32 * i;
-            if (e < D) wctx[(warp * GT + g) * D + e] = ctx[g][i];
-        }
-    }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < GT * D; idx += kThreads) {
-        const int g = idx / D, e = idx % D;
-        float M = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < kWarps; ++w) M = fmaxf(M, wm[w * GT + g]);
-        float L = 0.f, c = 0.f;
-#pragma unroll
-        for (int w = 0; w < kWarps; ++w) {
-            const float mw = wm[w * GT + g];
-            const float f = (mw == -INFINITY) ? 0.f : expf(mw - M);
-            L = fmaf(wl[w * GT + g], f, L);
-            c = fmaf(wctx[(w * GT + g) * D + e], f, c);
-        }
-        const size_t o = ((size_t)b * p.Hq + h0 + g) * p.nsplit + split;
-        p.part_ctx[o * D + e] = c;
-        if (e == 0) {
-            p.part_m[o] = M;
-            p.part_l[o] = L;
-        }
-    }
+    attn_decode_item<GT, NI>(p, smem, blockIdx.z, blockIdx.y, blockIdx.x, threadIdx.x, *p.d_len, SyncThreads());
 }
 
-// Merge the splits: out = ctx * (1/(l + 1e-9))  (self_attention.rs:287-290).  grid (B*Hq).
-// Thread 0 of block 0 advances the cache length afterwards (c.len = new_len, :179).
-__global__ void attn_decode_combine_kernel(const float *__restrict__ part_m, const float *__restrict__ part_l,
-                                           const float *__restrict__ part_ctx, float *__restrict__ out, int D,
-                                           int nsplit, int *d_len_bump) {
+// Merge the splits; grid (B*Hq).  Thread 0 of block 0 advances the cache length afterwards
+// (c.len = new_len, self_attention.rs:179).
+__global__ void attn_decode_combine_kernel(const float *part_m, const float *part_l, const float *part_ctx,
+                                           float *__restrict__ out, int D, int nsplit, int *d_len_bump) {
     const size_t row = blockIdx.x;
-    float M = -INFINITY;
-    for (int s = 0; s < nsplit; ++s) M = fmaxf(M, part_m[row * nsplit + s]);
-    float L = 0.f;
-    for (int s = 0; s < nsplit; ++s) {
-        const float ms = part_m[row * nsplit + s];
-        if (ms != -INFINITY) L = fmaf(part_l[row * nsplit + s], expf(ms - M), L);
-    }
-    const float inv = __fdiv_rn(1.0f, __fadd_rn(L, 1e-9f));
-    for (int e = threadIdx.x; e < D; e += blockDim.x) {
-        float c = 0.f;
-        for (int s = 0; s < nsplit; ++s) {
-            const float ms = part_m[row * nsplit + s];
-            if (ms != -INFINITY) c = fmaf(part_ctx[(row * nsplit + s) * D + e], expf(ms - M), c);
-        }
-        out[row * D + e] = __fmul_rn(c, inv);
-    }
+    for (int e = threadIdx.x; e < D; e += blockDim.x)
+        out[row * D + e] = attn_combine_elem(part_m, part_l, part_ctx, row, e, D, nsplit);
     if (d_len_bump && blockIdx.x == 0 && threadIdx.x == 0) *d_len_bump += 1;
 }
 
@@ -324,7 +122,7 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_kernel(PrefillParams p)
             float dot = 0.f;
 #pragma unroll
             for (int i = 0; i < NI; ++i) dot = fmaf(q[i], kr[u][i], dot);
-            dot = warp_sum(dot);
+            dot = attn_warp_sum(dot);
             const float sc = __fmul_rn(dot, p.scale);
             const float mn = fmaxf(m, sc);
             const float r = expf(m - mn);
@@ -399,7 +197,7 @@ int launch_attn_decode(lumen_ctx *ctx, const AttnDecodeArgs &a, cudaStream_t s) 
     p.part_l = a.part + rows;
     p.part_ctx = a.part + 2 * rows;
     dim3 grid(nsplit, (unsigned)(a.Hkv * (G / GT)), (unsigned)a.B);
-    size_t smem = ((size_t)GT * a.D + a.D + 2 * kWarps * GT + (size_t)kWarps * GT * a.D) * sizeof(float);
+    size_t smem = attn_decode_smem_floats(GT, (int)a.D) * sizeof(float);
     int rc;
     switch (GT) {
         case 8: rc = launch_decode_gt<8>(ctx, p, ni, grid, smem, s); break;

@@ -1,0 +1,284 @@
+// Device code of the decode (S == 1) attention step, shared by the stand-alone kernel and the
+// whole-step persistent kernel.
+//
+// Restates src/layers/attention/self_attention.rs:141-297 of the reference: rotate the new k into cache
+// row `len`, copy v, rotate q, then softmax(q.K^T * scale).V over rows 0..=len with the
+// `1/(l + 1e-9)` normalisation.  The reference walks the rows serially per (b,h) with a branching online
+// softmax; here the rows are split over CTAs and warps, each keeps a running (max, sum, ctx) and the
+// pieces are merged with the log-sum-exp rescale, so results agree to rounding.
+#pragma once
+
+#include "common.cuh"
+
+namespace lumen {
+
+constexpr int kAttnThreads = 256;
+constexpr int kAttnWarps = kAttnThreads / 32;
+
+__device__ __forceinline__ float attn_warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// Normalise (optional) and rotate one head vector held in shared memory `buf[D]` in place; called by
+// one warp.  RoPE as encoding.rs:195-203: dst[j] = x1*c - x2*s; dst[j+half] = x2*c + x1*s.
+__device__ __forceinline__ void head_norm_rope(float *buf, int D, const float *norm_w, float eps,
+                                               const float *cos_row, const float *sin_row, int lane) {
+    if (norm_w) {
+        float ss = 0.f;
+        for (int i = lane; i < D; i += 32) ss = fmaf(buf[i], buf[i], ss);
+        ss = attn_warp_sum(ss);
+        float inv = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(ss, (float)D), eps)));
+        for (int i = lane; i < D; i += 32) buf[i] = __fmul_rn(__fmul_rn(buf[i], inv), norm_w[i]);
+        __syncwarp();
+    }
+    if (cos_row) {
+        const int half = D / 2;
+        for (int j = lane; j < half; j += 32) {
+            float x1 = buf[j], x2 = buf[j + half];
+            float c = cos_row[j], s = sin_row[j];
+            buf[j] = __fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, s));
+            buf[j + half] = __fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, s));
+        }
+        __syncwarp();
+    }
+}
+
+// Loads one head vector (D <= 256) together with its cos/sin row in one batch of independent loads,
+// then normalises (optional) and rotates it into shared memory `buf[D]`.  Same arithmetic as
+// head_norm_rope; the loads are issued before anything depends on them so the whole step costs one
+// memory round trip.  Called by one warp.
+__device__ __forceinline__ void load_norm_rope(float *buf, const float *src, int D, const float *norm_w, float eps,
+                                               const float *cos_row, const float *sin_row, int lane) {
+    const int half = D / 2;
+    float v[8], nw[8], c[4], s[4];
+#pragma unroll
+    for (int t = 0; t < 8; ++t) {
+        const int i = lane + 32 * t;
+        v[t] = (i < D) ? __ldcg(src + i) : 0.f;
+        nw[t] = (norm_w && i < D) ? __ldg(norm_w + i) : 1.f;
+    }
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+        const int j = lane + 32 * t;
+        c[t] = (cos_row && j < half) ? __ldg(cos_row + j) : 1.f;
+        s[t] = (sin_row && j < half) ? __ldg(sin_row + j) : 0.f;
+    }
+    if (norm_w) {
+        float ss = 0.f;
+#pragma unroll
+        for (int t = 0; t < 8; ++t) ss = fmaf(v[t], v[t], ss);
+        ss = attn_warp_sum(ss);
+        const float inv = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(ss, (float)D), eps)));
+#pragma unroll
+        for (int t = 0; t < 8; ++t) v[t] = __fmul_rn(__fmul_rn(v[t], inv), nw[t]);
+    }
+#pragma unroll
+    for (int t = 0; t < 8; ++t) {
+        const int i = lane + 32 * t;
+        if (i < D) buf[i] = v[t];
+    }
+    __syncwarp();
+    if (cos_row) {
+        float lo[4], hi[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            const int j = lane + 32 * t;
+            lo[t] = (j < half) ? buf[j] : 0.f;
+            hi[t] = (j < half) ? buf[j + half] : 0.f;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            const int j = lane + 32 * t;
+            if (j < half) {
+                buf[j] = __fsub_rn(__fmul_rn(lo[t], c[t]), __fmul_rn(hi[t], s[t]));
+                buf[j + half] = __fadd_rn(__fmul_rn(hi[t], c[t]), __fmul_rn(lo[t], s[t]));
+            }
+        }
+        __syncwarp();
+    }
+}
+
+struct DecodeParams {
+    const float *q, *k_new, *v_new;
+    size_t q_stride, kv_stride;
+    float *k_cache, *v_cache;
+    const int *d_len;
+    int Hq, Hkv, D, max_seq;
+    const float *cos_t, *sin_t, *q_norm, *k_norm;
+    float norm_eps, scale;
+    float *part_m, *part_l, *part_ctx;  // [B,Hq,nsplit], [B,Hq,nsplit], [B,Hq,nsplit,D]
+    int nsplit;
+};
+
+__host__ __device__ inline size_t attn_decode_smem_floats(int GT, int D) {
+    return (size_t)GT * D + D + 2 * kAttnWarps * GT + (size_t)kAttnWarps * GT * D;
+}
+
+// One work item: batch row b, KV head group `ygroup` (= hk * (G/GT) + group), context split `split`.
+// Executed by kAttnThreads threads (tid = 0..255) that share `smem` and the barrier `bar()`.
+// GT query heads per item, NI = ceil(D/32) elements per lane.
+template <int GT, int NI, typename Bar>
+__device__ __forceinline__ void attn_decode_item(const DecodeParams &p, float *smem, int b, int ygroup, int split, int tid, int past,
+                                 Bar bar) {
+    const int D = p.D;
+    float *qs = smem;                        // [GT][D]
+    float *knew = qs + GT * D;               // [D]
+    float *wm = knew + D;                    // [warps][GT]
+    float *wl = wm + kAttnWarps * GT;        // [warps][GT]
+    float *wctx = wl + kAttnWarps * GT;      // [warps][GT][D]
+
+    const int lane = tid & 31, warp = tid >> 5;
+    const int G = p.Hq / p.Hkv;
+    const int groups_per_kv = G / GT;
+    const int hk = ygroup / groups_per_kv;
+    const int h0 = hk * G + (ygroup % groups_per_kv) * GT;
+
+    const int total = past + 1;
+    const int chunk = (total + p.nsplit - 1) / p.nsplit;
+    const int j0 = split * chunk;
+    const int j1 = min(total, j0 + chunk);
+    const int half = D / 2;
+    const float *cos_row = p.cos_t ? p.cos_t + (size_t)past * half : nullptr;
+    const float *sin_row = p.sin_t ? p.sin_t + (size_t)past * half : nullptr;
+
+    // Stage and rotate the GT query heads (one warp per head, round robin).
+    for (int g = warp; g < GT; g += kAttnWarps) {
+        const float *src = p.q + (size_t)b * p.q_stride + (size_t)(h0 + g) * D;
+        load_norm_rope(qs + g * D, src, D, p.q_norm, p.norm_eps, cos_row, sin_row, lane);
+    }
+    // Every item whose range holds row `past` rotates the new k into shared memory and uses that copy
+    // (and v_new straight from the projection buffer), so no item reads the cache row written during
+    // this step; the first head group of each KV head also stores the row into the cache.
+    const bool owns_new = (past >= j0 && past < j1);
+    const float *vnew_src = p.v_new + (size_t)b * p.kv_stride + (size_t)hk * D;
+    if (owns_new && warp == kAttnWarps - 1) {
+        const float *ksrc = p.k_new + (size_t)b * p.kv_stride + (size_t)hk * D;
+        load_norm_rope(knew, ksrc, D, p.k_norm, p.norm_eps, cos_row, sin_row, lane);
+        if (ygroup % groups_per_kv == 0) {
+            float *k_row = p.k_cache + (((size_t)b * p.Hkv + hk) * p.max_seq + past) * D;
+            float *v_row = p.v_cache + (((size_t)b * p.Hkv + hk) * p.max_seq + past) * D;
+            for (int i = lane; i < D; i += 32) {
+                k_row[i] = knew[i];
+                v_row[i] = __ldcg(vnew_src + i);
+            }
+        }
+    }
+    bar();
+
+    float q[GT][NI], ctx[GT][NI], m[GT], l[GT];
+#pragma unroll
+    for (int g = 0; g < GT; ++g) {
+        m[g] = -INFINITY;
+        l[g] = 0.f;
+#pragma unroll
+        for (int i = 0; i < NI; ++i) {
+            int e = lane + 32 * i;
+            q[g][i] = (e < D) ? qs[g * D + e] : 0.f;
+            ctx[g][i] = 0.f;
+        }
+    }
+
+    const float *kbase = p.k_cache + ((size_t)b * p.Hkv + hk) * p.max_seq * D;
+    const float *vbase = p.v_cache + ((size_t)b * p.Hkv + hk) * p.max_seq * D;
+    constexpr int UN = NI <= 2 ? 8 : (NI == 4 ? 4 : 2);  // rows whose K and V loads are in flight together
+    for (int jb = j0 + warp * UN; jb < j1; jb += kAttnWarps * UN) {
+        float kr[UN][NI], vr[UN][NI];
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+            const int j = jb + u;
+#pragma unroll
+            for (int i = 0; i < NI; ++i) {
+                const int e = lane + 32 * i;
+                float kv = 0.f, vv = 0.f;
+                if (j < j1 && e < D) {
+                    if (j == past) {  // the row appended by this step: use the staged copy
+                        kv = knew[e];
+                        vv = __ldcg(vnew_src + e);
+                    } else {
+                        kv = __ldcg(kbase + (size_t)j * D + e);
+                        vv = __ldcg(vbase + (size_t)j * D + e);
+                    }
+                }
+                kr[u][i] = kv;
+                vr[u][i] = vv;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+            if (jb + u >= j1) break;
+#pragma unroll
+            for (int g = 0; g < GT; ++g) {
+                float dot = 0.f;
+#pragma unroll
+                for (int i = 0; i < NI; ++i) dot = fmaf(q[g][i], kr[u][i], dot);
+                dot = attn_warp_sum(dot);
+                const float sc = __fmul_rn(dot, p.scale);
+                const float mn = fmaxf(m[g], sc);
+                const float r = expf(m[g] - mn);  // exp(-inf) = 0 on the first row
+                const float w = expf(sc - mn);
+                l[g] = fmaf(l[g], r, w);
+#pragma unroll
+                for (int i = 0; i < NI; ++i) ctx[g][i] = fmaf(w, vr[u][i], ctx[g][i] * r);
+                m[g] = mn;
+            }
+        }
+    }
+
+    // Merge the warps of this item.
+#pragma unroll
+    for (int g = 0; g < GT; ++g) {
+        if (lane == 0) {
+            wm[warp * GT + g] = m[g];
+            wl[warp * GT + g] = l[g];
+        }
+#pragma unroll
+        for (int i = 0; i < NI; ++i) {
+            int e = lane + 32 * i;
+            if (e < D) wctx[(warp * GT + g) * D + e] = ctx[g][i];
+        }
+    }
+    bar();
+    for (int idx = tid; idx < GT * D; idx += kAttnThreads) {
+        const int g = idx / D, e = idx % D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; ++w) M = fmaxf(M, wm[w * GT + g]);
+        float L = 0.f, c = 0.f;
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; ++w) {
+            const float mw = wm[w * GT + g];
+            const float f = (mw == -INFINITY) ? 0.f : expf(mw - M);
+            L = fmaf(wl[w * GT + g], f, L);
+            c = fmaf(wctx[(w * GT + g) * D + e], f, c);
+        }
+        const size_t o = ((size_t)b * p.Hq + h0 + g) * p.nsplit + split;
+        p.part_ctx[o * D + e] = c;
+        if (e == 0) {
+            p.part_m[o] = M;
+            p.part_l[o] = L;
+        }
+    }
+    bar();  // shared memory may be reused by the caller's next item
+}
+
+// Merges the splits of one (b, head) row: element e of out = ctx * (1/(l + 1e-9)) (self_attention.rs:287-290).
+__device__ __forceinline__ float attn_combine_elem(const float *part_m, const float *part_l, const float *part_ctx,
+                                                   size_t row, int e, int D, int nsplit) {
+    float M = -INFINITY;
+    for (int s = 0; s < nsplit; ++s) M = fmaxf(M, __ldcg(part_m + row * nsplit + s));
+    float L = 0.f, c = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+        const float ms = __ldcg(part_m + row * nsplit + s);
+        if (ms != -INFINITY) {
+            const float f = expf(ms - M);
+            L = fmaf(__ldcg(part_l + row * nsplit + s), f, L);
+            c = fmaf(__ldcg(part_ctx + (row * nsplit + s) * D + e), f, c);
+        }
+    }
+    return __fmul_rn(c, __fdiv_rn(1.0f, __fadd_rn(L, 1e-9f)));
+}
+
+}  // namespace lumen

@@ -39,6 +39,9 @@ struct lumen_ctx {
     lumen::DeviceStatus *h_status = nullptr;  // pinned mirror
     char err[512] = {0};
     unsigned long long launches = 0;  // kernels enqueued so far (graph replays add their node count)
+    // Grid-barrier state of the persistent decode kernel: [0] = arrival counter (u64), then an abort flag.
+    unsigned long long *d_mega_sync = nullptr;
+    unsigned long long mega_bar_base = 0;  // value of the counter when the next launch starts
 };
 
 struct lumen_storage {

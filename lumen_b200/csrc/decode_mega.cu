@@ -1,0 +1,757 @@
+// Whole-token persistent decode kernel (batch 1): one launch runs LlamaModel::forward for one new
+// token (src/models/llama.rs:181-206 of the reference; layer body :104-116, MLP :59-65, decode
+// attention self_attention.rs:141-297, vector-matrix products src/ops/matmul.rs:42-69).
+//
+// Design for B200: one CTA per SM, launched cooperatively.  Warp 8 of each CTA is a producer: one
+// elected lane walks a static schedule of weight tiles (the CTA's rows of every matrix of every layer,
+// in execution order) and streams them from HBM into a shared-memory ring with 1-D bulk TMA copies
+// (cp.async.bulk + mbarrier transaction counts, L2 evict-first).  The schedule does not depend on the
+// activations, so the producer keeps HBM busy across phase boundaries while the 8 consumer warps wait
+// at grid barriers or run the (weight-free) attention phase.
+//
+// Consumers: the 8 warps form G independent groups (G = 4, 2 or 1, chosen per matrix from its row
+// length); group g owns every G-th tile, so several tiles are processed at once and no CTA-wide barrier
+// sits between tiles.  Within a group every thread keeps its slice of the input vector in registers,
+// reads its 128-bit words of each weight row from shared memory, and the warp's partial sum per row goes
+// to a small shared table; once per phase the table is reduced and the fused epilogue runs (RMSNorm in
+// the prologue, residual add, SiLU*mul).  Phases of a layer: qkv | attention | o_proj(+residual) |
+// gate/up(+SiLU*mul) | down(+residual); activations cross CTAs through global memory (L2) behind a
+// grid barrier.  Everything between two barriers is arranged as ONE batch of independent loads, since an
+// L2 round trip (~1 us under load) is the unit of cost on the critical path.
+//
+// Every wait (mbarrier, grid barrier) is bounded: on expiry the CTA records LUMEN_ERR_TIMEOUT in the
+// device status word, raises an abort flag that the other CTAs poll, waits (bounded) for its own bulk
+// copies still in flight and returns; the kernel never traps or spins forever.
+#include <algorithm>
+#include <cstdlib>
+
+#include "attn_decode.cuh"
+#include "decode_mega.cuh"
+
+namespace lumen {
+namespace {
+
+constexpr int kConsumers = 256;
+constexpr int kConsumerWarps = kConsumers / 32;
+constexpr int kThreads = kConsumers + 32;  // + producer warp
+constexpr int kMaxRowsPerTile = 8;
+constexpr int kRowBlock = 256;             // rows reduced together (one per consumer thread)
+constexpr int kMaxSplit = 4;               // attention splits merged in the o_proj prologue
+constexpr long long kWaitCycles = 400000000LL;  // ~0.2 s at 1.9 GHz
+
+// ---- PTX helpers -------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cnt(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ uint64_t make_evict_first_policy() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+// 1-D bulk copy global -> this CTA's shared memory, completion counted in bytes on `bar`.
+__device__ __forceinline__ void bulk_load(void *dst_smem, const void *src, uint32_t bytes, uint64_t *bar, uint64_t pol) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+        ::"r"(smem_u32(dst_smem)), "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(pol)
+        : "memory");
+}
+__device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory"); }
+struct ConsumerBar {
+    __device__ __forceinline__ void operator()() const { consumer_bar(); }
+};
+// A consumer barrier after which all 256 threads agree on whether the CTA is aborting.  Exits must be
+// uniform (a thread that left would make the next bar.sync wait forever), so the flag is sampled by
+// thread 0 before the barrier into a slot that alternates with `k`, and read by everyone after it.
+__device__ __forceinline__ bool consumer_bar_ok(volatile int *abort, volatile int *decision, int tid, int &k) {
+    if (tid == 0) decision[k & 1] = *abort;
+    consumer_bar();
+    const bool ok = decision[k & 1] == 0;
+    ++k;
+    return ok;
+}
+__device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long long *p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void red_release_add_u64(unsigned long long *p, unsigned long long v) {
+    asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void trace_stamp(const MegaParams &p, int cta, int tid, int slot) {
+    if (p.trace && cta == 0 && tid == 0) p.trace[slot] = globaltimer_ns();
+}
+__device__ __forceinline__ int ld_volatile_int(const int *p) { return *reinterpret_cast<const volatile int *>(p); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float bf16_lo(uint32_t u) { return __uint_as_float(u << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t u) { return __uint_as_float(u & 0xffff0000u); }
+
+// ---- shared state ------------------------------------------------------------------------------------
+struct Shared {
+    unsigned char *stages;
+    float *part;       // [2][kRowBlock][kConsumerWarps] per-warp partial sums of the rows of one block
+    float *red;        // [kConsumerWarps]
+    float *attn;       // scratch of the attention item
+    uint64_t *full;    // [S]
+    uint64_t *empty;   // [S]
+    volatile int *abort;
+    volatile int *decision;  // [2] abort flag sampled by thread 0 before a barrier, read by all after it
+    volatile int *seen;      // [S] number of uses of each stage whose data a consumer has seen land
+    int S, stage_bytes;
+};
+
+__device__ __forceinline__ void raise_abort(const MegaParams &p, Shared &sh, int site, int value) {
+    *sh.abort = 1;
+    atomicExch(p.abort_flag, 1);
+    if (atomicCAS(&p.status->code, 0, LUMEN_ERR_TIMEOUT) == 0) {
+        p.status->detail0 = site;
+        p.status->detail1 = value;
+    }
+}
+
+// Bounded mbarrier wait; false = gave up (abort raised) or somebody else aborted.
+__device__ __forceinline__ bool mbar_wait(const MegaParams &p, Shared &sh, uint64_t *bar, uint32_t parity, int site) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    int spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++spins & 63) == 0) {
+            if (*sh.abort) return false;
+            if (clock64() - t0 > kWaitCycles) {
+                raise_abort(p, sh, site, (int)parity);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+// Bounded wait until `uses` fills of stage s are known to have landed (written by the groups that
+// consumed them).  In steady state this is already true and costs one shared-memory read.
+__device__ __forceinline__ bool stage_use_seen(const MegaParams &p, Shared &sh, int s, int uses, int site) {
+    if (sh.seen[s] >= uses) return true;
+    const long long t0 = clock64();
+    int spins = 0;
+    while (sh.seen[s] < uses) {
+        if ((++spins & 63) == 0) {
+            if (*sh.abort) return false;
+            if (clock64() - t0 > kWaitCycles) {
+                raise_abort(p, sh, site, uses);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+// ---- phases and tiles --------------------------------------------------------------------------------
+enum PhaseKind { PH_QKV = 0, PH_ATT = 1, PH_O = 2, PH_GATEUP = 3, PH_DOWN = 4, PH_LMHEAD = 5 };
+
+struct Phase {
+    int kind, layer, nmat, N, K;
+    const char *w0, *w1;
+};
+
+__device__ __forceinline__ Phase get_phase(const MegaParams &p, int ph) {
+    Phase g;
+    g.nmat = 1;
+    g.w1 = nullptr;
+    if (ph >= 5 * p.L) {
+        g.kind = PH_LMHEAD; g.layer = p.L; g.N = p.V; g.K = p.H; g.w0 = p.lm_head;
+        return g;
+    }
+    g.layer = ph / 5;
+    g.kind = ph % 5;
+    const MegaLayer &l = p.layers[g.layer];
+    switch (g.kind) {
+        case PH_QKV: g.N = p.qkv_rows; g.K = p.H; g.w0 = l.wqkv; break;
+        case PH_O: g.N = p.H; g.K = p.qd; g.w0 = l.wo; break;
+        case PH_GATEUP: g.N = p.I; g.K = p.H; g.w0 = l.wgate; g.w1 = l.wup; g.nmat = 2; break;
+        case PH_DOWN: g.N = p.H; g.K = p.I; g.w0 = l.wdown; break;
+        default: g.N = 0; g.K = 0; g.w0 = nullptr; break;  // PH_ATT streams no weights
+    }
+    return g;
+}
+
+// The CTA's tiles of one phase, in the order both the producer and the consumers walk them: chunks of up
+// to R whole rows; per chunk one tile per matrix (gate rows, then the same rows of up).
+struct TileIter {
+    long r, r0, r1;
+    int nmat, R, rowbytes, mat;
+    __device__ TileIter(const Phase &g, int esz, int stage_bytes, int cta, int nctas) {
+        rowbytes = g.K * esz;
+        nmat = g.nmat;
+        r0 = r = (long)g.N * cta / nctas;
+        r1 = (long)g.N * (cta + 1) / nctas;
+        R = max(1, min(kMaxRowsPerTile, stage_bytes / max(rowbytes, 1)));
+        mat = 0;
+    }
+    __device__ bool valid() const { return r < r1; }
+    __device__ int rows() const { return (int)min((long)R, r1 - r); }
+    __device__ void advance() {
+        if (++mat == nmat) {
+            mat = 0;
+            r += R;
+        }
+    }
+};
+
+// ---- producer ----------------------------------------------------------------------------------------
+__device__ __forceinline__ void producer_loop(const MegaParams &p, Shared &sh, int cta, int nctas) {
+    const uint64_t pol = make_evict_first_policy();
+    const int esz = p.wbf16 ? 2 : 4;
+    const int nphases = 5 * p.L + 1;
+    int s = 0;          // stage of the next tile
+    uint32_t use = 0;   // how many times the ring has wrapped
+    long issued = 0;
+    bool ok = true;
+    for (int ph = 0; ph < nphases && ok; ++ph) {
+        const Phase g = get_phase(p, ph);
+        if (g.kind == PH_ATT) continue;
+        bool first = true;
+        for (TileIter ti(g, esz, sh.stage_bytes, cta, nctas); ti.valid(); ti.advance()) {
+            if (first && p.trace && cta == 0) p.trace[3 * nphases + 1 + ph] = globaltimer_ns();
+            first = false;
+            if (use > 0 && !mbar_wait(p, sh, &sh.empty[s], (use - 1) & 1, 100 + g.kind)) {
+                ok = false;
+                break;
+            }
+            const uint32_t bytes = (uint32_t)ti.rows() * (uint32_t)ti.rowbytes;
+            const char *src = (ti.mat == 0 ? g.w0 : g.w1) + (size_t)ti.r * ti.rowbytes;
+            mbar_expect_tx(&sh.full[s], bytes);
+            bulk_load(sh.stages + (size_t)s * sh.stage_bytes, src, bytes, &sh.full[s], pol);
+            ++issued;
+            if (++s == sh.S) {
+                s = 0;
+                ++use;
+            }
+        }
+    }
+    if (!ok) {
+        // Wait (bounded) for the copies still in flight before the CTA may exit: the last min(issued, S) tiles.
+        const long n = issued < sh.S ? issued : sh.S;
+        for (long i = 0; i < n; ++i) {
+            const long idx = issued - 1 - i;
+            uint64_t *bar = &sh.full[idx % sh.S];
+            const uint32_t parity = (uint32_t)((idx / sh.S) & 1);
+            const long long t0 = clock64();
+            while (!mbar_try_wait(bar, parity) && clock64() - t0 < kWaitCycles) {}
+        }
+    }
+}
+
+// ---- consumers ---------------------------------------------------------------------------------------
+// Grid barrier number `index` (0-based within this launch).  All consumer threads call it.  The stores
+// the CTA made before the call are ordered before thread 0's release by the CTA barrier (cumulativity).
+__device__ __forceinline__ bool grid_sync(const MegaParams &p, Shared &sh, int index, int nctas, int tid, int &bk) {
+    consumer_bar();
+    if (tid == 0 && !*sh.abort) {
+        red_release_add_u64(p.bar_counter, 1ull);
+        const unsigned long long target = p.bar_base + (unsigned long long)(index + 1) * (unsigned long long)nctas;
+        const long long t0 = clock64();
+        int spins = 0;
+        while (ld_acquire_u64(p.bar_counter) < target) {
+            if ((++spins & 15) == 0) {
+                if (ld_volatile_int(p.abort_flag)) {
+                    *sh.abort = 1;
+                    break;
+                }
+                if (clock64() - t0 > kWaitCycles) {
+                    raise_abort(p, sh, 200, index);
+                    break;
+                }
+            }
+        }
+    }
+    return consumer_bar_ok(sh.abort, sh.decision, tid, bk);
+}
+
+template <typename WT>
+struct VecTraits;
+template <>
+struct VecTraits<float> {
+    static constexpr int XPV = 4;  // x elements per 16-byte weight vector
+    __device__ static __forceinline__ float dot(const uint4 &w, const float *x, float a) {
+        a = fmaf(__uint_as_float(w.x), x[0], a);
+        a = fmaf(__uint_as_float(w.y), x[1], a);
+        a = fmaf(__uint_as_float(w.z), x[2], a);
+        a = fmaf(__uint_as_float(w.w), x[3], a);
+        return a;
+    }
+};
+template <>
+struct VecTraits<__nv_bfloat16> {
+    static constexpr int XPV = 8;
+    __device__ static __forceinline__ float dot(const uint4 &w, const float *x, float a) {
+        a = fmaf(bf16_lo(w.x), x[0], a);
+        a = fmaf(bf16_hi(w.x), x[1], a);
+        a = fmaf(bf16_lo(w.y), x[2], a);
+        a = fmaf(bf16_hi(w.y), x[3], a);
+        a = fmaf(bf16_lo(w.z), x[4], a);
+        a = fmaf(bf16_hi(w.z), x[5], a);
+        a = fmaf(bf16_lo(w.w), x[6], a);
+        a = fmaf(bf16_hi(w.w), x[7], a);
+        return a;
+    }
+};
+
+__device__ __forceinline__ float embed_elem(const MegaParams &p, long id, int k) {
+    if (p.wbf16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(p.embed)[id * p.H + k]);
+    return __ldg(reinterpret_cast<const float *>(p.embed) + id * p.H + k);
+}
+
+// Stage / parity bookkeeping of the consumer side of the ring.
+struct RingPos {
+    int s;
+    uint32_t use;
+    __device__ void next(int S) {
+        if (++s == S) {
+            s = 0;
+            ++use;
+        }
+    }
+};
+
+// One vector-matrix phase for the consumer threads.
+//   NXV = 16-byte weight vectors per thread per row, G = warp groups (each owns every G-th tile).
+template <typename WT, int NXV, int G>
+__device__ __forceinline__ bool gemv_phase(const MegaParams &p, Shared &sh, const Phase &g, long id, RingPos &rp, int cta, int nctas, int tid,
+                           int &bk, int ph) {
+    constexpr int XPV = VecTraits<WT>::XPV;
+    constexpr int T = kConsumers / G;       // threads per group
+    constexpr int WG = kConsumerWarps / G;  // warps per group
+    const int lane = tid & 31, warp = tid >> 5;
+    const int grp = tid / T, gtid = tid % T, gwarp = warp % WG;
+    const int nvec = g.K / XPV;  // vectors per row
+    const MegaLayer *lw = g.layer < p.L ? &p.layers[g.layer] : nullptr;
+    TileIter ti(g, (int)sizeof(WT), sh.stage_bytes, cta, nctas);
+    const int my_rows = (int)(ti.r1 - ti.r0);
+
+    // ---- prologue: this thread's slice of the input vector, in registers; one batch of loads --------
+    float xr[NXV * XPV];
+    const float *norm_w = nullptr;
+    if (g.kind == PH_QKV) norm_w = lw->norm1;
+    else if (g.kind == PH_GATEUP) norm_w = lw->norm2;
+    else if (g.kind == PH_LMHEAD) norm_w = p.final_norm;
+    // residual of the row this thread will finish (h = x + attn_out, out = h + mlp_out): fetch it now
+    float resid = 0.f;
+    if ((g.kind == PH_O || g.kind == PH_DOWN) && tid < my_rows) resid = __ldcg(p.x + ti.r0 + tid);
+
+    if (g.kind == PH_O) {
+        // Merge the attention splits once per CTA into shared memory (the partial-sum table is idle now):
+        // out = ctx * (1/(l + 1e-9)) (self_attention.rs:287-290); then every thread picks up its slice.
+        float *xs = sh.part;
+        const int nv4 = g.K / 4;
+        for (int base = 0; base < nv4; base += 2 * kConsumers) {
+            float pm[2][kMaxSplit], pl[2][kMaxSplit];
+            float4 pc[2][kMaxSplit];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int v = base + tid + kConsumers * u;
+                const bool okv = v < nv4;
+                const int k0 = okv ? v * 4 : 0;
+                const size_t row = (size_t)(k0 / p.D);
+                const int e0 = k0 % p.D;
+#pragma unroll
+                for (int sp = 0; sp < kMaxSplit; ++sp) {
+                    const bool oks = okv && sp < p.nsplit;
+                    const size_t o = row * p.nsplit + (oks ? sp : 0);
+                    pm[u][sp] = oks ? __ldcg(p.part_m + o) : -INFINITY;
+                    pl[u][sp] = oks ? __ldcg(p.part_l + o) : 0.f;
+                    pc[u][sp] = oks ? __ldcg(reinterpret_cast<const float4 *>(p.part_ctx + o * p.D + e0))
+                                    : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int v = base + tid + kConsumers * u;
+                float M = -INFINITY;
+#pragma unroll
+                for (int sp = 0; sp < kMaxSplit; ++sp) M = fmaxf(M, pm[u][sp]);
+                float L = 0.f;
+                float4 c = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int sp = 0; sp < kMaxSplit; ++sp) {
+                    if (pm[u][sp] != -INFINITY) {
+                        const float f = expf(pm[u][sp] - M);
+                        L = fmaf(pl[u][sp], f, L);
+                        c.x = fmaf(pc[u][sp].x, f, c.x);
+                        c.y = fmaf(pc[u][sp].y, f, c.y);
+                        c.z = fmaf(pc[u][sp].z, f, c.z);
+                        c.w = fmaf(pc[u][sp].w, f, c.w);
+                    }
+                }
+                const float inv = __fdiv_rn(1.0f, __fadd_rn(L, 1e-9f));
+                if (v < nv4)
+                    reinterpret_cast<float4 *>(xs)[v] = make_float4(__fmul_rn(c.x, inv), __fmul_rn(c.y, inv),
+                                                                    __fmul_rn(c.z, inv), __fmul_rn(c.w, inv));
+            }
+        }
+        consumer_bar();
+#pragma unroll
+        for (int j = 0; j < NXV; ++j) {
+            const int v = gtid + T * j;
+#pragma unroll
+            for (int q = 0; q < XPV / 4; ++q) {
+                const float4 t = (v < nvec) ? reinterpret_cast<const float4 *>(xs)[(size_t)v * (XPV / 4) + q]
+                                            : make_float4(0.f, 0.f, 0.f, 0.f);
+                xr[j * XPV + 4 * q + 0] = t.x;
+                xr[j * XPV + 4 * q + 1] = t.y;
+                xr[j * XPV + 4 * q + 2] = t.z;
+                xr[j * XPV + 4 * q + 3] = t.w;
+            }
+        }
+        consumer_bar();  // the table is about to collect partial sums again
+    } else if (g.kind == PH_QKV && g.layer == 0 && p.wbf16) {
+        // Embedding::forward row of a bf16 table (embedding.rs:47-57)
+#pragma unroll
+        for (int j = 0; j < NXV; ++j) {
+            const int v = gtid + T * j;
+#pragma unroll
+            for (int e = 0; e < XPV; ++e) xr[j * XPV + e] = (v < nvec) ? embed_elem(p, id, v * XPV + e) : 0.f;
+        }
+    } else {
+        const float *src = (g.kind == PH_DOWN) ? p.act
+                           : (g.kind == PH_QKV && g.layer == 0) ? reinterpret_cast<const float *>(p.embed) + id * p.H
+                                                                : p.x;
+        const float4 *s4 = reinterpret_cast<const float4 *>(src);
+#pragma unroll
+        for (int j = 0; j < NXV; ++j) {
+            const int v = gtid + T * j;
+            const bool okv = v < nvec;
+#pragma unroll
+            for (int q = 0; q < XPV / 4; ++q) {
+                const float4 t = okv ? __ldcg(s4 + (size_t)v * (XPV / 4) + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+                xr[j * XPV + 4 * q + 0] = t.x;
+                xr[j * XPV + 4 * q + 1] = t.y;
+                xr[j * XPV + 4 * q + 2] = t.z;
+                xr[j * XPV + 4 * q + 3] = t.w;
+            }
+        }
+    }
+    if (norm_w) {
+        // RMSNorm::forward (rms_norm.rs:49-56): rms = sqrt(ss/dim + eps); x = (x * (1/rms)) * w.
+        // The gains are fetched before the reduction so that they share the round trip of x.
+        float nw[NXV * XPV];
+        const float4 *n4 = reinterpret_cast<const float4 *>(norm_w);
+#pragma unroll
+        for (int j = 0; j < NXV; ++j) {
+            const int v = gtid + T * j;
+            const bool okv = v < nvec;
+#pragma unroll
+            for (int q = 0; q < XPV / 4; ++q) {
+                const float4 t = okv ? __ldg(n4 + (size_t)v * (XPV / 4) + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+                nw[j * XPV + 4 * q + 0] = t.x;
+                nw[j * XPV + 4 * q + 1] = t.y;
+                nw[j * XPV + 4 * q + 2] = t.z;
+                nw[j * XPV + 4 * q + 3] = t.w;
+            }
+        }
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < NXV * XPV; ++i) ss = fmaf(xr[i], xr[i], ss);
+        ss = warp_sum(ss);
+        if (lane == 0) sh.red[warp] = ss;
+        consumer_bar();
+        float tot = 0.f;  // every group holds the whole vector: sum the warps of this thread's group
+#pragma unroll
+        for (int w = 0; w < WG; ++w) tot += sh.red[grp * WG + w];
+        const float inv = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(tot, (float)g.K), p.eps)));
+#pragma unroll
+        for (int i = 0; i < NXV * XPV; ++i) xr[i] = __fmul_rn(__fmul_rn(xr[i], inv), nw[i]);
+    }
+    trace_stamp(p, cta, tid, 3 * ph + 1);
+
+    // ---- tiles ---------------------------------------------------------------------------------------
+    const int rows_per_block = ti.R * (kRowBlock / ti.R);  // a block never splits a tile
+    long blk0 = ti.r0;                                     // first row of the current block
+    int tile = 0;
+    for (; ti.valid(); ti.advance(), ++tile) {
+        const int nr = ti.rows();
+        if (tile % G == grp) {
+            // A failed wait must not leave early (see consumer_bar_ok): skip the math, keep the sequence.
+            // A parity test tells two phases apart, not three: before testing for use `u` of this stage,
+            // use `u-1` (owned by another group) must be known to have landed.  Its owner publishes that.
+            bool have = stage_use_seen(p, sh, rp.s, (int)rp.use, 310 + g.kind);
+            have = have && mbar_wait(p, sh, &sh.full[rp.s], rp.use & 1, 300 + g.kind);
+            if (have && lane == 0) sh.seen[rp.s] = (int)rp.use + 1;
+            const uint4 *st = reinterpret_cast<const uint4 *>(sh.stages + (size_t)rp.s * sh.stage_bytes);
+            float acc[kMaxRowsPerTile];
+#pragma unroll
+            for (int r = 0; r < kMaxRowsPerTile; ++r) acc[r] = 0.f;
+            if (have) {
+#pragma unroll
+                for (int j = 0; j < NXV; ++j) {
+                    const int v = gtid + T * j;
+                    if (v < nvec) {
+#pragma unroll
+                        for (int r = 0; r < kMaxRowsPerTile; ++r) {
+                            if (r < nr) acc[r] = VecTraits<WT>::dot(st[r * nvec + v], &xr[j * XPV], acc[r]);
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cnt(&sh.empty[rp.s], G);  // the G-th share of the 8 expected arrivals
+            float *part = sh.part + ((size_t)ti.mat * kRowBlock + (size_t)(ti.r - blk0)) * kConsumerWarps + gwarp;
+#pragma unroll
+            for (int r = 0; r < kMaxRowsPerTile; ++r) {
+                if (r < nr) {
+                    const float v = warp_sum(acc[r]);
+                    if (lane == 0) part[r * kConsumerWarps] = v;
+                }
+            }
+        }
+        rp.next(sh.S);
+        // End of a row block (or of the phase): reduce the per-warp partials and run the epilogue.
+        const bool last_of_chunk = ti.mat == ti.nmat - 1;
+        const long next_r = ti.r + ti.R;
+        if (last_of_chunk && (next_r >= ti.r1 || next_r - blk0 >= rows_per_block)) {
+            const int nrows = (int)(min(next_r, ti.r1) - blk0);
+            if (!consumer_bar_ok(sh.abort, sh.decision, tid, bk)) return false;
+            if (tid < nrows) {
+                const float *p0 = sh.part + (size_t)tid * kConsumerWarps;
+                float tot = 0.f, tot1 = 0.f;
+#pragma unroll
+                for (int w = 0; w < WG; ++w) tot += p0[w];
+                if (g.nmat == 2) {
+#pragma unroll
+                    for (int w = 0; w < WG; ++w) tot1 += p0[(size_t)kRowBlock * kConsumerWarps + w];
+                }
+                const long row = blk0 + tid;
+                switch (g.kind) {
+                    case PH_QKV: p.qkv[row] = tot; break;
+                    case PH_O:      // h = x + attn_out                                   llama.rs:110
+                    case PH_DOWN:   // out = h + mlp_out                                  llama.rs:115
+                        p.x[row] = __fadd_rn(blk0 == ti.r0 ? resid : __ldcg(p.x + row), tot);
+                        break;
+                    case PH_GATEUP: {  // SiLU (activation.rs:143-146) then gate_act * up (llama.rs:61-63)
+                        const float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-tot)));
+                        p.act[row] = __fmul_rn(__fmul_rn(tot, sig), tot1);
+                        break;
+                    }
+                    default: p.logits[row] = tot; break;
+                }
+            }
+            blk0 = next_r;
+            if (next_r < ti.r1) consumer_bar();  // the table is rewritten by the next block
+        }
+    }
+    trace_stamp(p, cta, tid, 3 * ph + 2);
+    return true;
+}
+
+template <typename WT, int G>
+__device__ __forceinline__ bool gemv_phase_nxv(const MegaParams &p, Shared &sh, const Phase &g, long id, RingPos &rp, int cta,
+                                               int nctas, int tid, int &bk, int ph, int need) {
+    if (need <= 4) return gemv_phase<WT, 4, G>(p, sh, g, id, rp, cta, nctas, tid, bk, ph);
+    return gemv_phase<WT, 8, G>(p, sh, g, id, rp, cta, nctas, tid, bk, ph);
+}
+
+// Picks the number of warp groups: the most groups whose threads still hold their input slice in
+// registers (<= 8 vectors per thread for f32 weights, <= 4 preferred for bf16 whose vectors are twice
+// as wide in x).
+template <typename WT>
+__device__ __forceinline__ bool gemv_phase_dispatch(const MegaParams &p, Shared &sh, const Phase &g, long id, RingPos &rp, int cta, int nctas,
+                                    int tid, int &bk, int ph) {
+    constexpr int XPV = VecTraits<WT>::XPV;
+    constexpr int kPrefer = XPV == 4 ? 8 : 4;
+    const int nvec = g.K / XPV;
+    const int need4 = (nvec + kConsumers / 4 - 1) / (kConsumers / 4);
+    const int need2 = (nvec + kConsumers / 2 - 1) / (kConsumers / 2);
+    const int need1 = (nvec + kConsumers - 1) / kConsumers;
+    if (need4 <= kPrefer) return gemv_phase_nxv<WT, 4>(p, sh, g, id, rp, cta, nctas, tid, bk, ph, need4);
+    if (need2 <= kPrefer) return gemv_phase_nxv<WT, 2>(p, sh, g, id, rp, cta, nctas, tid, bk, ph, need2);
+    return gemv_phase_nxv<WT, 1>(p, sh, g, id, rp, cta, nctas, tid, bk, ph, need1);  // the launcher rejects need1 > 8
+}
+
+__device__ __forceinline__ void attention_phase(const MegaParams &p, Shared &sh, int layer, int past, int cta, int nctas, int tid) {
+    const MegaLayer &l = p.layers[layer];
+    DecodeParams dp;
+    dp.q = p.qkv; dp.k_new = p.qkv + p.qd; dp.v_new = p.qkv + p.qd + p.kvd;
+    dp.q_stride = 0; dp.kv_stride = 0;
+    dp.k_cache = l.k_cache; dp.v_cache = l.v_cache; dp.d_len = l.d_len;
+    dp.Hq = p.Hq; dp.Hkv = p.Hkv; dp.D = p.D; dp.max_seq = p.max_seq;
+    dp.cos_t = p.cos_t; dp.sin_t = p.sin_t; dp.q_norm = l.qn; dp.k_norm = l.kn;
+    dp.norm_eps = p.eps; dp.scale = p.scale;
+    dp.part_m = p.part_m; dp.part_l = p.part_l; dp.part_ctx = p.part_ctx;
+    dp.nsplit = p.nsplit;
+    const int items = p.Hq * p.nsplit;
+    for (int item = cta; item < items; item += nctas) {
+        const int h = item / p.nsplit, split = item % p.nsplit;
+        if (p.D <= 32) attn_decode_item<1, 1>(dp, sh.attn, 0, h, split, tid, past, ConsumerBar());
+        else if (p.D <= 64) attn_decode_item<1, 2>(dp, sh.attn, 0, h, split, tid, past, ConsumerBar());
+        else if (p.D <= 128) attn_decode_item<1, 4>(dp, sh.attn, 0, h, split, tid, past, ConsumerBar());
+        else attn_decode_item<1, 8>(dp, sh.attn, 0, h, split, tid, past, ConsumerBar());
+    }
+}
+
+__device__ __forceinline__ void consumer_loop(const MegaParams &p, Shared &sh, int cta, int nctas, int tid) {
+    // Token id: f32 -> usize with Rust's saturating cast (embedding.rs:50); id >= vocab is the reference's
+    // panic: record it and run nothing (every CTA takes the same branch, so no barrier is left hanging).
+    const float f = __ldcg(p.ids);
+    const int past = __ldcg(p.layers[0].d_len);  // context length before this token, the same for every layer
+    const unsigned long long uid = (f != f || f <= 0.f) ? 0ull : (f >= 1.8e19f ? ~0ull : (unsigned long long)f);
+    if (uid >= (unsigned long long)p.vocab) {
+        if (cta == 0 && tid == 0 && atomicCAS(&p.status->code, 0, LUMEN_ERR_EMBED_RANGE) == 0) {
+            p.status->detail0 = 0;
+            p.status->detail1 = (int)min(uid, (unsigned long long)0x7fffffff);
+        }
+        if (tid == 0) *sh.abort = 1;  // releases the producer
+        return;
+    }
+    const long id = (long)uid;
+    // The residual stream starts as the embedding row; each CTA stores its slice of it.
+    {
+        const long k0 = (long)p.H * cta / nctas, k1 = (long)p.H * (cta + 1) / nctas;
+        for (long k = k0 + tid; k < k1; k += kConsumers) p.x[k] = embed_elem(p, id, (int)k);
+    }
+    const int nphases = 5 * p.L + 1;
+    RingPos rp{0, 0};
+    int barrier = 0, bk = 0;
+    for (int ph = 0; ph < nphases; ++ph) {
+        const Phase g = get_phase(p, ph);
+        trace_stamp(p, cta, tid, 3 * ph);
+        if (g.kind == PH_ATT) {
+            attention_phase(p, sh, g.layer, past, cta, nctas, tid);
+            trace_stamp(p, cta, tid, 3 * ph + 1);
+            trace_stamp(p, cta, tid, 3 * ph + 2);
+        } else {
+            const bool ok = p.wbf16 ? gemv_phase_dispatch<__nv_bfloat16>(p, sh, g, id, rp, cta, nctas, tid, bk, ph)
+                                    : gemv_phase_dispatch<float>(p, sh, g, id, rp, cta, nctas, tid, bk, ph);
+            if (!ok) return;
+        }
+        if (ph + 1 < nphases && !grid_sync(p, sh, barrier++, nctas, tid, bk)) return;
+    }
+    trace_stamp(p, cta, tid, 3 * nphases);
+    // c.len = new_len (self_attention.rs:179) for every layer's cache.
+    for (int l = tid; cta == 0 && l < p.L; l += kConsumers) *p.layers[l].d_len = past + 1;
+}
+
+// The parameter block is __grid_constant__ so that helpers can take it by reference without the compiler
+// materialising a per-thread copy in local memory: with ~200 KB of shared memory in use the L1 is tiny,
+// and every stack access would become an L2 round trip on the critical path.
+__global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const __grid_constant__ MegaParams p) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ uint64_t bars[2 * kMegaMaxStages];
+    __shared__ int abort_flag;
+    __shared__ int decision[2];
+    __shared__ int seen[kMegaMaxStages];
+    Shared sh;
+    sh.S = p.stages;
+    sh.stage_bytes = p.stage_bytes;
+    sh.stages = smem_raw;
+    float *fl = reinterpret_cast<float *>(smem_raw + (size_t)p.stages * p.stage_bytes);
+    sh.part = fl;
+    sh.red = sh.part + 2 * kRowBlock * kConsumerWarps;
+    sh.attn = sh.red + kConsumerWarps;
+    sh.full = bars;
+    sh.empty = bars + kMegaMaxStages;
+    sh.abort = &abort_flag;
+    sh.decision = decision;
+    sh.seen = seen;
+    const int tid = threadIdx.x;
+    if (tid == 0) {
+        abort_flag = 0;
+        decision[0] = decision[1] = 0;
+        for (int s = 0; s < kMegaMaxStages; ++s) seen[s] = 0;
+        for (int s = 0; s < sh.S; ++s) {
+            mbar_init(&sh.full[s], 1);                 // the producer's arrive.expect_tx
+            mbar_init(&sh.empty[s], kConsumerWarps);   // 8 arrivals: the owning group's warps, G each
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const int cta = blockIdx.x, nctas = gridDim.x;
+    if (tid >= kConsumers) {
+        if (tid == kConsumers) producer_loop(p, sh, cta, nctas);
+    } else {
+        consumer_loop(p, sh, cta, nctas, tid);
+    }
+}
+
+}  // namespace
+
+size_t decode_mega_smem_bytes(int stages, int stage_bytes, int head_dim) {
+    return (size_t)stages * stage_bytes +
+           (2 * kRowBlock * kConsumerWarps + kConsumerWarps + attn_decode_smem_floats(1, head_dim)) * sizeof(float);
+}
+
+int decode_mega_max_splits() { return kMaxSplit; }
+
+int decode_mega_supported(const MegaParams &p, char *why, size_t why_len) {
+    const int esz = p.wbf16 ? 2 : 4;
+    const int ks[3] = {p.H, p.qd, p.I};
+    for (int k : ks) {
+        if ((k * esz) % 16) {
+            snprintf(why, why_len, "row of %d elements is not a multiple of 16 bytes", k);
+            return 0;
+        }
+        const int nvec = k * esz / 16;
+        if ((nvec + kConsumers - 1) / kConsumers > 8) {
+            snprintf(why, why_len, "K=%d too large for the register-resident input slice", k);
+            return 0;
+        }
+    }
+    if (p.D > 256 || (p.D % 4)) {
+        snprintf(why, why_len, "head_dim %d is not a multiple of 4", p.D);
+        return 0;
+    }
+    if ((size_t)p.qd * sizeof(float) > 2 * kRowBlock * kConsumerWarps * sizeof(float)) {
+        snprintf(why, why_len, "attention width %d exceeds the shared staging table", p.qd);
+        return 0;
+    }
+    return 1;
+}
+
+int launch_decode_mega(lumen_ctx *ctx, MegaParams &p, cudaStream_t s) {
+    // Ring geometry: 32 KB stages (a row of every supported matrix fits), as many as fit beside the
+    // scratch areas in the 227 KB a CTA may use.
+    p.stage_bytes = 32 * 1024;
+    const size_t budget = 227 * 1024 - 1024;  // static shared (barriers, flags) and alignment slack
+    int stages = kMegaMaxStages;
+    while (stages > 2 && decode_mega_smem_bytes(stages, p.stage_bytes, p.D) > budget) --stages;
+    p.stages = stages;
+    const size_t smem = decode_mega_smem_bytes(stages, p.stage_bytes, p.D);
+    static bool attr_set = false;
+    if (!attr_set) {  // once, for the largest ring any head_dim can ask for
+        LUMEN_CUDA(ctx, cudaFuncSetAttribute(decode_mega_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget));
+        attr_set = true;
+    }
+    // All CTAs must be resident at once (they meet at grid barriers): one per SM, cooperative launch.
+    const int grid = ctx->num_sms;
+    void *args[] = {&p};
+    LUMEN_CUDA(ctx, cudaLaunchCooperativeKernel((const void *)decode_mega_kernel, dim3(grid), dim3(kThreads), args, smem, s));
+    ctx->launches += 1;
+    return LUMEN_OK;
+}
+
+int decode_mega_barriers_per_launch(int layers) { return 5 * layers; }
+
+}  // namespace lumen

@@ -102,6 +102,14 @@ class LlamaModel:
         for name, value in params.items():
             self.set_param(name, value)
 
+    def decode_trace(self) -> np.ndarray:
+        """Phase timestamps (ns) of the last persistent decode step; needs LUMEN_DECODE_TRACE=1."""
+        n = 4 * (5 * self.config.num_hidden_layers + 1) + 1
+        buf = (C.c_uint64 * n)()
+        got = C.c_size_t()
+        self.ctx.check(self.ctx._lib.lumen_llama_decode_trace(self.h, buf, n, C.byref(got)))
+        return np.frombuffer(buf, dtype=np.uint64, count=got.value).copy()
+
     @property
     def weight_bytes_per_step(self) -> int:
         return int(self.ctx._lib.lumen_llama_weight_bytes(self.h))

@@ -100,10 +100,34 @@ def test_graph_replay_equals_eager(L, monkeypatch):
     cfg = small_cfg(max_seq_len=300)
     params = make_params(L, cfg, 41, std=0.08)
     ids = np.random.default_rng(42).integers(0, cfg["vocab_size"], size=(1, 280)).astype(np.float32)
+    monkeypatch.setenv("LUMEN_NO_MEGA", "1")  # batch 1 would otherwise take the persistent kernel
     graph, _, _ = _gpu_run(L, cfg, params, ids, 3)
     monkeypatch.setenv("LUMEN_NO_GRAPH", "1")
     eager, _, _ = _gpu_run(L, cfg, params, ids, 3)
     assert np.array_equal(graph, eager)
+
+
+@pytest.mark.parametrize("over", [dict(), dict(num_key_value_heads=1, hidden_size=96, num_attention_heads=6),
+                                  dict(head_dim=32, qk_norm=True, rope_theta=1e6),
+                                  dict(hidden_size=256, intermediate_size=2304, num_attention_heads=4, vocab_size=1000)])
+@pytest.mark.parametrize("wdt", ["f32", "bf16"])
+def test_persistent_kernel_equals_per_op_path(L, oracle, monkeypatch, over, wdt):
+    """Batch-1 decode runs as one persistent kernel per token; the per-op kernels (one launch per
+    operator) compute the same step.  Both are checked against the oracle and against each other over a
+    context that crosses the attention split thresholds."""
+    cfg = small_cfg(max_seq_len=200, **over)
+    params = make_params(L, cfg, 61, std=0.08, round_bf16=(wdt == "bf16"), random_norms=True)
+    ids = np.random.default_rng(62).integers(0, cfg["vocab_size"], size=(1, 180)).astype(np.float32)
+    mega, _, gc = _gpu_run(L, cfg, params, ids, 2, wdt)
+    monkeypatch.setenv("LUMEN_NO_MEGA", "1")
+    per_op, _, _ = _gpu_run(L, cfg, params, ids, 2, wdt)
+    want, oc = _oracle_run(oracle, cfg, params, ids, 2, "f64")
+    for t in range(ids.shape[1]):
+        assert rel_err(mega[:, t], want[:, t]) < TOL_F32, t
+    assert rel_err(mega, per_op) < 2e-5
+    for l in range(cfg["num_hidden_layers"]):
+        k, v = gc[l].read()
+        assert rel_err(k, oc[l].k) < 1e-5 and rel_err(v, oc[l].v) < 1e-5
 
 
 def test_reset_and_reuse_caches(L):
