@@ -512,7 +512,7 @@ int lumen_llama_new(lumen_ctx *ctx, const lumen_llama_config *cfg, lumen_llama *
     m->use_mega = !(nm && nm[0] == '1');
     const char *tr = getenv("LUMEN_DECODE_TRACE");
     if (tr && tr[0] == '1') {
-        const size_t n = 4 * (5 * m->L + 1) + 1;
+        const size_t n = 4 * (5 * m->L + 1) + 1 + 1024;
         if (cudaMalloc(&m->d_trace, n * sizeof(unsigned long long)) == cudaSuccess) cudaMemset(m->d_trace, 0, n * sizeof(unsigned long long));
         else m->d_trace = nullptr;
     }
@@ -665,7 +665,7 @@ int lumen_llama_decode_trace(lumen_llama *m, uint64_t *out, size_t capacity, siz
     if (!m || !out || !n_out) return LUMEN_ERR_INVALID;
     lumen_ctx *ctx = m->ctx;
     if (!m->d_trace) return set_error(ctx, LUMEN_ERR_UNSUPPORTED, "decode trace is off (set LUMEN_DECODE_TRACE=1 before creating the model)");
-    const size_t n = std::min<size_t>(capacity, 4 * (5 * m->L + 1) + 1);
+    const size_t n = std::min<size_t>(capacity, 4 * (5 * m->L + 1) + 1 + 1024);
     LUMEN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     LUMEN_CUDA(ctx, cudaMemcpy(out, m->d_trace, n * sizeof(uint64_t), cudaMemcpyDeviceToHost));
     *n_out = n;

@@ -37,6 +37,7 @@ constexpr int kThreads = kConsumers + 32;  // + producer warp
 constexpr int kMaxRowsPerTile = 8;
 constexpr int kRowBlock = 256;             // rows reduced together (one per consumer thread)
 constexpr int kMaxSplit = 4;               // attention splits merged in the o_proj prologue
+constexpr int kTileTrace = 512;            // tiles of CTA 0 whose issue / arrival times the trace keeps
 constexpr long long kWaitCycles = 400000000LL;  // ~0.2 s at 1.9 GHz
 
 // ---- PTX helpers -------------------------------------------------------------------------------------
@@ -223,9 +224,8 @@ struct TileIter {
 };
 
 // ---- producer ----------------------------------------------------------------------------------------
-__device__ __forceinline__ void producer_loop(const MegaParams &p, Shared &sh, int cta, int nctas) {
+__device__ __forceinline__ void producer_loop(const MegaParams &p, Shared &sh, int cta, int nctas, int esz) {
     const uint64_t pol = make_evict_first_policy();
-    const int esz = p.wbf16 ? 2 : 4;
     const int nphases = 5 * p.L + 1;
     int s = 0;          // stage of the next tile
     uint32_t use = 0;   // how many times the ring has wrapped
@@ -246,6 +246,7 @@ __device__ __forceinline__ void producer_loop(const MegaParams &p, Shared &sh, i
             const char *src = (ti.mat == 0 ? g.w0 : g.w1) + (size_t)ti.r * ti.rowbytes;
             mbar_expect_tx(&sh.full[s], bytes);
             bulk_load(sh.stages + (size_t)s * sh.stage_bytes, src, bytes, &sh.full[s], pol);
+            if (p.trace && cta == 0 && issued < kTileTrace) p.trace[4 * nphases + 1 + issued] = globaltimer_ns();
             ++issued;
             if (++s == sh.S) {
                 s = 0;
@@ -297,26 +298,28 @@ struct VecTraits;
 template <>
 struct VecTraits<float> {
     static constexpr int XPV = 4;  // x elements per 16-byte weight vector
-    __device__ static __forceinline__ float dot(const uint4 &w, const float *x, float a) {
-        a = fmaf(__uint_as_float(w.x), x[0], a);
-        a = fmaf(__uint_as_float(w.y), x[1], a);
-        a = fmaf(__uint_as_float(w.z), x[2], a);
-        a = fmaf(__uint_as_float(w.w), x[3], a);
+    static constexpr int XQ = 1;   // float4 registers of x per weight vector
+    __device__ static __forceinline__ float dot(const uint4 &w, const float4 *x, float a) {
+        a = fmaf(__uint_as_float(w.x), x[0].x, a);
+        a = fmaf(__uint_as_float(w.y), x[0].y, a);
+        a = fmaf(__uint_as_float(w.z), x[0].z, a);
+        a = fmaf(__uint_as_float(w.w), x[0].w, a);
         return a;
     }
 };
 template <>
 struct VecTraits<__nv_bfloat16> {
     static constexpr int XPV = 8;
-    __device__ static __forceinline__ float dot(const uint4 &w, const float *x, float a) {
-        a = fmaf(bf16_lo(w.x), x[0], a);
-        a = fmaf(bf16_hi(w.x), x[1], a);
-        a = fmaf(bf16_lo(w.y), x[2], a);
-        a = fmaf(bf16_hi(w.y), x[3], a);
-        a = fmaf(bf16_lo(w.z), x[4], a);
-        a = fmaf(bf16_hi(w.z), x[5], a);
-        a = fmaf(bf16_lo(w.w), x[6], a);
-        a = fmaf(bf16_hi(w.w), x[7], a);
+    static constexpr int XQ = 2;
+    __device__ static __forceinline__ float dot(const uint4 &w, const float4 *x, float a) {
+        a = fmaf(bf16_lo(w.x), x[0].x, a);
+        a = fmaf(bf16_hi(w.x), x[0].y, a);
+        a = fmaf(bf16_lo(w.y), x[0].z, a);
+        a = fmaf(bf16_hi(w.y), x[0].w, a);
+        a = fmaf(bf16_lo(w.z), x[1].x, a);
+        a = fmaf(bf16_hi(w.z), x[1].y, a);
+        a = fmaf(bf16_lo(w.w), x[1].z, a);
+        a = fmaf(bf16_hi(w.w), x[1].w, a);
         return a;
     }
 };
@@ -344,6 +347,7 @@ template <typename WT, int NXV, int G>
 __device__ __forceinline__ bool gemv_phase(const MegaParams &p, Shared &sh, const Phase &g, long id, RingPos &rp, int cta, int nctas, int tid,
                            int &bk, int ph) {
     constexpr int XPV = VecTraits<WT>::XPV;
+    constexpr int XQ = VecTraits<WT>::XQ;
     constexpr int T = kConsumers / G;       // threads per group
     constexpr int WG = kConsumerWarps / G;  // warps per group
     const int lane = tid & 31, warp = tid >> 5;
@@ -354,7 +358,7 @@ __device__ __forceinline__ bool gemv_phase(const MegaParams &p, Shared &sh, cons
     const int my_rows = (int)(ti.r1 - ti.r0);
 
     // ---- prologue: this thread's slice of the input vector, in registers; one batch of loads --------
-    float xr[NXV * XPV];
+    float4 xr[NXV * XQ];
     const float *norm_w = nullptr;
     if (g.kind == PH_QKV) norm_w = lw->norm1;
     else if (g.kind == PH_GATEUP) norm_w = lw->norm2;
@@ -418,13 +422,9 @@ __device__ __forceinline__ bool gemv_phase(const MegaParams &p, Shared &sh, cons
         for (int j = 0; j < NXV; ++j) {
             const int v = gtid + T * j;
 #pragma unroll
-            for (int q = 0; q < XPV / 4; ++q) {
-                const float4 t = (v < nvec) ? reinterpret_cast<const float4 *>(xs)[(size_t)v * (XPV / 4) + q]
+            for (int q = 0; q < XQ; ++q) {
+                xr[j * XQ + q] = (v < nvec) ? reinterpret_cast<const float4 *>(xs)[(size_t)v * XQ + q]
                                             : make_float4(0.f, 0.f, 0.f, 0.f);
-                xr[j * XPV + 4 * q + 0] = t.x;
-                xr[j * XPV + 4 * q + 1] = t.y;
-                xr[j * XPV + 4 * q + 2] = t.z;
-                xr[j * XPV + 4 * q + 3] = t.w;
             }
         }
         consumer_bar();  // the table is about to collect partial sums again
@@ -434,7 +434,12 @@ __device__ __forceinline__ bool gemv_phase(const MegaParams &p, Shared &sh, cons
         for (int j = 0; j < NXV; ++j) {
             const int v = gtid + T * j;
 #pragma unroll
-            for (int e = 0; e < XPV; ++e) xr[j * XPV + e] = (v < nvec) ? embed_elem(p, id, v * XPV + e) : 0.f;
+            for (int q = 0; q < XQ; ++q) {
+                const int k = v * XPV + 4 * q;
+                xr[j * XQ + q] = (v < nvec) ? make_float4(embed_elem(p, id, k), embed_elem(p, id, k + 1),
+                                                          embed_elem(p, id, k + 2), embed_elem(p, id, k + 3))
+                                            : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
         }
     } else {
         const float *src = (g.kind == PH_DOWN) ? p.act
@@ -447,35 +452,35 @@ __device__ __forceinline__ bool gemv_phase(const MegaParams &p, Shared &sh, cons
             const bool okv = v < nvec;
 #pragma unroll
             for (int q = 0; q < XPV / 4; ++q) {
-                const float4 t = okv ? __ldcg(s4 + (size_t)v * (XPV / 4) + q) : make_float4(0.f, 0.f, 0.f, 0.f);
-                xr[j * XPV + 4 * q + 0] = t.x;
-                xr[j * XPV + 4 * q + 1] = t.y;
-                xr[j * XPV + 4 * q + 2] = t.z;
-                xr[j * XPV + 4 * q + 3] = t.w;
+                xr[j * XQ + q] = okv ? __ldcg(s4 + (size_t)v * XQ + q) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
         }
     }
     if (norm_w) {
         // RMSNorm::forward (rms_norm.rs:49-56): rms = sqrt(ss/dim + eps); x = (x * (1/rms)) * w.
         // The gains are fetched before the reduction so that they share the round trip of x.
-        float nw[NXV * XPV];
+        // (When x alone already takes 64 registers the gains are fetched after the reduction instead.)
+        constexpr bool kEarlyGains = NXV * XQ <= 8;
+        float4 nw[NXV * XQ];
         const float4 *n4 = reinterpret_cast<const float4 *>(norm_w);
+        if (kEarlyGains) {
 #pragma unroll
-        for (int j = 0; j < NXV; ++j) {
-            const int v = gtid + T * j;
-            const bool okv = v < nvec;
+            for (int j = 0; j < NXV; ++j) {
+                const int v = gtid + T * j;
+                const bool okv = v < nvec;
 #pragma unroll
-            for (int q = 0; q < XPV / 4; ++q) {
-                const float4 t = okv ? __ldg(n4 + (size_t)v * (XPV / 4) + q) : make_float4(0.f, 0.f, 0.f, 0.f);
-                nw[j * XPV + 4 * q + 0] = t.x;
-                nw[j * XPV + 4 * q + 1] = t.y;
-                nw[j * XPV + 4 * q + 2] = t.z;
-                nw[j * XPV + 4 * q + 3] = t.w;
+                for (int q = 0; q < XQ; ++q)
+                    nw[j * XQ + q] = okv ? __ldg(n4 + (size_t)v * XQ + q) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
         }
         float ss = 0.f;
 #pragma unroll
-        for (int i = 0; i < NXV * XPV; ++i) ss = fmaf(xr[i], xr[i], ss);
+        for (int i = 0; i < NXV * XQ; ++i) {
+            ss = fmaf(xr[i].x, xr[i].x, ss);
+            ss = fmaf(xr[i].y, xr[i].y, ss);
+            ss = fmaf(xr[i].z, xr[i].z, ss);
+            ss = fmaf(xr[i].w, xr[i].w, ss);
+        }
         ss = warp_sum(ss);
         if (lane == 0) sh.red[warp] = ss;
         consumer_bar();
@@ -483,49 +488,108 @@ __device__ __forceinline__ bool gemv_phase(const MegaParams &p, Shared &sh, cons
 #pragma unroll
         for (int w = 0; w < WG; ++w) tot += sh.red[grp * WG + w];
         const float inv = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(tot, (float)g.K), p.eps)));
+        if (!kEarlyGains) {
 #pragma unroll
-        for (int i = 0; i < NXV * XPV; ++i) xr[i] = __fmul_rn(__fmul_rn(xr[i], inv), nw[i]);
+            for (int j = 0; j < NXV; ++j) {
+                const int v = gtid + T * j;
+                const bool okv = v < nvec;
+#pragma unroll
+                for (int q = 0; q < XQ; ++q)
+                    nw[j * XQ + q] = okv ? __ldg(n4 + (size_t)v * XQ + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < NXV * XQ; ++i) {
+            xr[i].x = __fmul_rn(__fmul_rn(xr[i].x, inv), nw[i].x);
+            xr[i].y = __fmul_rn(__fmul_rn(xr[i].y, inv), nw[i].y);
+            xr[i].z = __fmul_rn(__fmul_rn(xr[i].z, inv), nw[i].z);
+            xr[i].w = __fmul_rn(__fmul_rn(xr[i].w, inv), nw[i].w);
+        }
     }
     trace_stamp(p, cta, tid, 3 * ph + 1);
 
     // ---- tiles ---------------------------------------------------------------------------------------
+    // Branch-free inner loop: vector indices are clamped into the row (x is zero there, so the extra
+    // products vanish) and rows are taken in static blocks of RB with the row index clamped to the last
+    // valid row, so every block issues its 128-bit shared loads back to back and the RB shuffle
+    // reductions interleave.  Guarded, fully unrolled row/vector slots would serialise into one
+    // load -> FMA chain per slot.
+    int vidx[NXV];
+#pragma unroll
+    for (int j = 0; j < NXV; ++j) vidx[j] = min(gtid + T * j, nvec - 1);
     const int rows_per_block = ti.R * (kRowBlock / ti.R);  // a block never splits a tile
     long blk0 = ti.r0;                                     // first row of the current block
     int tile = 0;
     for (; ti.valid(); ti.advance(), ++tile) {
         const int nr = ti.rows();
         if (tile % G == grp) {
-            // A failed wait must not leave early (see consumer_bar_ok): skip the math, keep the sequence.
             // A parity test tells two phases apart, not three: before testing for use `u` of this stage,
             // use `u-1` (owned by another group) must be known to have landed.  Its owner publishes that.
-            bool have = stage_use_seen(p, sh, rp.s, (int)rp.use, 310 + g.kind);
+            // A failed wait must not leave early (see consumer_bar_ok): skip the math, keep the sequence.
+            bool have = (G == 1) || stage_use_seen(p, sh, rp.s, (int)rp.use, 310 + g.kind);
             have = have && mbar_wait(p, sh, &sh.full[rp.s], rp.use & 1, 300 + g.kind);
-            if (have && lane == 0) sh.seen[rp.s] = (int)rp.use + 1;
+            if (have && lane == 0) sh.seen[rp.s] = (int)rp.use + 1;  // also when G == 1: a later phase may need it
             const uint4 *st = reinterpret_cast<const uint4 *>(sh.stages + (size_t)rp.s * sh.stage_bytes);
-            float acc[kMaxRowsPerTile];
+            float *part = sh.part + ((size_t)ti.mat * kRowBlock + (size_t)(ti.r - blk0)) * kConsumerWarps + gwarp;
+            if (ti.R >= 4) {
+                for (int rb = 0; rb < nr; rb += 4) {
+                    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                    const uint4 *rp0 = st + (size_t)min(rb + 0, nr - 1) * nvec, *rp1 = st + (size_t)min(rb + 1, nr - 1) * nvec;
+                    const uint4 *rp2 = st + (size_t)min(rb + 2, nr - 1) * nvec, *rp3 = st + (size_t)min(rb + 3, nr - 1) * nvec;
+                    if (have) {
 #pragma unroll
-            for (int r = 0; r < kMaxRowsPerTile; ++r) acc[r] = 0.f;
-            if (have) {
-#pragma unroll
-                for (int j = 0; j < NXV; ++j) {
-                    const int v = gtid + T * j;
-                    if (v < nvec) {
-#pragma unroll
-                        for (int r = 0; r < kMaxRowsPerTile; ++r) {
-                            if (r < nr) acc[r] = VecTraits<WT>::dot(st[r * nvec + v], &xr[j * XPV], acc[r]);
+                        for (int j = 0; j < NXV; ++j) {
+                            acc[0] = VecTraits<WT>::dot(rp0[vidx[j]], &xr[j * XQ], acc[0]);
+                            acc[1] = VecTraits<WT>::dot(rp1[vidx[j]], &xr[j * XQ], acc[1]);
+                            acc[2] = VecTraits<WT>::dot(rp2[vidx[j]], &xr[j * XQ], acc[2]);
+                            acc[3] = VecTraits<WT>::dot(rp3[vidx[j]], &xr[j * XQ], acc[3]);
                         }
                     }
-                }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cnt(&sh.empty[rp.s], G);  // the G-th share of the 8 expected arrivals
-            float *part = sh.part + ((size_t)ti.mat * kRowBlock + (size_t)(ti.r - blk0)) * kConsumerWarps + gwarp;
+                    if (rb + 4 >= nr) {  // last block of the tile: the stage can go back to the producer
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_cnt(&sh.empty[rp.s], G);  // the G-th share of the 8 arrivals
+                    }
 #pragma unroll
-            for (int r = 0; r < kMaxRowsPerTile; ++r) {
-                if (r < nr) {
-                    const float v = warp_sum(acc[r]);
-                    if (lane == 0) part[r * kConsumerWarps] = v;
+                    for (int i = 0; i < 4; ++i) {
+                        const float v = warp_sum(acc[i]);
+                        if (lane == 0 && rb + i < nr) part[(rb + i) * kConsumerWarps] = v;
+                    }
                 }
+            } else if (ti.R >= 2) {
+                for (int rb = 0; rb < nr; rb += 2) {
+                    float acc[2] = {0.f, 0.f};
+                    const uint4 *rp0 = st + (size_t)rb * nvec, *rp1 = st + (size_t)min(rb + 1, nr - 1) * nvec;
+                    if (have) {
+#pragma unroll
+                        for (int j = 0; j < NXV; ++j) {
+                            acc[0] = VecTraits<WT>::dot(rp0[vidx[j]], &xr[j * XQ], acc[0]);
+                            acc[1] = VecTraits<WT>::dot(rp1[vidx[j]], &xr[j * XQ], acc[1]);
+                        }
+                    }
+                    if (rb + 2 >= nr) {
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_cnt(&sh.empty[rp.s], G);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        const float v = warp_sum(acc[i]);
+                        if (lane == 0 && rb + i < nr) part[(rb + i) * kConsumerWarps] = v;
+                    }
+                }
+            } else {
+                // One row per tile (long rows): two accumulators break the FMA dependency chain.
+                float a0 = 0.f, a1 = 0.f;
+                if (have) {
+#pragma unroll
+                    for (int j = 0; j < NXV; j += 2) {
+                        a0 = VecTraits<WT>::dot(st[vidx[j]], &xr[j * XQ], a0);
+                        a1 = VecTraits<WT>::dot(st[vidx[j + 1]], &xr[(j + 1) * XQ], a1);
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cnt(&sh.empty[rp.s], G);
+                const float v = warp_sum(a0 + a1);
+                if (lane == 0) part[0] = v;
             }
         }
         rp.next(sh.S);
@@ -612,6 +676,7 @@ __device__ __forceinline__ void attention_phase(const MegaParams &p, Shared &sh,
     }
 }
 
+template <typename WT>
 __device__ __forceinline__ void consumer_loop(const MegaParams &p, Shared &sh, int cta, int nctas, int tid) {
     // Token id: f32 -> usize with Rust's saturating cast (embedding.rs:50); id >= vocab is the reference's
     // panic: record it and run nothing (every CTA takes the same branch, so no barrier is left hanging).
@@ -643,8 +708,7 @@ __device__ __forceinline__ void consumer_loop(const MegaParams &p, Shared &sh, i
             trace_stamp(p, cta, tid, 3 * ph + 1);
             trace_stamp(p, cta, tid, 3 * ph + 2);
         } else {
-            const bool ok = p.wbf16 ? gemv_phase_dispatch<__nv_bfloat16>(p, sh, g, id, rp, cta, nctas, tid, bk, ph)
-                                    : gemv_phase_dispatch<float>(p, sh, g, id, rp, cta, nctas, tid, bk, ph);
+            const bool ok = gemv_phase_dispatch<WT>(p, sh, g, id, rp, cta, nctas, tid, bk, ph);
             if (!ok) return;
         }
         if (ph + 1 < nphases && !grid_sync(p, sh, barrier++, nctas, tid, bk)) return;
@@ -657,6 +721,9 @@ __device__ __forceinline__ void consumer_loop(const MegaParams &p, Shared &sh, i
 // The parameter block is __grid_constant__ so that helpers can take it by reference without the compiler
 // materialising a per-thread copy in local memory: with ~200 KB of shared memory in use the L1 is tiny,
 // and every stack access would become an L2 round trip on the critical path.
+// One kernel per weight type: the bf16 variants hold twice as many activation registers per weight
+// vector, and fusing both into one kernel makes the f32 path spill.
+template <typename WT>
 __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const __grid_constant__ MegaParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ uint64_t bars[2 * kMegaMaxStages];
@@ -690,9 +757,9 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const __grid_c
     __syncthreads();
     const int cta = blockIdx.x, nctas = gridDim.x;
     if (tid >= kConsumers) {
-        if (tid == kConsumers) producer_loop(p, sh, cta, nctas);
+        if (tid == kConsumers) producer_loop(p, sh, cta, nctas, (int)sizeof(WT));
     } else {
-        consumer_loop(p, sh, cta, nctas, tid);
+        consumer_loop<WT>(p, sh, cta, nctas, tid);
     }
 }
 
@@ -739,15 +806,16 @@ int launch_decode_mega(lumen_ctx *ctx, MegaParams &p, cudaStream_t s) {
     while (stages > 2 && decode_mega_smem_bytes(stages, p.stage_bytes, p.D) > budget) --stages;
     p.stages = stages;
     const size_t smem = decode_mega_smem_bytes(stages, p.stage_bytes, p.D);
-    static bool attr_set = false;
-    if (!attr_set) {  // once, for the largest ring any head_dim can ask for
-        LUMEN_CUDA(ctx, cudaFuncSetAttribute(decode_mega_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget));
-        attr_set = true;
+    const void *kern = p.wbf16 ? (const void *)decode_mega_kernel<__nv_bfloat16> : (const void *)decode_mega_kernel<float>;
+    static bool attr_set[2] = {false, false};
+    if (!attr_set[p.wbf16 ? 1 : 0]) {  // once, for the largest ring any head_dim can ask for
+        LUMEN_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget));
+        attr_set[p.wbf16 ? 1 : 0] = true;
     }
     // All CTAs must be resident at once (they meet at grid barriers): one per SM, cooperative launch.
     const int grid = ctx->num_sms;
     void *args[] = {&p};
-    LUMEN_CUDA(ctx, cudaLaunchCooperativeKernel((const void *)decode_mega_kernel, dim3(grid), dim3(kThreads), args, smem, s));
+    LUMEN_CUDA(ctx, cudaLaunchCooperativeKernel(kern, dim3(grid), dim3(kThreads), args, smem, s));
     ctx->launches += 1;
     return LUMEN_OK;
 }

@@ -104,7 +104,7 @@ class LlamaModel:
 
     def decode_trace(self) -> np.ndarray:
         """Phase timestamps (ns) of the last persistent decode step; needs LUMEN_DECODE_TRACE=1."""
-        n = 4 * (5 * self.config.num_hidden_layers + 1) + 1
+        n = 4 * (5 * self.config.num_hidden_layers + 1) + 1 + 1024
         buf = (C.c_uint64 * n)()
         got = C.c_size_t()
         self.ctx.check(self.ctx._lib.lumen_llama_decode_trace(self.h, buf, n, C.byref(got)))
