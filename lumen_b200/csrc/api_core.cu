@@ -62,9 +62,8 @@ int check_device_status(lumen_ctx *ctx) {
     if (ctx->h_status->code != 0) {
         int code = ctx->h_status->code, d0 = ctx->h_status->detail0, d1 = ctx->h_status->detail1;
         LUMEN_CUDA(ctx, cudaMemsetAsync(ctx->d_status, 0, sizeof(DeviceStatus), ctx->stream));
-        // A persistent decode kernel that gave up leaves its barrier counter mid-way: start over.
+        // A persistent decode kernel that gave up leaves its abort flag raised: clear it.
         LUMEN_CUDA(ctx, cudaMemsetAsync(ctx->d_mega_sync, 0, 16, ctx->stream));
-        ctx->mega_bar_base = 0;
         if (code == LUMEN_ERR_EMBED_RANGE) return set_error(ctx, code, "Embedding index out of bounds: id %d at position %d", d1, d0);
         if (code == LUMEN_ERR_TIMEOUT) return set_error(ctx, code, "device-side wait gave up (site %d, value %d)", d0, d1);
         return set_error(ctx, code, "device status %d (%d, %d)", code, d0, d1);

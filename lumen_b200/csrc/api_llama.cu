@@ -82,6 +82,7 @@ struct lumen_llama {
     MegaLayer *d_mega_layers = nullptr;
     const void *mega_key = nullptr;  // first cache's k pointer the layer table was built for
     unsigned long long *d_trace = nullptr;  // phase timestamps of the last persistent step (LUMEN_DECODE_TRACE=1)
+    uint2 *d_exchange = nullptr;            // tagged activation exchange buffers of the persistent kernel
 };
 
 namespace {
@@ -316,21 +317,33 @@ int run_mega(lumen_llama *m, lumen_kv_cache **caches) {
     p.cos_t = m->cos_t; p.sin_t = m->sin_t;
     p.eps = m->cfg.rms_norm_eps;
     p.scale = 1.0f / sqrtf((float)m->D);
-    p.ids = w.ids; p.x = w.x; p.qkv = w.qkv; p.act = w.act; p.logits = w.logits;
-    // Attention work items = heads x splits, about one per SM, with at least 32 rows per split.
+    p.ids = w.ids; p.logits = w.logits;
+    // Exchange buffers of tagged words (zeroed once; tag 0 is never used).
+    const size_t words = decode_mega_exchange_words(p);
+    if (!m->d_exchange) {
+        LUMEN_CUDA(ctx, cudaMalloc(&m->d_exchange, words * sizeof(uint2)));
+        LUMEN_CUDA(ctx, cudaMemsetAsync(m->d_exchange, 0, words * sizeof(uint2), ctx->stream));
+    }
+    const unsigned int per_launch = decode_mega_epochs_per_launch(p.L);
+    if (ctx->mega_epoch > 0xf0000000u - per_launch) {  // tags are about to wrap: start over from clean buffers
+        LUMEN_CUDA(ctx, cudaMemsetAsync(m->d_exchange, 0, words * sizeof(uint2), ctx->stream));
+        ctx->mega_epoch = 1;
+    }
+    p.xT = m->d_exchange;
+    p.qkvT = p.xT + ((p.H + 1) & ~1);
+    p.actT = p.qkvT + ((p.qkv_rows + 1) & ~1);
+    p.partT = p.actT + ((p.I + 1) & ~1);
+    p.epoch_base = ctx->mega_epoch;
+    // Attention work items = heads x splits, at most one per SM, with at least 128 rows per split.
     const size_t len = caches[0]->len + 1;
     int nsplit = std::max(1, std::min(decode_mega_max_splits(), ctx->num_sms / std::max(1, p.Hq)));
-    nsplit = (int)std::max<size_t>(1, std::min<size_t>(nsplit, len / 32));
+    nsplit = (int)std::max<size_t>(1, std::min<size_t>(nsplit, len / 128));
     p.nsplit = nsplit;
-    const size_t rows = (size_t)p.Hq * nsplit;
-    p.part_m = w.part; p.part_l = w.part + rows; p.part_ctx = w.part + 2 * rows;
-    p.bar_counter = ctx->d_mega_sync;
-    p.bar_base = ctx->mega_bar_base;
     p.abort_flag = reinterpret_cast<int *>(ctx->d_mega_sync + 1);
     p.status = ctx->d_status;
     p.trace = m->d_trace;
     LUMEN_TRY(launch_decode_mega(ctx, p, ctx->stream));
-    ctx->mega_bar_base += (unsigned long long)decode_mega_barriers_per_launch(p.L) * (unsigned long long)ctx->num_sms;
+    ctx->mega_epoch += per_launch;
     return LUMEN_OK;
 }
 
@@ -338,6 +351,7 @@ bool mega_usable(lumen_llama *m, size_t b, size_t s) {
     if (!m->use_mega || b != 1 || s != 1 || m->ctx->tp_size != 1 || m->L == 0) return false;
     MegaParams p{};
     p.H = (int)m->H; p.I = (int)m->inter_l; p.qd = (int)m->qd_l; p.D = (int)m->D;
+    p.qkv_rows = (int)m->qkv_rows; p.kvd = (int)m->kvd_l;
     p.wbf16 = m->cfg.weight_dtype == LUMEN_BF16;
     char why[128];
     return decode_mega_supported(p, why, sizeof(why)) != 0;
@@ -678,6 +692,7 @@ int lumen_llama_free(lumen_llama *m) {
     drop_graphs(m);
     if (m->d_mega_layers) cudaFree(m->d_mega_layers);
     if (m->d_trace) cudaFree(m->d_trace);
+    if (m->d_exchange) cudaFree(m->d_exchange);
     if (m->ws.base) cudaFree(m->ws.base);
     if (m->ws.h_ids) cudaFreeHost(m->ws.h_ids);
     if (m->ws.h_logits) cudaFreeHost(m->ws.h_logits);

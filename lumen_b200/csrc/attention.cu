@@ -23,7 +23,8 @@ struct SyncThreads {
 template <int GT, int NI>
 __global__ void __launch_bounds__(kThreads) attn_decode_kernel(DecodeParams p) {
     extern __shared__ __align__(16) float smem[];
-    attn_decode_item<GT, NI>(p, smem, blockIdx.z, blockIdx.y, blockIdx.x, threadIdx.x, *p.d_len, SyncThreads());
+    attn_decode_item<GT, NI, false, kWarps>(p, smem, blockIdx.z, blockIdx.y, blockIdx.x, threadIdx.x, *p.d_len, SyncThreads(),
+                                    PartOut{&p}, NoStage());
 }
 
 // Merge the splits; grid (B*Hq).  Thread 0 of block 0 advances the cache length afterwards

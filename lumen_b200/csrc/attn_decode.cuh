@@ -49,6 +49,7 @@ __device__ __forceinline__ void head_norm_rope(float *buf, int D, const float *n
 // then normalises (optional) and rotates it into shared memory `buf[D]`.  Same arithmetic as
 // head_norm_rope; the loads are issued before anything depends on them so the whole step costs one
 // memory round trip.  Called by one warp.
+template <bool LOCAL = false>
 __device__ __forceinline__ void load_norm_rope(float *buf, const float *src, int D, const float *norm_w, float eps,
                                                const float *cos_row, const float *sin_row, int lane) {
     const int half = D / 2;
@@ -56,7 +57,7 @@ __device__ __forceinline__ void load_norm_rope(float *buf, const float *src, int
 #pragma unroll
     for (int t = 0; t < 8; ++t) {
         const int i = lane + 32 * t;
-        v[t] = (i < D) ? __ldcg(src + i) : 0.f;
+        v[t] = (i < D) ? (LOCAL ? src[i] : __ldcg(src + i)) : 0.f;  // LOCAL: src is already in shared memory
         nw[t] = (norm_w && i < D) ? __ldg(norm_w + i) : 1.f;
     }
 #pragma unroll
@@ -113,22 +114,45 @@ struct DecodeParams {
     int nsplit;
 };
 
-__host__ __device__ inline size_t attn_decode_smem_floats(int GT, int D) {
-    return (size_t)GT * D + D + 2 * kAttnWarps * GT + (size_t)kAttnWarps * GT * D;
+__host__ __device__ inline size_t attn_decode_smem_floats(int GT, int D, int warps = kAttnWarps) {
+    return (size_t)GT * D + D + 2 * warps * GT + (size_t)warps * GT * D;
 }
 
+// Default sink of an item's result: the plain partial arrays of DecodeParams.
+struct PartOut {
+    const DecodeParams *p;
+    __device__ __forceinline__ void operator()(size_t row, int split, int e, float c, float M, float L) const {
+        const size_t o = row * p->nsplit + split;
+        p->part_ctx[o * p->D + e] = c;
+        if (e == 0) {
+            p->part_m[o] = M;
+            p->part_l[o] = L;
+        }
+    }
+};
+
 // One work item: batch row b, KV head group `ygroup` (= hk * (G/GT) + group), context split `split`.
-// Executed by kAttnThreads threads (tid = 0..255) that share `smem` and the barrier `bar()`.
+// Executed by NW warps (tid = 0 .. 32*NW-1) that share `smem` and the barrier `bar()`.
 // GT query heads per item, NI = ceil(D/32) elements per lane.
-template <int GT, int NI, typename Bar>
-__device__ __forceinline__ void attn_decode_item(const DecodeParams &p, float *smem, int b, int ygroup, int split, int tid, int past,
-                                 Bar bar) {
+// LOCAL_IN: p.q / p.k_new / p.v_new point at this item's vectors already staged in shared memory
+// ([GT*D], [D], [D]) instead of the global projection buffer.
+// out(row = b*Hq + head, split, e, ctx_e, max, sum) receives the item's partial result.
+// The first K/V rows of every warp are requested before q is staged: cached rows do not depend on this
+// step's projections, so their round trip overlaps the wait for q.
+// stage() runs after those requests are issued and before q is read: the persistent kernel waits there
+// for the projections of this step (and copies them to shared memory); elsewhere it is a no-op.
+struct NoStage {
+    __device__ __forceinline__ void operator()() const {}
+};
+template <int GT, int NI, bool LOCAL_IN, int NW, typename Bar, typename Out, typename Stage>
+__device__ __forceinline__ void attn_decode_item(const DecodeParams &p, float *smem, int b, int ygroup, int split, int tid,
+                                                 int past, Bar bar, Out out, Stage stage) {
     const int D = p.D;
     float *qs = smem;                        // [GT][D]
     float *knew = qs + GT * D;               // [D]
     float *wm = knew + D;                    // [warps][GT]
-    float *wl = wm + kAttnWarps * GT;        // [warps][GT]
-    float *wctx = wl + kAttnWarps * GT;      // [warps][GT][D]
+    float *wl = wm + NW * GT;        // [warps][GT]
+    float *wctx = wl + NW * GT;      // [warps][GT][D]
 
     const int lane = tid & 31, warp = tid >> 5;
     const int G = p.Hq / p.Hkv;
@@ -143,26 +167,48 @@ __device__ __forceinline__ void attn_decode_item(const DecodeParams &p, float *s
     const int half = D / 2;
     const float *cos_row = p.cos_t ? p.cos_t + (size_t)past * half : nullptr;
     const float *sin_row = p.sin_t ? p.sin_t + (size_t)past * half : nullptr;
+    const float *kbase = p.k_cache + ((size_t)b * p.Hkv + hk) * p.max_seq * D;
+    const float *vbase = p.v_cache + ((size_t)b * p.Hkv + hk) * p.max_seq * D;
+
+    constexpr int UN = NI <= 2 ? 8 : (NI == 4 ? 4 : 2);  // rows whose K and V loads are in flight together
+    float kr[UN][NI], vr[UN][NI];
+    // Rows other than `past` come from the cache (row `past` is patched in from shared memory later).
+    auto load_chunk = [&](int jb) {
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+            const int j = jb + u;
+#pragma unroll
+            for (int i = 0; i < NI; ++i) {
+                const int e = lane + 32 * i;
+                const bool ok = j < j1 && j != past && e < D;
+                kr[u][i] = ok ? __ldcg(kbase + (size_t)j * D + e) : 0.f;
+                vr[u][i] = ok ? __ldcg(vbase + (size_t)j * D + e) : 0.f;
+            }
+        }
+    };
+    int jb = j0 + warp * UN;
+    if (jb < j1) load_chunk(jb);
+    stage();
 
     // Stage and rotate the GT query heads (one warp per head, round robin).
-    for (int g = warp; g < GT; g += kAttnWarps) {
-        const float *src = p.q + (size_t)b * p.q_stride + (size_t)(h0 + g) * D;
-        load_norm_rope(qs + g * D, src, D, p.q_norm, p.norm_eps, cos_row, sin_row, lane);
+    for (int g = warp; g < GT; g += NW) {
+        const float *src = LOCAL_IN ? p.q + (size_t)g * D : p.q + (size_t)b * p.q_stride + (size_t)(h0 + g) * D;
+        load_norm_rope<LOCAL_IN>(qs + g * D, src, D, p.q_norm, p.norm_eps, cos_row, sin_row, lane);
     }
     // Every item whose range holds row `past` rotates the new k into shared memory and uses that copy
-    // (and v_new straight from the projection buffer), so no item reads the cache row written during
-    // this step; the first head group of each KV head also stores the row into the cache.
+    // (and v_new straight from the projection), so no item reads the cache row written during this step;
+    // the first head group of each KV head also stores the row into the cache.
     const bool owns_new = (past >= j0 && past < j1);
-    const float *vnew_src = p.v_new + (size_t)b * p.kv_stride + (size_t)hk * D;
-    if (owns_new && warp == kAttnWarps - 1) {
-        const float *ksrc = p.k_new + (size_t)b * p.kv_stride + (size_t)hk * D;
-        load_norm_rope(knew, ksrc, D, p.k_norm, p.norm_eps, cos_row, sin_row, lane);
+    const float *vnew_src = LOCAL_IN ? p.v_new : p.v_new + (size_t)b * p.kv_stride + (size_t)hk * D;
+    if (owns_new && warp == NW - 1) {
+        const float *ksrc = LOCAL_IN ? p.k_new : p.k_new + (size_t)b * p.kv_stride + (size_t)hk * D;
+        load_norm_rope<LOCAL_IN>(knew, ksrc, D, p.k_norm, p.norm_eps, cos_row, sin_row, lane);
         if (ygroup % groups_per_kv == 0) {
             float *k_row = p.k_cache + (((size_t)b * p.Hkv + hk) * p.max_seq + past) * D;
             float *v_row = p.v_cache + (((size_t)b * p.Hkv + hk) * p.max_seq + past) * D;
             for (int i = lane; i < D; i += 32) {
                 k_row[i] = knew[i];
-                v_row[i] = __ldcg(vnew_src + i);
+                v_row[i] = LOCAL_IN ? vnew_src[i] : __ldcg(vnew_src + i);
             }
         }
     }
@@ -181,29 +227,19 @@ __device__ __forceinline__ void attn_decode_item(const DecodeParams &p, float *s
         }
     }
 
-    const float *kbase = p.k_cache + ((size_t)b * p.Hkv + hk) * p.max_seq * D;
-    const float *vbase = p.v_cache + ((size_t)b * p.Hkv + hk) * p.max_seq * D;
-    constexpr int UN = NI <= 2 ? 8 : (NI == 4 ? 4 : 2);  // rows whose K and V loads are in flight together
-    for (int jb = j0 + warp * UN; jb < j1; jb += kAttnWarps * UN) {
-        float kr[UN][NI], vr[UN][NI];
+    while (jb < j1) {
+        if (past >= jb && past < jb + UN) {  // the row appended by this step: use the staged copies
+            const int u_new = past - jb;
 #pragma unroll
-        for (int u = 0; u < UN; ++u) {
-            const int j = jb + u;
+            for (int u = 0; u < UN; ++u) {
+                if (u == u_new) {
 #pragma unroll
-            for (int i = 0; i < NI; ++i) {
-                const int e = lane + 32 * i;
-                float kv = 0.f, vv = 0.f;
-                if (j < j1 && e < D) {
-                    if (j == past) {  // the row appended by this step: use the staged copy
-                        kv = knew[e];
-                        vv = __ldcg(vnew_src + e);
-                    } else {
-                        kv = __ldcg(kbase + (size_t)j * D + e);
-                        vv = __ldcg(vbase + (size_t)j * D + e);
+                    for (int i = 0; i < NI; ++i) {
+                        const int e = lane + 32 * i;
+                        kr[u][i] = (e < D) ? knew[e] : 0.f;
+                        vr[u][i] = (e < D) ? (LOCAL_IN ? vnew_src[e] : __ldcg(vnew_src + e)) : 0.f;
                     }
                 }
-                kr[u][i] = kv;
-                vr[u][i] = vv;
             }
         }
 #pragma unroll
@@ -225,6 +261,8 @@ __device__ __forceinline__ void attn_decode_item(const DecodeParams &p, float *s
                 m[g] = mn;
             }
         }
+        jb += NW * UN;
+        if (jb < j1) load_chunk(jb);
     }
 
     // Merge the warps of this item.
@@ -241,25 +279,20 @@ __device__ __forceinline__ void attn_decode_item(const DecodeParams &p, float *s
         }
     }
     bar();
-    for (int idx = tid; idx < GT * D; idx += kAttnThreads) {
+    for (int idx = tid; idx < GT * D; idx += (NW * 32)) {
         const int g = idx / D, e = idx % D;
         float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < kAttnWarps; ++w) M = fmaxf(M, wm[w * GT + g]);
+        for (int w = 0; w < NW; ++w) M = fmaxf(M, wm[w * GT + g]);
         float L = 0.f, c = 0.f;
 #pragma unroll
-        for (int w = 0; w < kAttnWarps; ++w) {
+        for (int w = 0; w < NW; ++w) {
             const float mw = wm[w * GT + g];
             const float f = (mw == -INFINITY) ? 0.f : expf(mw - M);
             L = fmaf(wl[w * GT + g], f, L);
             c = fmaf(wctx[(w * GT + g) * D + e], f, c);
         }
-        const size_t o = ((size_t)b * p.Hq + h0 + g) * p.nsplit + split;
-        p.part_ctx[o * D + e] = c;
-        if (e == 0) {
-            p.part_m[o] = M;
-            p.part_l[o] = L;
-        }
+        out((size_t)b * p.Hq + h0 + g, split, e, c, M, L);
     }
     bar();  // shared memory may be reused by the caller's next item
 }

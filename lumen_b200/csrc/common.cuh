@@ -39,9 +39,10 @@ struct lumen_ctx {
     lumen::DeviceStatus *h_status = nullptr;  // pinned mirror
     char err[512] = {0};
     unsigned long long launches = 0;  // kernels enqueued so far (graph replays add their node count)
-    // Grid-barrier state of the persistent decode kernel: [0] = arrival counter (u64), then an abort flag.
+    // Persistent decode kernel: 16 device bytes whose second word is the cross-CTA abort flag, and the
+    // epoch from which the next launch derives the tags of its exchanged activations.
     unsigned long long *d_mega_sync = nullptr;
-    unsigned long long mega_bar_base = 0;  // value of the counter when the next launch starts
+    unsigned int mega_epoch = 1;
 };
 
 struct lumen_storage {

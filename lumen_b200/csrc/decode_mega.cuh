@@ -24,22 +24,30 @@ struct MegaParams {
     const float *cos_t, *sin_t;
     float eps, scale;
     const float *ids;         // [1] f32 token id
-    float *x, *qkv, *act, *logits;
-    float *part_m, *part_l, *part_ctx;  // attention partials [Hq, nsplit], [Hq, nsplit], [Hq, nsplit, D]
+    float *logits;            // [V]
+    // Activations that cross CTAs are exchanged as 8-byte {f32 bits, epoch tag} words: a consumer polls the
+    // words it needs until they carry the tag of the producing phase, so the data is its own signal and no
+    // grid barrier is needed.  tag(phase) = epoch_base + phase + 1; epoch_base grows with every launch.
+    uint2 *xT;                // [H]          residual stream (o_proj and down outputs)
+    uint2 *qkvT;              // [qkv_rows]   q | k | v projections
+    uint2 *actT;              // [I]          SiLU(gate) * up
+    uint2 *partT;             // [Hq, nsplit, 2 + D]: {max}, {sum}, ctx[D] of every attention work item
+    unsigned int epoch_base;
     int nsplit;
-    unsigned long long *bar_counter;    // monotonically increasing arrival counter of the grid barrier
-    unsigned long long bar_base;        // its value when this launch starts
     int *abort_flag;
     DeviceStatus *status;
     int stages, stage_bytes;            // filled by the launcher
     // Optional trace: CTA 0 stores a nanosecond timestamp at the start of each phase, after its prologue
     // and after its last tile (3 per phase), then one at the end.  Null = off.
     unsigned long long *trace;
+    int l2_ahead;  // tiles the producer's L2 prefetch cursor runs ahead of the shared-memory ring
+    int debug_flags;  // bit 0: stream no weight tiles (measures the sync + prologue chain alone; results are wrong)
 };
 
-size_t decode_mega_smem_bytes(int stages, int stage_bytes, int head_dim);
+size_t decode_mega_smem_bytes(int stages, int stage_bytes, int head_dim, int kmax);
 int decode_mega_supported(const MegaParams &p, char *why, size_t why_len);
-int decode_mega_barriers_per_launch(int layers);
+unsigned int decode_mega_epochs_per_launch(int layers);
+size_t decode_mega_exchange_words(const MegaParams &p);  // uint2 words of the four exchange buffers
 int decode_mega_max_splits();
 int launch_decode_mega(lumen_ctx *ctx, MegaParams &p, cudaStream_t s);
 
