@@ -99,10 +99,17 @@ class ClockSampler(threading.Thread):
                 "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
-def tinyllama_cfg(dtype: str, max_seq: int):
+# dram__bytes_read + dram__bytes_write of one persistent-kernel launch divided by its algorithmic bytes,
+# from the ncu capture summarised in profiles/decode_mega_kernel_tinyllama_f32.md (976.5 MB / 967.3 MB).
+MEGA_TRAFFIC_RATIO = 1.0095
+
+
+def tinyllama_cfg(dtype: str, max_seq: int, layers: int = 0):
     from lumen_b200 import synth
     cfg = dict(synth.TINYLLAMA)
     cfg["max_seq_len"] = max_seq
+    if layers:
+        cfg["num_hidden_layers"] = layers
     return cfg
 
 
@@ -174,6 +181,9 @@ def main():
     ap.add_argument("--impl", choices=["lumen", "reference"], default="lumen")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-budget-s", type=float, default=12.0)
+    ap.add_argument("--profile-layers", type=int, default=0,
+                    help="profiling aid: truncate the model to this many layers so that a profiler capture stays "
+                         "small; the printed line is then marked and is not a benchmark value")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
@@ -199,7 +209,7 @@ def main():
     max_seq = 2048
     if total > max_seq:
         raise SystemExit(f"prompt + warmup + steps = {total} exceeds max_seq_len {max_seq}")
-    cfg = tinyllama_cfg(args.dtype, max_seq)
+    cfg = tinyllama_cfg(args.dtype, max_seq, args.profile_layers)
 
     nccl_id = None
     if world > 1:
@@ -302,10 +312,17 @@ def main():
         "gpu_launches": int(launches),
         "clocks": sampler.summary(),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
-                     "kernel": "whole decode step (CUDA graph of %d kernels)" % (launches // max(args.steps, 1)),
+                     "traffic": (bytes_step * MEGA_TRAFFIC_RATIO if launches == args.steps else None),
+                     "traffic_note": "ncu dram bytes of a 4-layer capture (profiles/decode_mega_kernel_tinyllama_f32.md), "
+                                     "scaled by algorithmic bytes", "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
+                     "kernel": ("decode_mega_kernel: one persistent launch runs the whole token"
+                                if launches == args.steps else
+                                "whole decode step (CUDA graph of %d kernels)" % (launches // max(args.steps, 1))),
                      "algorithmic_bytes_per_step": bytes_step},
     }
+    if args.profile_layers:
+        line["profile_only"] = f"model truncated to {args.profile_layers} layers: not a benchmark value"
+        line["config"]["workload"] += f"_truncated_{args.profile_layers}_layers"
     if keep_params:
         tps_cpu, n, threads, cpu_logits = cpu_decode(cfg, params, ids[:PROMPT_LEN + args.warmup + 4 + 64], args.cpu_budget_s,
                                                      args.warmup + 4)
