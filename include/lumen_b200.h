@@ -115,6 +115,20 @@ int lumen_fused_softmax(lumen_ctx *ctx, const lumen_tensor *x, float scale, int 
 int lumen_gemv(lumen_ctx *ctx, const float *x_dev, const void *w_dev, lumen_dtype w_dtype, int layout_kn,
                size_t k, size_t n, float *y_dev);
 
+/* lumen_gemv with layout_kn == 1, for callers that must not allocate: the split-K partial sums live in a
+ * fixed 8 MiB device array inside the library instead of a buffer obtained and released per call, and the
+ * call uses no allocating or freeing routine.  No counterpart in the reference (its tensors are heap
+ * arrays, src/autograd.rs:17-27).
+ *  - Set-up: the first call for a device resolves the array's address (cudaGetSymbolAddress, which may load
+ *    the module); make that call before any stream capture begins.
+ *  - Limit: sizes whose partial sums exceed 8 MiB are refused with LUMEN_ERR_UNSUPPORTED (on 148 SMs that is
+ *    beyond roughly 800k columns); nothing is truncated.  Use lumen_gemv there.
+ *  - Nothing has to be zeroed: each call overwrites every partial sum it later reads.
+ *  - The array is one per device: two calls in flight at once on the same device (other streams, other
+ *    contexts) race on it; calls on one context's stream are ordered and safe. */
+int lumen_gemv_kn_static(lumen_ctx *ctx, const float *x_dev, const void *w_dev, lumen_dtype w_dtype, size_t k,
+                         size_t n, float *y_dev);
+
 /* ---- RotaryEmbedding — src/layers/attention/encoding.rs ------------------------------------
  * new      <- RotaryEmbedding::new + precompute_freqs_cis (:17-54); tables are built on the host
  *             with the f32 recipe of :38-51 and uploaded.

@@ -68,6 +68,7 @@ PROTOTYPES = {
     "lumen_embedding": (_I, [_P, _P, _P, _PP]),
     "lumen_fused_softmax": (_I, [_P, _P, _F, _I, _PP]),
     "lumen_gemv": (_I, [_P, _FP, _P, _I, _I, _SZ, _SZ, _FP]),
+    "lumen_gemv_kn_static": (_I, [_P, _FP, _P, _I, _SZ, _SZ, _FP]),
     "lumen_rope_new": (_I, [_P, _SZ, _SZ, _F, _PP]),
     "lumen_rope_forward": (_I, [_P, _P, _SZ, _PP]),
     "lumen_rope_free": (_I, [_P]),

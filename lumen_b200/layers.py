@@ -41,6 +41,11 @@ def gemv(ctx: Context, x_ptr: int, w_ptr: int, w_dtype: int, layout_kn: bool, k:
     ctx.check(ctx._lib.lumen_gemv(ctx.h, x_ptr, w_ptr, w_dtype, int(layout_kn), k, n, y_ptr))
 
 
+def gemv_kn_static(ctx: Context, x_ptr: int, w_ptr: int, w_dtype: int, k: int, n: int, y_ptr: int) -> None:
+    """[K,N]-layout vector-matrix product that allocates nothing (`lumen_gemv_kn_static`)."""
+    ctx.check(ctx._lib.lumen_gemv_kn_static(ctx.h, x_ptr, w_ptr, w_dtype, k, n, y_ptr))
+
+
 # ---- Module (src/module.rs:12-24) ------------------------------------------------------------------------
 class Module:
     def forward(self, input: Tensor) -> Tensor:  # noqa: A002 - the reference's argument name
