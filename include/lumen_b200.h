@@ -210,6 +210,13 @@ typedef struct {
  *                       the reference's caller keeps, src/main.rs:155-163).
  * forward_device     <- same as forward with DEVICE ids / logits and no synchronisation. */
 int lumen_llama_new(lumen_ctx *ctx, const lumen_llama_config *cfg, lumen_llama **out);
+/* Tensor-parallel shard plan, host arithmetic only (needs no device): the part of the named parameter that
+ * rank tp_rank of tp_size keeps.  out = {rows, cols, row0, nrows, col0, ncols}: rows [row0, row0+nrows) x
+ * columns [col0, col0+ncols) of the full [rows, cols] tensor; cols == 0 means a vector kept whole.  Split:
+ * q/k/v/gate/up by output rows (whole heads; a KV head is replicated when there are fewer than ranks), o/down
+ * by input columns, lm_head by vocabulary rows, norms and the embedding table replicated.  set_param applies
+ * exactly this plan.  No counterpart in the reference (single process). */
+int lumen_tp_param_slice(const lumen_llama_config *cfg, int tp_rank, int tp_size, const char *name, size_t out[6]);
 int lumen_llama_set_param(lumen_llama *m, const char *name, const void *host_data, const size_t *shape, int ndim, lumen_dtype dtype);
 int lumen_llama_init_kv_caches(lumen_llama *m, size_t batch, lumen_kv_cache **caches_out);
 int lumen_llama_reset_kv_caches(lumen_llama *m, lumen_kv_cache **caches, size_t n_caches);

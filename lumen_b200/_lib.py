@@ -88,6 +88,7 @@ PROTOTYPES = {
     "lumen_self_attention_free": (_I, [_P]),
     "lumen_attention_decode": (_I, [_P, _FP, _FP, _FP, _SZ, _P, _P, _I, _FP]),
     "lumen_llama_new": (_I, [_P, C.POINTER(LlamaConfigC), _PP]),
+    "lumen_tp_param_slice": (_I, [C.POINTER(LlamaConfigC), _I, _I, C.c_char_p, _SZP]),
     "lumen_llama_set_param": (_I, [_P, C.c_char_p, _P, _SZP, _I, _I]),
     "lumen_llama_init_kv_caches": (_I, [_P, _SZ, _PP]),
     "lumen_llama_reset_kv_caches": (_I, [_P, _PP, _SZ]),

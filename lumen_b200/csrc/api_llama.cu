@@ -16,6 +16,7 @@
 
 #include "common.cuh"
 #include "decode_mega.cuh"
+#include "tp_plan.cuh"
 
 using namespace lumen;
 
@@ -456,22 +457,16 @@ int lumen_llama_new(lumen_ctx *ctx, const lumen_llama_config *cfg, lumen_llama *
     m->esz = cfg->weight_dtype == LUMEN_F32 ? 4 : 2;
     const size_t T = ctx->tp_size, r = ctx->tp_rank, Hq = cfg->num_attention_heads, Hkv = cfg->num_key_value_heads;
     if (m->D == 0 || (m->D & 1) || m->D > 256) { delete m; return set_error(ctx, LUMEN_ERR_UNSUPPORTED, "head_dim %zu (need even, <= 256)", m->D); }
-    if (Hq % T || m->I % T || m->V % T) { delete m; return set_error(ctx, LUMEN_ERR_UNSUPPORTED, "heads/intermediate/vocab not divisible by tp_size %zu", T); }
-    m->hq_l = Hq / T;
-    m->q_head0 = r * m->hq_l;
-    if (Hkv % T == 0) {
-        m->hkv_l = Hkv / T;
-        m->kv_head0 = r * m->hkv_l;
-    } else if (T % Hkv == 0) {  // fewer KV heads than ranks: each KV head is replicated on T/Hkv ranks
-        m->hkv_l = 1;
-        m->kv_head0 = r / (T / Hkv);
-    } else {
+    TpHeads th;
+    if (tp_head_plan(*cfg, T, r, th) != LUMEN_OK) {
         delete m;
-        return set_error(ctx, LUMEN_ERR_UNSUPPORTED, "kv heads %zu vs tp_size %zu", Hkv, T);
+        return set_error(ctx, LUMEN_ERR_UNSUPPORTED,
+                         "tp_size %zu does not divide heads %zu / kv heads %zu / intermediate %zu / vocab %zu", T, Hq, Hkv,
+                         cfg->intermediate_size, cfg->vocab_size);
     }
+    m->hq_l = th.hq_l; m->q_head0 = th.q_head0; m->hkv_l = th.hkv_l; m->kv_head0 = th.kv_head0;
     m->qd_l = m->hq_l * m->D; m->kvd_l = m->hkv_l * m->D; m->inter_l = m->I / T; m->vocab_l = m->V / T;
     m->qkv_rows = m->qd_l + 2 * m->kvd_l;
-    if (m->hq_l % m->hkv_l) { delete m; return set_error(ctx, LUMEN_ERR_UNSUPPORTED, "local q heads %zu not a multiple of local kv heads %zu", m->hq_l, m->hkv_l); }
 
     // Slab layout.
     const size_t e = m->esz, H = m->H;
@@ -538,73 +533,47 @@ int lumen_llama_set_param(lumen_llama *m, const char *name, const void *host_dat
     if (!m || !name || !host_data || !shape) return LUMEN_ERR_INVALID;
     lumen_ctx *ctx = m->ctx;
     if (dtype != LUMEN_F32 && dtype != LUMEN_BF16) return set_error(ctx, LUMEN_ERR_DTYPE, "set_param: dtype %d", (int)dtype);
-    const size_t H = m->H, D = m->D, T = ctx->tp_size, r = ctx->tp_rank;
-    const size_t Hq = m->cfg.num_attention_heads, Hkv = m->cfg.num_key_value_heads;
     const lumen_dtype wdt = m->cfg.weight_dtype;
-    const size_t se = dtype == LUMEN_F32 ? 4 : 2;
-    auto expect = [&](size_t r0, size_t c0) -> int {
-        if (c0 == 0) {
-            if (ndim != 1 || shape[0] != r0) return set_error(ctx, LUMEN_ERR_SHAPE, "%s: expected [%zu]", name, r0);
-        } else if (ndim != 2 || shape[0] != r0 || shape[1] != c0) {
-            return set_error(ctx, LUMEN_ERR_SHAPE, "%s: expected [%zu,%zu]", name, r0, c0);
-        }
-        return LUMEN_OK;
-    };
-    auto rows_at = [&](size_t row0, size_t cols) { return static_cast<const char *>(host_data) + row0 * cols * se; };
-    int rc = LUMEN_ERR_PARAM_NAME;
-    if (!strcmp(name, "model.embed_tokens.weight")) {
-        LUMEN_TRY(expect(m->V, H));
-        rc = upload_block(ctx, m->embed, wdt, host_data, dtype, m->V, H, 0, H);
-    } else if (!strcmp(name, "model.norm.weight")) {
-        LUMEN_TRY(expect(H, 0));
-        rc = upload_block(ctx, m->final_norm, LUMEN_F32, host_data, dtype, 1, H, 0, H);
-    } else if (!strcmp(name, "lm_head.weight")) {
-        LUMEN_TRY(expect(m->V, H));
-        rc = upload_block(ctx, m->lm_head, wdt, rows_at(r * m->vocab_l, H), dtype, m->vocab_l, H, 0, H);
+    const size_t se = dtype == LUMEN_F32 ? 4 : 2, e = m->esz, H = m->H;
+    // Which part of the tensor this rank keeps comes from the shard plan; what is left here is where it goes.
+    TpSlice sl;
+    long li = -1;
+    const char *leaf = name;
+    int rc = tp_param_slice(m->cfg, ctx->tp_size, ctx->tp_rank, name, sl, &li, &leaf);
+    if (rc != LUMEN_OK) return set_error(ctx, rc, "unknown parameter '%s'", name);
+    if (sl.cols == 0) {
+        if (ndim != 1 || shape[0] != sl.rows) return set_error(ctx, LUMEN_ERR_SHAPE, "%s: expected [%zu]", name, sl.rows);
+    } else if (ndim != 2 || shape[0] != sl.rows || shape[1] != sl.cols) {
+        return set_error(ctx, LUMEN_ERR_SHAPE, "%s: expected [%zu,%zu]", name, sl.rows, sl.cols);
+    }
+    char *dst = nullptr;
+    lumen_dtype ddt = wdt;
+    if (li < 0) {
+        if (!strcmp(leaf, "model.embed_tokens.weight")) dst = m->embed;
+        else if (!strcmp(leaf, "lm_head.weight")) dst = m->lm_head;
+        else { dst = reinterpret_cast<char *>(m->final_norm); ddt = LUMEN_F32; }
     } else {
-        long li = -1;
-        char rest[128];
-        if (sscanf(name, "model.layers.%ld.%127s", &li, rest) != 2 || li < 0 || (size_t)li >= m->L)
-            return set_error(ctx, LUMEN_ERR_PARAM_NAME, "unknown parameter '%s'", name);
         LayerW &w = m->layers[li];
-        const size_t e = m->esz;
-        if (!strcmp(rest, "self_attn.q_proj.weight")) {
-            LUMEN_TRY(expect(Hq * D, H));
-            rc = upload_block(ctx, w.wqkv, wdt, rows_at(m->q_head0 * D, H), dtype, m->qd_l, H, 0, H);
-        } else if (!strcmp(rest, "self_attn.k_proj.weight")) {
-            LUMEN_TRY(expect(Hkv * D, H));
-            rc = upload_block(ctx, w.wqkv + m->qd_l * H * e, wdt, rows_at(m->kv_head0 * D, H), dtype, m->kvd_l, H, 0, H);
-        } else if (!strcmp(rest, "self_attn.v_proj.weight")) {
-            LUMEN_TRY(expect(Hkv * D, H));
-            rc = upload_block(ctx, w.wqkv + (m->qd_l + m->kvd_l) * H * e, wdt, rows_at(m->kv_head0 * D, H), dtype, m->kvd_l, H, 0, H);
-        } else if (!strcmp(rest, "self_attn.o_proj.weight")) {
-            LUMEN_TRY(expect(H, Hq * D));
-            rc = upload_block(ctx, w.wo, wdt, host_data, dtype, H, Hq * D, m->q_head0 * D, m->qd_l);
-        } else if (!strcmp(rest, "mlp.gate_proj.weight")) {
-            LUMEN_TRY(expect(m->I, H));
-            rc = upload_block(ctx, w.wgate, wdt, rows_at(r * m->inter_l, H), dtype, m->inter_l, H, 0, H);
-        } else if (!strcmp(rest, "mlp.up_proj.weight")) {
-            LUMEN_TRY(expect(m->I, H));
-            rc = upload_block(ctx, w.wup, wdt, rows_at(r * m->inter_l, H), dtype, m->inter_l, H, 0, H);
-        } else if (!strcmp(rest, "mlp.down_proj.weight")) {
-            LUMEN_TRY(expect(H, m->I));
-            rc = upload_block(ctx, w.wdown, wdt, host_data, dtype, H, m->I, r * m->inter_l, m->inter_l);
-        } else if (!strcmp(rest, "input_layernorm.weight")) {
-            LUMEN_TRY(expect(H, 0));
-            rc = upload_block(ctx, w.norm1, LUMEN_F32, host_data, dtype, 1, H, 0, H);
-        } else if (!strcmp(rest, "post_attention_layernorm.weight")) {
-            LUMEN_TRY(expect(H, 0));
-            rc = upload_block(ctx, w.norm2, LUMEN_F32, host_data, dtype, 1, H, 0, H);
-        } else if (m->cfg.qk_norm && !strcmp(rest, "self_attn.q_norm.weight")) {
-            LUMEN_TRY(expect(D, 0));
-            rc = upload_block(ctx, w.qn, LUMEN_F32, host_data, dtype, 1, D, 0, D);
-        } else if (m->cfg.qk_norm && !strcmp(rest, "self_attn.k_norm.weight")) {
-            LUMEN_TRY(expect(D, 0));
-            rc = upload_block(ctx, w.kn, LUMEN_F32, host_data, dtype, 1, D, 0, D);
-        } else {
-            return set_error(ctx, LUMEN_ERR_PARAM_NAME, "unknown parameter '%s'", name);
+        if (!strcmp(leaf, "self_attn.q_proj.weight")) dst = w.wqkv;
+        else if (!strcmp(leaf, "self_attn.k_proj.weight")) dst = w.wqkv + m->qd_l * H * e;
+        else if (!strcmp(leaf, "self_attn.v_proj.weight")) dst = w.wqkv + (m->qd_l + m->kvd_l) * H * e;
+        else if (!strcmp(leaf, "self_attn.o_proj.weight")) dst = w.wo;
+        else if (!strcmp(leaf, "mlp.gate_proj.weight")) dst = w.wgate;
+        else if (!strcmp(leaf, "mlp.up_proj.weight")) dst = w.wup;
+        else if (!strcmp(leaf, "mlp.down_proj.weight")) dst = w.wdown;
+        else {
+            ddt = LUMEN_F32;
+            if (!strcmp(leaf, "input_layernorm.weight")) dst = reinterpret_cast<char *>(w.norm1);
+            else if (!strcmp(leaf, "post_attention_layernorm.weight")) dst = reinterpret_cast<char *>(w.norm2);
+            else if (!strcmp(leaf, "self_attn.q_norm.weight")) dst = reinterpret_cast<char *>(w.qn);
+            else dst = reinterpret_cast<char *>(w.kn);
         }
-        (void)T;
+    }
+    if (sl.cols == 0) {
+        rc = upload_block(ctx, dst, ddt, host_data, dtype, 1, sl.rows, 0, sl.rows);
+    } else {
+        const char *src = static_cast<const char *>(host_data) + sl.row0 * sl.cols * se;
+        rc = upload_block(ctx, dst, ddt, src, dtype, sl.nrows, sl.cols, sl.col0, sl.ncols);
     }
     if (rc == LUMEN_ERR_PARAM_NAME) return set_error(ctx, rc, "unknown parameter '%s'", name);
     if (rc == LUMEN_OK) m->is_set[name] = true;

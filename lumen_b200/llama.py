@@ -59,6 +59,17 @@ class LlamaConfig:
         return shapes
 
 
+def tp_param_slice(config: "LlamaConfig", tp_rank: int, tp_size: int, name: str) -> dict:
+    """The part of parameter `name` that rank `tp_rank` of `tp_size` keeps (`lumen_tp_param_slice`; host
+    arithmetic, needs no GPU).  Returns full shape and the kept row / column ranges."""
+    from ._lib import check, load
+    out = (C.c_size_t * 6)()
+    cfg_c = config.to_c()
+    check(load().lumen_tp_param_slice(C.byref(cfg_c), tp_rank, tp_size, name.encode(), out))
+    rows, cols, r0, nr, c0, nc = (int(v) for v in out)
+    return {"shape": (rows,) if cols == 0 else (rows, cols), "rows": (r0, r0 + nr), "cols": (c0, c0 + nc)}
+
+
 class _ParamRef:
     """What `named_parameters()` hands to a loader: `set_raw_data` uploads into the model's slab."""
 
