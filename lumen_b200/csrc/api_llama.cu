@@ -81,6 +81,10 @@ struct lumen_llama {
     // persistent whole-step decode kernel (batch 1)
     bool use_mega = true;
     MegaLayer *d_mega_layers = nullptr;
+    uint4 *d_sched = nullptr;      // producer schedule of the persistent kernel (see MegaParams::sched)
+    int *d_sched_count = nullptr;
+    size_t sched_capacity = 0;
+    int sched_stride = 0;
     const void *mega_key = nullptr;  // first cache's k pointer the layer table was built for
     unsigned long long *d_trace = nullptr;  // phase timestamps of the last persistent step (LUMEN_DECODE_TRACE=1)
     uint2 *d_exchange = nullptr;            // tagged activation exchange buffers of the persistent kernel
@@ -295,26 +299,44 @@ int check_caches(lumen_llama *m, size_t b, size_t s, lumen_kv_cache **caches, si
 // Batch-1 decode through the persistent kernel: one launch per token.
 int run_mega(lumen_llama *m, lumen_kv_cache **caches) {
     lumen_ctx *ctx = m->ctx;
-    if (m->mega_key != (const void *)caches[0]->k || !m->d_mega_layers) {
-        std::vector<MegaLayer> host(m->L);
-        for (size_t l = 0; l < m->L; ++l) {
-            const LayerW &w = m->layers[l];
-            host[l] = MegaLayer{w.wqkv, w.wo, w.wgate, w.wup, w.wdown, w.norm1, w.norm2, w.qn, w.kn,
-                                caches[l]->k, caches[l]->v, caches[l]->d_len};
-        }
-        if (!m->d_mega_layers) LUMEN_CUDA(ctx, cudaMalloc(&m->d_mega_layers, std::max<size_t>(m->L, 1) * sizeof(MegaLayer)));
-        LUMEN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // earlier launches may still read the table
-        LUMEN_CUDA(ctx, cudaMemcpy(m->d_mega_layers, host.data(), m->L * sizeof(MegaLayer), cudaMemcpyHostToDevice));
-        m->mega_key = caches[0]->k;
-    }
     Workspace &w = m->ws;
     MegaParams p{};
-    p.layers = m->d_mega_layers;
     p.L = (int)m->L; p.H = (int)m->H; p.I = (int)m->inter_l; p.V = (int)m->vocab_l; p.vocab = (int)m->V;
     p.Hq = (int)m->hq_l; p.Hkv = (int)m->hkv_l; p.D = (int)m->D;
     p.qkv_rows = (int)m->qkv_rows; p.qd = (int)m->qd_l; p.kvd = (int)m->kvd_l; p.max_seq = (int)caches[0]->max_seq;
     p.wbf16 = m->cfg.weight_dtype == LUMEN_BF16;
     p.embed = m->embed; p.final_norm = m->final_norm; p.lm_head = m->lm_head;
+    if (m->mega_key != (const void *)caches[0]->k || !m->d_mega_layers) {
+        // (Re)build what depends on addresses: the layer table and the producer's copy schedule.
+        std::vector<MegaLayer> host(m->L);
+        for (size_t l = 0; l < m->L; ++l) {
+            const LayerW &lw = m->layers[l];
+            host[l] = MegaLayer{lw.wqkv, lw.wo, lw.wgate, lw.wup, lw.wdown, lw.norm1, lw.norm2, lw.qn, lw.kn,
+                                caches[l]->k, caches[l]->v, caches[l]->d_len};
+        }
+        std::vector<uint4> entries;
+        std::vector<int> counts;
+        int stride = 0;
+        decode_mega_build_schedule(p, host.data(), ctx->num_sms, entries, counts, stride);
+        LUMEN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // earlier launches may still read the tables
+        if (!m->d_mega_layers) LUMEN_CUDA(ctx, cudaMalloc(&m->d_mega_layers, std::max<size_t>(m->L, 1) * sizeof(MegaLayer)));
+        if (m->d_sched && m->sched_capacity < entries.size()) {
+            cudaFree(m->d_sched);
+            m->d_sched = nullptr;
+        }
+        if (!m->d_sched) {
+            LUMEN_CUDA(ctx, cudaMalloc(&m->d_sched, entries.size() * sizeof(uint4)));
+            m->sched_capacity = entries.size();
+        }
+        if (!m->d_sched_count) LUMEN_CUDA(ctx, cudaMalloc(&m->d_sched_count, counts.size() * sizeof(int)));
+        LUMEN_CUDA(ctx, cudaMemcpy(m->d_mega_layers, host.data(), m->L * sizeof(MegaLayer), cudaMemcpyHostToDevice));
+        LUMEN_CUDA(ctx, cudaMemcpy(m->d_sched, entries.data(), entries.size() * sizeof(uint4), cudaMemcpyHostToDevice));
+        LUMEN_CUDA(ctx, cudaMemcpy(m->d_sched_count, counts.data(), counts.size() * sizeof(int), cudaMemcpyHostToDevice));
+        m->sched_stride = stride;
+        m->mega_key = caches[0]->k;
+    }
+    p.layers = m->d_mega_layers;
+    p.sched = m->d_sched; p.sched_count = m->d_sched_count; p.sched_stride = m->sched_stride;
     p.cos_t = m->cos_t; p.sin_t = m->sin_t;
     p.eps = m->cfg.rms_norm_eps;
     p.scale = 1.0f / sqrtf((float)m->D);
@@ -521,7 +543,7 @@ int lumen_llama_new(lumen_ctx *ctx, const lumen_llama_config *cfg, lumen_llama *
     m->use_mega = !(nm && nm[0] == '1');
     const char *tr = getenv("LUMEN_DECODE_TRACE");
     if (tr && tr[0] == '1') {
-        const size_t n = 4 * (5 * m->L + 1) + 1 + 1024;
+        const size_t n = decode_mega_trace_words(m->L);
         if (cudaMalloc(&m->d_trace, n * sizeof(unsigned long long)) == cudaSuccess) cudaMemset(m->d_trace, 0, n * sizeof(unsigned long long));
         else m->d_trace = nullptr;
     }
@@ -648,7 +670,7 @@ int lumen_llama_decode_trace(lumen_llama *m, uint64_t *out, size_t capacity, siz
     if (!m || !out || !n_out) return LUMEN_ERR_INVALID;
     lumen_ctx *ctx = m->ctx;
     if (!m->d_trace) return set_error(ctx, LUMEN_ERR_UNSUPPORTED, "decode trace is off (set LUMEN_DECODE_TRACE=1 before creating the model)");
-    const size_t n = std::min<size_t>(capacity, 4 * (5 * m->L + 1) + 1 + 1024);
+    const size_t n = std::min<size_t>(capacity, decode_mega_trace_words(m->L));
     LUMEN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     LUMEN_CUDA(ctx, cudaMemcpy(out, m->d_trace, n * sizeof(uint64_t), cudaMemcpyDeviceToHost));
     *n_out = n;
@@ -660,6 +682,8 @@ int lumen_llama_free(lumen_llama *m) {
     cudaStreamSynchronize(m->ctx->stream);
     drop_graphs(m);
     if (m->d_mega_layers) cudaFree(m->d_mega_layers);
+    if (m->d_sched) cudaFree(m->d_sched);
+    if (m->d_sched_count) cudaFree(m->d_sched_count);
     if (m->d_trace) cudaFree(m->d_trace);
     if (m->d_exchange) cudaFree(m->d_exchange);
     if (m->ws.base) cudaFree(m->ws.base);

@@ -3,19 +3,19 @@
 // attention self_attention.rs:141-297, vector-matrix products src/ops/matmul.rs:42-69).
 //
 // Design for B200: one CTA per SM (launched cooperatively so that all CTAs are co-resident).  The
-// last warp of each CTA is a producer: one elected lane walks a static schedule of weight tiles (the
-// CTA's rows of every matrix of every layer, in execution order) and streams them from HBM into a
-// shared-memory ring with 1-D bulk TMA copies (cp.async.bulk + mbarrier transaction counts, L2
-// evict-first).  The schedule does not depend on the activations, so the producer keeps HBM busy across
-// phase boundaries while the consumer warps wait for activations or run the (weight-free) attention.
+// last warp of each CTA is a producer: it walks a schedule of bulk copies that the host built once (the
+// CTA's rows of every matrix of every layer, in execution order) and streams the weight tiles from HBM
+// into a shared-memory ring with 1-D bulk TMA copies (cp.async.bulk + mbarrier transaction counts, L2
+// evict-first, a short cp.async.bulk.prefetch.L2 look-ahead).  The schedule does not depend on the
+// activations, so the producer keeps HBM busy across phase boundaries while the consumer warps wait for
+// activations or run the (weight-free) attention.
 //
-// Consumers: the 4 consumer warps form G independent groups (G = 4, 2 or 1, chosen per matrix from its
-// row length); group g owns every G-th tile, so several tiles are processed at once and no CTA-wide
-// barrier sits between tiles.  Within a group every thread keeps its slice of the input vector in
-// registers (4 warps leave each thread the full 255 registers), reads its 128-bit words of each weight
-// row from shared memory, and the warp's partial sum per row goes to a small shared table; once per row
-// block the table is reduced and the fused epilogue runs (RMSNorm in the prologue, residual add,
-// SiLU*mul).  Phases of a layer: qkv | attention | o_proj(+residual) | gate/up(+SiLU*mul) |
+// Consumers: a phase's input vector is staged in shared memory (RMSNorm applied in place), tiles go
+// round-robin to the 4 consumer warps, and a warp works through its own tiles alone: per 16-byte step
+// a lane reads one vector of x and the matching vector of up to 4 weight rows with conflict-free 128-bit
+// shared loads, the row sums are folded across lanes by one butterfly, and the only CTA-wide barrier is
+// at the end of a row block, where the fused epilogue runs (residual add, SiLU*mul) and the results are
+// published.  Phases of a layer: qkv | attention | o_proj(+residual) | gate/up(+SiLU*mul) |
 // down(+residual).
 //
 // Activations cross CTAs through global memory (L2) as tagged words {f32 bits, tag}: a consumer polls
@@ -45,14 +45,13 @@ constexpr int kThreads = kConsumers + 32;  // + producer warp
 constexpr int kMaxRowsPerTile = 8;
 constexpr int kRowBlock = 128;             // rows reduced together (one per consumer thread)
 constexpr int kMaxSplit = 4;               // attention splits merged in the o_proj prologue
-constexpr int kTileTrace = 512;            // tiles of CTA 0 whose issue / arrival times the trace keeps
 constexpr long long kWaitCycles = 400000000LL;  // ~0.2 s at 1.9 GHz
 
-// Floats of the shared table that holds the per-warp partial sums of a row block ([2][kRowBlock][8]) and,
-// during a phase's prologue, the staged input vector (up to kmax floats).
+// Floats of the staged input vector of a phase (up to kmax elements, zero-padded to four whole steps of a
+// warp through a row: 4 x 32 lanes x 8 elements) and of the table of row sums of a row block ([2][kRowBlock][4]).
+__host__ __device__ inline size_t mega_xs_floats(int kmax) { return (((size_t)kmax + 1023) / 1024) * 1024; }
 __host__ __device__ inline size_t mega_table_floats(int kmax) {
-    const size_t part = 2 * (size_t)kRowBlock * kConsumerWarps;
-    return part > (size_t)kmax ? part : (((size_t)kmax + 3) / 4) * 4;
+    return mega_xs_floats(kmax) + 2 * (size_t)kRowBlock * kConsumerWarps;
 }
 
 // ---- PTX helpers -------------------------------------------------------------------------------------
@@ -123,7 +122,8 @@ __device__ __forceinline__ float bf16_hi(uint32_t u) { return __uint_as_float(u 
 // ---- shared state ------------------------------------------------------------------------------------
 struct Shared {
     unsigned char *stages;
-    float *part;       // [2][kRowBlock][kConsumerWarps] per-warp partial sums of the rows of one block
+    float *xs;         // the phase's input vector (zero-padded)
+    float *part;       // [2][kRowBlock][kConsumerWarps]: row sums of one block (first slot of each row)
     float *red;        // [kConsumerWarps]
     float *attn;       // scratch of the attention item
     uint64_t *full;    // [S]
@@ -186,7 +186,7 @@ struct Phase {
     const char *w0, *w1;
 };
 
-__device__ __forceinline__ Phase get_phase(const MegaParams &p, int ph) {
+__host__ __device__ __forceinline__ Phase get_phase(const MegaParams &p, const MegaLayer *layers, int ph) {
     Phase g;
     g.nmat = 1;
     g.w1 = nullptr;
@@ -196,7 +196,7 @@ __device__ __forceinline__ Phase get_phase(const MegaParams &p, int ph) {
     }
     g.layer = ph / 5;
     g.kind = ph % 5;
-    const MegaLayer &l = p.layers[g.layer];
+    const MegaLayer &l = layers[g.layer];
     switch (g.kind) {
         case PH_QKV: g.N = p.qkv_rows; g.K = p.H; g.w0 = l.wqkv; break;
         case PH_O: g.N = p.H; g.K = p.qd; g.w0 = l.wo; break;
@@ -212,18 +212,20 @@ __device__ __forceinline__ Phase get_phase(const MegaParams &p, int ph) {
 struct TileIter {
     long r, r0, r1;
     int nmat, R, rowbytes, mat;
-    __device__ TileIter(const Phase &g, int esz, int stage_bytes, int cta, int nctas, bool skip_tiles = false) {
+    __host__ __device__ TileIter(const Phase &g, int esz, int stage_bytes, int cta, int nctas, bool skip_tiles = false) {
         rowbytes = g.K * esz;
         nmat = g.nmat;
         r0 = r = (long)g.N * cta / nctas;
         r1 = (long)g.N * (cta + 1) / nctas;
-        R = max(1, min(kMaxRowsPerTile, stage_bytes / max(rowbytes, 1)));
+        R = stage_bytes / (rowbytes > 0 ? rowbytes : 1);
+        R = R < 1 ? 1 : (R > kMaxRowsPerTile ? kMaxRowsPerTile : R);
+        if (R > 4 && R < 8) R = 4;  // the consumers take rows four at a time
         mat = 0;
         if (skip_tiles) r = r1;  // debug: keep the row range, stream nothing
     }
-    __device__ bool valid() const { return r < r1; }
-    __device__ int rows() const { return (int)min((long)R, r1 - r); }
-    __device__ void advance() {
+    __host__ __device__ bool valid() const { return r < r1; }
+    __host__ __device__ int rows() const { return (int)((long)R < r1 - r ? (long)R : r1 - r); }
+    __host__ __device__ void advance() {
         if (++mat == nmat) {
             mat = 0;
             r += R;
@@ -231,81 +233,81 @@ struct TileIter {
     }
 };
 
-// ---- producer ----------------------------------------------------------------------------------------
-// Walks the CTA's weight tiles of the whole token in execution order.
-struct TileWalker {
-    int ph, nphases, esz, stage_bytes, cta, nctas;
-    Phase g;
-    TileIter ti;
-    __device__ TileWalker(const MegaParams &p, int esz_, int stage_bytes_, int cta_, int nctas_)
-        : ph(-1), nphases(5 * p.L + 1), esz(esz_), stage_bytes(stage_bytes_), cta(cta_), nctas(nctas_),
-          g(get_phase(p, 0)), ti(g, esz_, stage_bytes_, cta_, nctas_) {
-        ti.r = ti.r1;  // forces the first call of next() to open phase 0
-    }
-    // Moves to the next tile; false when the token's schedule is exhausted.
-    __device__ bool next(const MegaParams &p, bool first_call) {
-        if (!first_call && ti.valid()) ti.advance();
-        while (!ti.valid()) {
-            if (++ph >= nphases) return false;
-            g = get_phase(p, ph);
-            if (g.kind == PH_ATT) continue;
-            ti = TileIter(g, esz, stage_bytes, cta, nctas, (p.debug_flags & 1) != 0);
-        }
-        return true;
-    }
-    __device__ const char *src() const { return (ti.mat == 0 ? g.w0 : g.w1) + (size_t)ti.r * ti.rowbytes; }
-    __device__ uint32_t bytes() const { return (uint32_t)ti.rows() * (uint32_t)ti.rowbytes; }
-};
-
 __device__ __forceinline__ void prefetch_l2(const void *src, uint32_t bytes) {
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
 }
 
-// One elected thread.  Two cursors run over the same schedule: `ld` feeds the shared-memory ring and
-// blocks when the ring is full; `pf` runs `p.l2_ahead` tiles in front of it and only asks the L2 to fetch
-// the tile (cp.async.bulk.prefetch.L2).  While the consumers sit in barriers or in the attention phase the
-// ring fills up within a few microseconds, but HBM keeps streaming the prefetched tiles into the 126 MB
-// L2, and the ring later refills from L2 faster than HBM could deliver.
-__device__ __forceinline__ void producer_loop(const MegaParams &p, Shared &sh, int cta, int nctas, int esz) {
+// ---- producer ----------------------------------------------------------------------------------------
+// The producer warp walks the CTA's precomputed schedule of bulk copies (MegaParams::sched).  All 32 lanes
+// fetch a batch of 32 entries with one coalesced load (the next batch is requested before the current one
+// is issued, so its latency is hidden); lane 0 then issues the copies: on the first copy of a tile it waits
+// for the stage to be free and arms the stage's mbarrier with the tile's byte count.  A tile made of row
+// segments is one copy per row, packed back to back in the stage.
+__device__ __forceinline__ void producer_loop(const MegaParams &p, Shared &sh, int cta, int lane) {
     const uint64_t pol = make_evict_first_policy();
     const int nphases = 5 * p.L + 1;
-    int s = 0;          // stage of the next tile
-    uint32_t use = 0;   // how many times the ring has wrapped
-    long issued = 0, prefetched = 0;
-    bool ok = true;
-    TileWalker ld(p, esz, sh.stage_bytes, cta, nctas), pf(p, esz, sh.stage_bytes, cta, nctas);
-    bool pf_more = pf.next(p, true);
+    const uint4 *sched = p.sched + (size_t)cta * p.sched_stride;
+    const int n = p.sched_count[cta];
+    int s = -1;          // stage of the current tile
+    uint32_t use = 0;    // how many times the ring has wrapped
+    uint32_t off = 0;    // bytes of the current tile already requested
+    long tiles = 0;
     int last_ph = -1;
-    for (bool more = ld.next(p, true); more; more = ld.next(p, false)) {
-        // keep the L2 cursor ahead (the tiles the ring itself holds need no L2 copy)
-        while (pf_more && prefetched < issued + sh.S + p.l2_ahead) {
-            if (prefetched >= issued + sh.S) prefetch_l2(pf.src(), pf.bytes());
-            ++prefetched;
-            pf_more = pf.next(p, false);
-        }
-        if (ld.ph != last_ph) {
-            if (p.trace && cta == 0) p.trace[3 * nphases + 1 + ld.ph] = globaltimer_ns();
-            last_ph = ld.ph;
-        }
-        if (use > 0 && !mbar_wait(p, sh, &sh.empty[s], (use - 1) & 1, 100 + ld.g.kind)) {
-            ok = false;
-            break;
-        }
-        const uint32_t bytes = ld.bytes();
-        mbar_expect_tx(&sh.full[s], bytes);
-        bulk_load(sh.stages + (size_t)s * sh.stage_bytes, ld.src(), bytes, &sh.full[s], pol);
-        if (p.trace && cta == 0 && issued < kTileTrace) p.trace[4 * nphases + 1 + issued] = globaltimer_ns();
-        ++issued;
-        if (++s == sh.S) {
-            s = 0;
-            ++use;
+    bool ok = true;
+    uint4 nxt = lane < n ? sched[lane] : make_uint4(0u, 0u, 0u, 0u);
+    for (int base = 0; base < n; base += 32) {
+        const uint4 cur = nxt;
+        if (base + 32 + lane < n) nxt = sched[base + 32 + lane];
+        const int cnt = min(32, n - base);
+        for (int i = 0; i < cnt; ++i) {
+            // L2 look-ahead: the lane that holds the entry `ahead` copies further on (in this batch or the
+            // next) asks the L2 to fetch it.  While the consumers wait for activations the ring fills up
+            // within a few microseconds, but HBM keeps streaming into the 126 MB L2, and the ring later
+            // refills from there faster than HBM could deliver.
+            if (p.l2_ahead > 0) {
+                const int j = i + p.l2_ahead;
+                if (lane == (j & 31) && j < 64 && base + j < n) {
+                    const uint4 f = j < 32 ? cur : nxt;
+                    prefetch_l2(reinterpret_cast<const char *>(((unsigned long long)f.y << 32) | f.x), f.z & 0xffffu);
+                }
+            }
+            uint4 e;
+            e.x = __shfl_sync(0xffffffffu, cur.x, i);
+            e.y = __shfl_sync(0xffffffffu, cur.y, i);
+            e.z = __shfl_sync(0xffffffffu, cur.z, i);
+            e.w = __shfl_sync(0xffffffffu, cur.w, i);
+            if (lane != 0 || !ok) continue;
+            if (e.w) {  // first copy of a tile: next stage
+                if (++s == sh.S) {
+                    s = 0;
+                    ++use;
+                }
+                const int ph = (int)(e.z >> 16);
+                if (p.trace && cta == 0 && ph != last_ph) {
+                    p.trace[3 * nphases + 1 + ph] = globaltimer_ns();
+                    last_ph = ph;
+                }
+                if (use > 0 && !mbar_wait(p, sh, &sh.empty[s], (use - 1) & 1, 100)) {
+                    ok = false;
+                    --s;  // this tile was not issued (s == -1 cannot occur here: use > 0)
+                    continue;
+                }
+                mbar_expect_tx(&sh.full[s], e.w);
+                off = 0;
+                if (p.trace && cta == 0 && tiles < kMegaTileTrace) p.trace[7 * nphases + 1 + tiles] = globaltimer_ns();
+                ++tiles;
+            }
+            const uint32_t bytes = e.z & 0xffffu;
+            const char *src = reinterpret_cast<const char *>(((unsigned long long)e.y << 32) | e.x);
+            bulk_load(sh.stages + (size_t)s * sh.stage_bytes + off, src, bytes, &sh.full[s], pol);
+            off += bytes;
         }
     }
-    if (!ok) {
-        // Wait (bounded) for the copies still in flight before the CTA may exit: the last min(issued, S) tiles.
-        const long n = issued < sh.S ? issued : sh.S;
-        for (long i = 0; i < n; ++i) {
-            const long idx = issued - 1 - i;
+    if (lane == 0 && !ok) {
+        // Wait (bounded) for the copies still in flight before the CTA may exit: the last min(tiles, S) tiles.
+        const long m = tiles < sh.S ? tiles : sh.S;
+        for (long i = 0; i < m; ++i) {
+            const long idx = tiles - 1 - i;
             uint64_t *bar = &sh.full[idx % sh.S];
             const uint32_t parity = (uint32_t)((idx / sh.S) & 1);
             const long long t0 = clock64();
@@ -348,35 +350,45 @@ __device__ __forceinline__ bool poll_continue(const MegaParams &p, volatile int 
 
 // All consumer threads: wait until the `n` tagged words at `src` (n even) carry `tag`, and leave their
 // values as floats in shared memory `xs[n]`.  Returns false (uniformly) when the CTA is aborting.
-__device__ __forceinline__ bool poll_vector(const MegaParams &p, Shared &sh, const uint2 *src, int n, uint32_t tag, float *xs,
-                                            int tid, int &bk, int site) {
-    constexpr int kBatch = 4;  // 16-byte loads in flight per thread and pass
-    const uint4 *s4 = reinterpret_cast<const uint4 *>(src);
-    const int npairs = n / 2;
-    for (int base = 0; base < npairs; base += kConsumers * kBatch) {
-        uint4 v[kBatch];
-        const long long t0 = clock64();
-        int spins = 0;
-        bool done = false, alive = true;
-        while (!done && alive) {
-            done = true;
+template <int kBatch>  // 16-byte loads in flight per thread and pass
+__device__ __forceinline__ void poll_vector_pass(const MegaParams &p, Shared &sh, const uint4 *s4, int npairs, int base, uint32_t tag,
+                                                 float *xs, int tid, int site) {
+    uint4 v[kBatch];
+    const long long t0 = clock64();
+    int spins = 0;
+    bool done = false, alive = true;
+    while (!done && alive) {
+        done = true;
 #pragma unroll
-            for (int u = 0; u < kBatch; ++u) {
-                const int idx = base + tid + kConsumers * u;
-                v[u] = idx < npairs ? ld_tagged2(s4 + idx) : make_uint4(0u, tag, 0u, tag);
-            }
-#pragma unroll
-            for (int u = 0; u < kBatch; ++u) done = done && v[u].y == tag && v[u].w == tag;
-            if (!done) alive = poll_continue(p, sh.abort, spins, t0, site, base);
+        for (int u = 0; u < kBatch; ++u) {
+            const int idx = base + tid + kConsumers * u;
+            v[u] = idx < npairs ? ld_tagged2(s4 + idx) : make_uint4(0u, tag, 0u, tag);
         }
-        if (done) {
 #pragma unroll
-            for (int u = 0; u < kBatch; ++u) {
-                const int idx = base + tid + kConsumers * u;
-                if (idx < npairs) *reinterpret_cast<float2 *>(xs + 2 * idx) = make_float2(__uint_as_float(v[u].x), __uint_as_float(v[u].z));
-            }
+        for (int u = 0; u < kBatch; ++u) done = done && v[u].y == tag && v[u].w == tag;
+        if (!done) alive = poll_continue(p, sh.abort, spins, t0, site, base);
+    }
+    if (done) {
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+            const int idx = base + tid + kConsumers * u;
+            if (idx < npairs) *reinterpret_cast<float2 *>(xs + 2 * idx) = make_float2(__uint_as_float(v[u].x), __uint_as_float(v[u].z));
         }
     }
+}
+
+// The whole vector is requested in one pass whenever it fits 24 loads per thread (6144 words): every pass
+// costs a round trip through L2, which is what this wait is made of.
+__device__ __forceinline__ bool poll_vector(const MegaParams &p, Shared &sh, const uint2 *src, int n, uint32_t tag, float *xs,
+                                            int tid, int &bk, int site) {
+    const uint4 *s4 = reinterpret_cast<const uint4 *>(src);
+    const int npairs = n / 2;
+    const int per_thread = (npairs + kConsumers - 1) / kConsumers;
+    if (per_thread <= 4) poll_vector_pass<4>(p, sh, s4, npairs, 0, tag, xs, tid, site);
+    else if (per_thread <= 8) poll_vector_pass<8>(p, sh, s4, npairs, 0, tag, xs, tid, site);
+    else if (per_thread <= 16) poll_vector_pass<16>(p, sh, s4, npairs, 0, tag, xs, tid, site);
+    else
+        for (int base = 0; base < npairs; base += kConsumers * 24) poll_vector_pass<24>(p, sh, s4, npairs, base, tag, xs, tid, site);
     return consumer_bar_ok(sh.abort, sh.decision, tid, bk);
 }
 
@@ -417,305 +429,319 @@ __device__ __forceinline__ float embed_elem(const MegaParams &p, long id, int k)
 }
 
 // Stage / parity bookkeeping of the consumer side of the ring.
+// Hands a stage back to the producer (this warp's share of the stage's arrivals) and, when tracing,
+// notes the time the first warp did so.
+__device__ __forceinline__ void release_stage(const MegaParams &p, Shared &sh, int rs, int count, uint32_t slot, int cta, int gwarp) {
+    mbar_arrive_cnt(&sh.empty[rs], count);
+    if (p.trace && cta == 0 && gwarp == 0 && slot < (uint32_t)kMegaTileTrace)
+        p.trace[7 * (5 * p.L + 1) + 1 + kMegaTileTrace + slot] = globaltimer_ns();
+}
+
+// Tiles this CTA has consumed so far in the token: tile n of the CTA's schedule sits in ring stage n % S,
+// and it is use n / S of that stage.
 struct RingPos {
-    int s;
-    uint32_t use;
-    __device__ void next(int S) {
-        if (++s == S) {
-            s = 0;
-            ++use;
-        }
-    }
+    uint32_t n;
 };
 
 // o_proj prologue: wait for the partial results of every attention work item and merge the splits,
 // out = ctx * (1/(l + 1e-9)) (self_attention.rs:287-290), into shared memory xs[qd].
-__device__ __forceinline__ bool poll_attention(const MegaParams &p, Shared &sh, uint32_t tag, float *xs, int tid, int &bk) {
+template <int NS, int VB>  // NS = context splits handled, VB = output vectors per thread and pass
+__device__ __forceinline__ void poll_attention_pass(const MegaParams &p, Shared &sh, uint32_t tag, float *xs, int tid, int vbase) {
     const int nv4 = p.qd / 4;
     const int rec_words = 2 + p.D;  // uint2 words per (head, split) record
-    for (int v = tid; v < nv4; v += kConsumers) {
-        const int k0 = v * 4, h = k0 / p.D, e0 = k0 % p.D;
-        uint4 ml[kMaxSplit], c01[kMaxSplit], c23[kMaxSplit];
-        const long long t0 = clock64();
-        int spins = 0;
-        bool done = false, alive = true;
-        while (!done && alive) {
-            done = true;
+    uint4 ml[VB][NS], c01[VB][NS], c23[VB][NS];
+    const long long t0 = clock64();
+    int spins = 0;
+    bool done = false, alive = true;
+    while (!done && alive) {
+        done = true;
 #pragma unroll
-            for (int s = 0; s < kMaxSplit; ++s) {
-                const bool oks = s < p.nsplit;
-                const uint4 *rec = reinterpret_cast<const uint4 *>(p.partT + ((size_t)h * p.nsplit + (oks ? s : 0)) * rec_words);
+        for (int b = 0; b < VB; ++b) {
+            const int v = vbase + tid + kConsumers * b;
+            const int k0 = v * 4, h = k0 / p.D, e0 = k0 % p.D;
+#pragma unroll
+            for (int s = 0; s < NS; ++s) {
+                const bool oks = s < p.nsplit && v < nv4;
+                const uint4 *rec = reinterpret_cast<const uint4 *>(p.partT + ((size_t)(oks ? h : 0) * p.nsplit + (oks ? s : 0)) * rec_words);
                 const uint4 ok_word = make_uint4(0xff800000u, tag, 0u, tag);  // {max = -inf, sum = 0}
-                ml[s] = oks ? ld_tagged2(rec) : ok_word;
-                c01[s] = oks ? ld_tagged2(rec + 1 + e0 / 2) : make_uint4(0u, tag, 0u, tag);
-                c23[s] = oks ? ld_tagged2(rec + 2 + e0 / 2) : make_uint4(0u, tag, 0u, tag);
+                ml[b][s] = oks ? ld_tagged2(rec) : ok_word;
+                c01[b][s] = oks ? ld_tagged2(rec + 1 + e0 / 2) : make_uint4(0u, tag, 0u, tag);
+                c23[b][s] = oks ? ld_tagged2(rec + 2 + e0 / 2) : make_uint4(0u, tag, 0u, tag);
             }
-#pragma unroll
-            for (int s = 0; s < kMaxSplit; ++s)
-                done = done && ml[s].y == tag && ml[s].w == tag && c01[s].y == tag && c01[s].w == tag && c23[s].y == tag &&
-                       c23[s].w == tag;
-            if (!done) alive = poll_continue(p, sh.abort, spins, t0, 320, v);
         }
-        if (done) {
-            float M = -INFINITY;
 #pragma unroll
-            for (int s = 0; s < kMaxSplit; ++s) M = fmaxf(M, __uint_as_float(ml[s].x));
-            float L = 0.f;
-            float4 c = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int b = 0; b < VB; ++b)
 #pragma unroll
-            for (int s = 0; s < kMaxSplit; ++s) {
-                const float ms = __uint_as_float(ml[s].x);
-                if (ms != -INFINITY) {
-                    const float f = expf(ms - M);
-                    L = fmaf(__uint_as_float(ml[s].z), f, L);
-                    c.x = fmaf(__uint_as_float(c01[s].x), f, c.x);
-                    c.y = fmaf(__uint_as_float(c01[s].z), f, c.y);
-                    c.z = fmaf(__uint_as_float(c23[s].x), f, c.z);
-                    c.w = fmaf(__uint_as_float(c23[s].z), f, c.w);
-                }
-            }
-            const float inv = __fdiv_rn(1.0f, __fadd_rn(L, 1e-9f));
-            reinterpret_cast<float4 *>(xs)[v] =
-                make_float4(__fmul_rn(c.x, inv), __fmul_rn(c.y, inv), __fmul_rn(c.z, inv), __fmul_rn(c.w, inv));
-        }
+            for (int s = 0; s < NS; ++s)
+                done = done && ml[b][s].y == tag && ml[b][s].w == tag && c01[b][s].y == tag && c01[b][s].w == tag &&
+                       c23[b][s].y == tag && c23[b][s].w == tag;
+        if (!done) alive = poll_continue(p, sh.abort, spins, t0, 320, vbase);
     }
+    if (!done) return;
+#pragma unroll
+    for (int b = 0; b < VB; ++b) {
+        const int v = vbase + tid + kConsumers * b;
+        if (v >= nv4) continue;
+        float M = -INFINITY;
+#pragma unroll
+        for (int s = 0; s < NS; ++s) M = fmaxf(M, __uint_as_float(ml[b][s].x));
+        float L = 0.f;
+        float4 c = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int s = 0; s < NS; ++s) {
+            const float ms = __uint_as_float(ml[b][s].x);
+            if (ms != -INFINITY) {
+                const float f = expf(ms - M);
+                L = fmaf(__uint_as_float(ml[b][s].z), f, L);
+                c.x = fmaf(__uint_as_float(c01[b][s].x), f, c.x);
+                c.y = fmaf(__uint_as_float(c01[b][s].z), f, c.y);
+                c.z = fmaf(__uint_as_float(c23[b][s].x), f, c.z);
+                c.w = fmaf(__uint_as_float(c23[b][s].z), f, c.w);
+            }
+        }
+        const float inv = __fdiv_rn(1.0f, __fadd_rn(L, 1e-9f));
+        reinterpret_cast<float4 *>(xs)[v] =
+            make_float4(__fmul_rn(c.x, inv), __fmul_rn(c.y, inv), __fmul_rn(c.z, inv), __fmul_rn(c.w, inv));
+    }
+}
+
+// As many of a thread's vectors as registers allow are requested per pass (each pass is a round trip
+// through L2): four with one context split, two with two, one with up to kMaxSplit.
+__device__ __forceinline__ bool poll_attention(const MegaParams &p, Shared &sh, uint32_t tag, float *xs, int tid, int &bk) {
+    const int nv4 = p.qd / 4;
+    if (p.nsplit == 1)
+        for (int vb = 0; vb < nv4; vb += 4 * kConsumers) poll_attention_pass<1, 4>(p, sh, tag, xs, tid, vb);
+    else if (p.nsplit == 2)
+        for (int vb = 0; vb < nv4; vb += 2 * kConsumers) poll_attention_pass<2, 2>(p, sh, tag, xs, tid, vb);
+    else
+        for (int vb = 0; vb < nv4; vb += kConsumers) poll_attention_pass<kMaxSplit, 1>(p, sh, tag, xs, tid, vb);
     return consumer_bar_ok(sh.abort, sh.decision, tid, bk);
 }
 
 // One vector-matrix phase for the consumer threads.
-//   NXV = 16-byte weight vectors per thread per row, G = warp groups (each owns every G-th tile).
+//
+// The input vector lives in shared memory for the whole phase (normalised in place when the phase starts
+// with an RMSNorm), so a warp needs no registers for it and any warp can take any tile: tiles go
+// round-robin to the four consumer warps, each warp works through its own tiles without ever meeting the
+// others, and the only CTA-wide synchronisation is at the end of a row block.  Per 16-byte step a lane
+// reads one vector of x and the matching vector of RB weight rows (all conflict-free 128-bit shared loads)
+// and feeds RB accumulators; the RB cross-lane sums are folded into one butterfly (reduce_rows).
 //   xres = the residual-stream value of the row this thread finishes in the o_proj / down phases (the row
 //   split of those two phases is the same, so the value never leaves the thread).
-template <typename WT, int NXV, int G>
+
+// Sum over the 32 lanes of RB accumulators at once: every step halves the number of values a lane still
+// carries by trading the other half with its partner, so RB = 4 costs 6 shuffles instead of 20.  The sum of
+// row reduce_row_of<RB>(lane) ends up in lanes that are multiples of 32 / RB.
+template <int RB>
+__device__ __forceinline__ float reduce_rows(float (&a)[RB], int lane) {
+    int bit = 16;
+#pragma unroll
+    for (int n = RB; n > 1; n >>= 1) {
+        const bool up = (lane & bit) != 0;
+#pragma unroll
+        for (int i = 0; i < n / 2; ++i) {
+            const float send = up ? a[i] : a[i + n / 2];
+            const float keep = up ? a[i + n / 2] : a[i];
+            a[i] = keep + __shfl_xor_sync(0xffffffffu, send, bit);
+        }
+        bit >>= 1;
+    }
+#pragma unroll
+    for (int b = 16 / RB; b > 0; b >>= 1) a[0] += __shfl_xor_sync(0xffffffffu, a[0], b);
+    return a[0];
+}
+template <int RB>
+__device__ __forceinline__ int reduce_row_of(int lane) {
+    if (lane % (32 / RB) != 0) return -1;
+    int row = 0, bit = 16;
+#pragma unroll
+    for (int n = RB; n > 1; n >>= 1) {
+        if (lane & bit) row += n / 2;
+        bit >>= 1;
+    }
+    return row;
+}
+
+// Rows [rb, rb + RB) of one tile (row indices clamped to the tile's last row; x is zero-padded so that the
+// clamped vector index of the last lanes contributes nothing).
+template <typename WT, int RB>
+__device__ __forceinline__ void tile_rows(const uint4 *st, const float4 *xs4, int nvec, int njl, int lane, int nr, int rb,
+                                          float (&acc)[RB]) {
+    constexpr int XQ = VecTraits<WT>::XQ;
+    constexpr int NA = RB >= 4 ? 1 : 4 / RB;  // accumulators per row: four independent FMA chains in all
+    const uint4 *row[RB];
+    float a[RB][NA];
+#pragma unroll
+    for (int i = 0; i < RB; ++i) {
+        row[i] = st + (size_t)min(rb + i, nr - 1) * nvec;
+#pragma unroll
+        for (int c = 0; c < NA; ++c) a[i][c] = 0.f;
+    }
+    const int vlast = nvec - 1;
+    for (int j0 = 0; j0 < njl; j0 += 4) {  // four steps at a time (x is zero-padded to a whole four steps)
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+            const int vx = lane + 32 * (j0 + jj);
+            const int v = min(vx, vlast);
+            float4 x[XQ];
+#pragma unroll
+            for (int q = 0; q < XQ; ++q) x[q] = xs4[vx * XQ + q];
+#pragma unroll
+            for (int i = 0; i < RB; ++i) a[i][jj % NA] = VecTraits<WT>::dot(row[i][v], x, a[i][jj % NA]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < RB; ++i) {
+        float t = a[i][0];
+#pragma unroll
+        for (int c = 1; c < NA; ++c) t += a[i][c];
+        acc[i] = t;
+    }
+}
+
+template <typename WT, int RB>
+__device__ __forceinline__ void consume_tile(const MegaParams &p, Shared &sh, const uint4 *st, const float4 *xs4, int nvec, int njl,
+                                             int lane, int nr, bool have, float *part, int rs, uint32_t slot, int cta) {
+    for (int rb = 0; rb < nr; rb += RB) {
+        float acc[RB];
+        if (have) {
+            tile_rows<WT, RB>(st, xs4, nvec, njl, lane, nr, rb, acc);
+        } else {
+#pragma unroll
+            for (int i = 0; i < RB; ++i) acc[i] = 0.f;
+        }
+        if (rb + RB >= nr) {  // the tile's last loads are done: the stage can go back to the producer
+            __syncwarp();
+            if (lane == 0) release_stage(p, sh, rs, kConsumerWarps, slot, cta, 0);  // all 4 arrivals of the stage
+        }
+        const float s = reduce_rows<RB>(acc, lane);
+        const int r = reduce_row_of<RB>(lane);
+        if (r >= 0 && rb + r < nr) part[(rb + r) * kConsumerWarps] = s;
+    }
+}
+
+template <typename WT>
 __device__ __forceinline__ bool gemv_phase(const MegaParams &p, Shared &sh, const Phase &g, long id, RingPos &rp, int cta, int nctas,
                                            int tid, int &bk, int ph, float &xres) {
     constexpr int XPV = VecTraits<WT>::XPV;
     constexpr int XQ = VecTraits<WT>::XQ;
-    constexpr int T = kConsumers / G;       // threads per group
-    constexpr int WG = kConsumerWarps / G;  // warps per group
     const int lane = tid & 31, warp = tid >> 5;
-    const int grp = tid / T, gtid = tid % T, gwarp = warp % WG;
-    const int nvec = g.K / XPV;  // vectors per row
     const MegaLayer *lw = g.layer < p.L ? &p.layers[g.layer] : nullptr;
-    TileIter ti(g, (int)sizeof(WT), sh.stage_bytes, cta, nctas, (p.debug_flags & 1) != 0);
+    const TileIter ti(g, (int)sizeof(WT), sh.stage_bytes, cta, nctas, (p.debug_flags & 1) != 0);
     if (ti.r0 == ti.r1) return true;  // no rows of this matrix here: nothing to read, nothing to publish
+    const int nvec = g.K / XPV;          // 16-byte weight vectors per row
+    const int njl = (nvec + 31) / 32;    // steps of a lane through a row
 
-    // ---- prologue: this thread's slice of the input vector, in registers ---------------------------------
-    float4 xr[NXV * XQ];
-    const float *norm_w = nullptr;
-    if (g.kind == PH_QKV) norm_w = lw->norm1;
-    else if (g.kind == PH_GATEUP) norm_w = lw->norm2;
-    else if (g.kind == PH_LMHEAD) norm_w = p.final_norm;
-    // RMSNorm gains are fetched first so that they share the wait for x.  (When x alone already takes 64
-    // registers they are fetched after the reduction instead.)
-    constexpr bool kEarlyGains = NXV * XQ <= 8;
-    float4 nw[NXV * XQ];
-    const float4 *n4 = reinterpret_cast<const float4 *>(norm_w);
-    if (norm_w && kEarlyGains) {
-#pragma unroll
-        for (int j = 0; j < NXV; ++j) {
-            const int v = gtid + T * j;
-#pragma unroll
-            for (int q = 0; q < XQ; ++q)
-                nw[j * XQ + q] = v < nvec ? __ldg(n4 + (size_t)v * XQ + q) : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-    }
-    float *xs = sh.part;  // the partial-sum table is idle during the prologue: stage the input vector there
+    // ---- prologue: the input vector, in shared memory ---------------------------------------------------
+    float *xs = sh.xs;
+    float4 *xs4 = reinterpret_cast<float4 *>(xs);
+    const int njl4 = (njl + 3) & ~3;     // the inner loop takes four steps at a time
+    for (int k = g.K + tid; k < njl4 * 32 * XPV; k += kConsumers) xs[k] = 0.f;  // zero padding up to whole steps
     if (g.kind == PH_QKV && g.layer == 0) {
         // Embedding::forward (embedding.rs:47-57): the token's row is the first layer's input
-#pragma unroll
-        for (int j = 0; j < NXV; ++j) {
-            const int v = gtid + T * j;
-#pragma unroll
-            for (int q = 0; q < XQ; ++q) {
-                const int k = v * XPV + 4 * q;
-                xr[j * XQ + q] = (v < nvec) ? make_float4(embed_elem(p, id, k), embed_elem(p, id, k + 1),
-                                                          embed_elem(p, id, k + 2), embed_elem(p, id, k + 3))
-                                            : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-        }
+        for (int k = tid; k < g.K; k += kConsumers) xs[k] = embed_elem(p, id, k);
+        consumer_bar();
     } else {
         const uint32_t tag = phase_tag(p, ph - 1);  // every phase consumes what the phase before it published
         bool ok;
         if (g.kind == PH_O) ok = poll_attention(p, sh, tag, xs, tid, bk);
         else ok = poll_vector(p, sh, g.kind == PH_DOWN ? p.actT : p.xT, g.K, tag, xs, tid, bk, 330 + g.kind);
         if (!ok) return false;
-        if (p.trace && cta == 0 && tid == 0) p.trace[4 * (5 * p.L + 1) + 1 + kTileTrace + ph] = globaltimer_ns();
-#pragma unroll
-        for (int j = 0; j < NXV; ++j) {
-            const int v = gtid + T * j;
-#pragma unroll
-            for (int q = 0; q < XQ; ++q)
-                xr[j * XQ + q] = (v < nvec) ? reinterpret_cast<const float4 *>(xs)[(size_t)v * XQ + q]
-                                            : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
+        if (p.trace && cta == 0 && tid == 0) p.trace[4 * (5 * p.L + 1) + 1 + ph] = globaltimer_ns();
     }
+    const float *norm_w = nullptr;
+    if (g.kind == PH_QKV) norm_w = lw->norm1;
+    else if (g.kind == PH_GATEUP) norm_w = lw->norm2;
+    else if (g.kind == PH_LMHEAD) norm_w = p.final_norm;
     if (norm_w) {
-        // RMSNorm::forward (rms_norm.rs:49-56): rms = sqrt(ss/dim + eps); x = (x * (1/rms)) * w
+        // RMSNorm::forward (rms_norm.rs:49-56): rms = sqrt(ss/dim + eps); x = (x * (1/rms)) * w, in place
+        const float4 *n4 = reinterpret_cast<const float4 *>(norm_w);
+        const int n4s = g.K / 4;
         float ss = 0.f;
-#pragma unroll
-        for (int i = 0; i < NXV * XQ; ++i) {
-            ss = fmaf(xr[i].x, xr[i].x, ss);
-            ss = fmaf(xr[i].y, xr[i].y, ss);
-            ss = fmaf(xr[i].z, xr[i].z, ss);
-            ss = fmaf(xr[i].w, xr[i].w, ss);
+        for (int i = tid; i < n4s; i += kConsumers) {
+            const float4 v = xs4[i];
+            ss = fmaf(v.x, v.x, ss);
+            ss = fmaf(v.y, v.y, ss);
+            ss = fmaf(v.z, v.z, ss);
+            ss = fmaf(v.w, v.w, ss);
         }
         ss = warp_sum(ss);
         if (lane == 0) sh.red[warp] = ss;
-        consumer_bar();  // also: everybody has copied its slice out of xs before partial sums land there
-        float tot = 0.f;  // every group holds the whole vector: sum the warps of this thread's group
-#pragma unroll
-        for (int w = 0; w < WG; ++w) tot += sh.red[grp * WG + w];
+        consumer_bar();
+        const float tot = (sh.red[0] + sh.red[1]) + (sh.red[2] + sh.red[3]);
         const float inv = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(tot, (float)g.K), p.eps)));
-        if (!kEarlyGains) {
-#pragma unroll
-            for (int j = 0; j < NXV; ++j) {
-                const int v = gtid + T * j;
-#pragma unroll
-                for (int q = 0; q < XQ; ++q)
-                    nw[j * XQ + q] = v < nvec ? __ldg(n4 + (size_t)v * XQ + q) : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
+        for (int i = tid; i < n4s; i += kConsumers) {
+            float4 v = xs4[i];
+            const float4 w = __ldg(n4 + i);
+            v.x = __fmul_rn(__fmul_rn(v.x, inv), w.x);
+            v.y = __fmul_rn(__fmul_rn(v.y, inv), w.y);
+            v.z = __fmul_rn(__fmul_rn(v.z, inv), w.z);
+            v.w = __fmul_rn(__fmul_rn(v.w, inv), w.w);
+            xs4[i] = v;
         }
-#pragma unroll
-        for (int i = 0; i < NXV * XQ; ++i) {
-            xr[i].x = __fmul_rn(__fmul_rn(xr[i].x, inv), nw[i].x);
-            xr[i].y = __fmul_rn(__fmul_rn(xr[i].y, inv), nw[i].y);
-            xr[i].z = __fmul_rn(__fmul_rn(xr[i].z, inv), nw[i].z);
-            xr[i].w = __fmul_rn(__fmul_rn(xr[i].w, inv), nw[i].w);
-        }
-    } else {
-        consumer_bar();  // everybody has copied its slice out of xs before partial sums land there
+        consumer_bar();
     }
     trace_stamp(p, cta, tid, 3 * ph + 1);
-    // ---- tiles ---------------------------------------------------------------------------------------
-    // Branch-free inner loop: vector indices are clamped into the row (x is zero there, so the extra
-    // products vanish) and rows are taken in static blocks of RB with the row index clamped to the last
-    // valid row, so every block issues its 128-bit shared loads back to back and the RB shuffle
-    // reductions interleave.  Guarded, fully unrolled row/vector slots would serialise into one
-    // load -> FMA chain per slot.
-    const int vlast = nvec - 1;
-    const int rows_per_block = ti.R * (kRowBlock / ti.R);  // a block never splits a tile
-    long blk0 = ti.r0;                                     // first row of the current block
-    int tile = 0;
-    for (; ti.valid(); ti.advance(), ++tile) {
-        const int nr = ti.rows();
-        if (tile % G == grp) {
+
+    // ---- tiles ------------------------------------------------------------------------------------------
+    // Tiles are addressed in closed form: tile t of the phase covers rows [R * (t / nmat), +R) of the CTA's
+    // range in matrix t % nmat (gate rows, then the same rows of up) and sits in ring slot (tiles consumed
+    // so far + t).  Warp w owns tiles w, w + 4, ...  Rows are reduced and published in blocks of at most
+    // kRowBlock (a block never splits a tile).
+    const int R = ti.R, nmat = ti.nmat;
+    const int nrows_cta = (int)(ti.r1 - ti.r0);
+    const int chunks = (p.debug_flags & 1) ? 0 : (nrows_cta + R - 1) / R;
+    const int chunks_per_block = kRowBlock / R;
+    for (int cb = 0; cb < chunks; cb += chunks_per_block) {
+        const int cend = min(chunks, cb + chunks_per_block);
+        const int t0 = cb * nmat, t1 = cend * nmat;
+        const int row0_blk = cb * R;  // first row of the block, relative to the CTA's first row
+        for (int t = t0 + ((warp - t0) & (kConsumerWarps - 1)); t < t1; t += kConsumerWarps) {
+            const int chunk = t / nmat, mat = t - chunk * nmat;
+            const int rrel = chunk * R;
+            const int nr = min(R, nrows_cta - rrel);
+            const uint32_t slot = rp.n + (uint32_t)t;
+            const int rs = (int)(slot % (uint32_t)sh.S);
+            const uint32_t use = slot / (uint32_t)sh.S;
             // A parity test tells two phases apart, not three: before testing for use `u` of this stage,
-            // use `u-1` (owned by another group) must be known to have landed.  Its owner publishes that.
+            // use `u-1` (owned by another warp) must be known to have landed.  Its owner publishes that.
             // A failed wait must not leave early (see consumer_bar_ok): skip the math, keep the sequence.
-            bool have = (G == 1) || stage_use_seen(p, sh, rp.s, (int)rp.use, 310 + g.kind);
-            have = have && mbar_wait(p, sh, &sh.full[rp.s], rp.use & 1, 300 + g.kind);
-            if (have && lane == 0) sh.seen[rp.s] = (int)rp.use + 1;  // also when G == 1: a later phase may need it
-            const uint4 *st = reinterpret_cast<const uint4 *>(sh.stages + (size_t)rp.s * sh.stage_bytes);
-            float *part = sh.part + ((size_t)ti.mat * kRowBlock + (size_t)(ti.r - blk0)) * kConsumerWarps + gwarp;
-            if (ti.R >= 4) {
-                for (int rb = 0; rb < nr; rb += 4) {
-                    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-                    const uint4 *rp0 = st + (size_t)min(rb + 0, nr - 1) * nvec, *rp1 = st + (size_t)min(rb + 1, nr - 1) * nvec;
-                    const uint4 *rp2 = st + (size_t)min(rb + 2, nr - 1) * nvec, *rp3 = st + (size_t)min(rb + 3, nr - 1) * nvec;
-                    if (have) {
-                        // The empty asm every fourth vector keeps the compiler from hoisting every load of
-                        // the tile to the top, which would need more registers than exist.
-#pragma unroll
-                        for (int j = 0; j < NXV; ++j) {
-                            const int v = min(gtid + T * j, vlast);
-                            const uint4 w0 = rp0[v], w1 = rp1[v], w2 = rp2[v], w3 = rp3[v];
-                            acc[0] = VecTraits<WT>::dot(w0, &xr[j * XQ], acc[0]);
-                            acc[1] = VecTraits<WT>::dot(w1, &xr[j * XQ], acc[1]);
-                            acc[2] = VecTraits<WT>::dot(w2, &xr[j * XQ], acc[2]);
-                            acc[3] = VecTraits<WT>::dot(w3, &xr[j * XQ], acc[3]);
-                            if ((j & 3) == 3) asm volatile("" ::: "memory");
-                        }
-                    }
-                    if (rb + 4 >= nr) {  // last block of the tile: the stage can go back to the producer
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive_cnt(&sh.empty[rp.s], G);  // the G-th share of the 4 arrivals
-                    }
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const float v = warp_sum(acc[i]);
-                        if (lane == 0 && rb + i < nr) part[(rb + i) * kConsumerWarps] = v;
-                    }
+            bool have = stage_use_seen(p, sh, rs, (int)use, 310 + g.kind);
+            have = have && mbar_wait(p, sh, &sh.full[rs], use & 1, 300 + g.kind);
+            if (have && lane == 0) sh.seen[rs] = (int)use + 1;
+            if (p.debug_flags & 4) have = false;  // debug: wait for the tiles but skip the arithmetic
+            const uint4 *st = reinterpret_cast<const uint4 *>(sh.stages + (size_t)rs * sh.stage_bytes);
+            float *part = sh.part + ((size_t)mat * kRowBlock + (size_t)(rrel - row0_blk)) * kConsumerWarps;
+            if (R >= 4) consume_tile<WT, 4>(p, sh, st, xs4, nvec, njl, lane, nr, have, part, rs, slot, cta);
+            else if (R >= 2) consume_tile<WT, 2>(p, sh, st, xs4, nvec, njl, lane, nr, have, part, rs, slot, cta);
+            else consume_tile<WT, 1>(p, sh, st, xs4, nvec, njl, lane, nr, have, part, rs, slot, cta);
+        }
+        // End of a row block: run the epilogue on the row sums and publish.
+        const int nrows = min(cend * R, nrows_cta) - row0_blk;
+        if (!consumer_bar_ok(sh.abort, sh.decision, tid, bk)) return false;
+        if (tid < nrows) {
+            const float tot = sh.part[(size_t)tid * kConsumerWarps];
+            const long row = ti.r0 + row0_blk + tid;
+            const uint32_t tag = phase_tag(p, ph);
+            switch (g.kind) {
+                case PH_QKV: st_tagged(p.qkvT + row, tot, tag); break;
+                case PH_O:      // h = x + attn_out                                   llama.rs:110
+                case PH_DOWN:   // out = h + mlp_out                                  llama.rs:115
+                    xres = __fadd_rn(xres, tot);  // (these phases have a single row block: see the launcher)
+                    st_tagged(p.xT + row, xres, tag);
+                    break;
+                case PH_GATEUP: {  // SiLU (activation.rs:143-146) then gate_act * up (llama.rs:61-63)
+                    const float up = sh.part[((size_t)kRowBlock + tid) * kConsumerWarps];
+                    const float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-tot)));
+                    st_tagged(p.actT + row, __fmul_rn(__fmul_rn(tot, sig), up), tag);
+                    break;
                 }
-            } else if (ti.R >= 2) {
-                for (int rb = 0; rb < nr; rb += 2) {
-                    float acc[2] = {0.f, 0.f};
-                    const uint4 *rp0 = st + (size_t)rb * nvec, *rp1 = st + (size_t)min(rb + 1, nr - 1) * nvec;
-                    if (have) {
-#pragma unroll
-                        for (int j = 0; j < NXV; ++j) {
-                            const int v = min(gtid + T * j, vlast);
-                            const uint4 w0 = rp0[v], w1 = rp1[v];
-                            acc[0] = VecTraits<WT>::dot(w0, &xr[j * XQ], acc[0]);
-                            acc[1] = VecTraits<WT>::dot(w1, &xr[j * XQ], acc[1]);
-                            if ((j & 7) == 7) asm volatile("" ::: "memory");
-                        }
-                    }
-                    if (rb + 2 >= nr) {
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive_cnt(&sh.empty[rp.s], G);
-                    }
-#pragma unroll
-                    for (int i = 0; i < 2; ++i) {
-                        const float v = warp_sum(acc[i]);
-                        if (lane == 0 && rb + i < nr) part[(rb + i) * kConsumerWarps] = v;
-                    }
-                }
-            } else {
-                // One row per tile (long rows): two accumulators keep the FMA chains short.
-                float a0 = 0.f, a1 = 0.f;
-                if (have) {
-#pragma unroll
-                    for (int j = 0; j < NXV; j += 2) {
-                        const uint4 w0 = st[min(gtid + T * j, vlast)];
-                        const uint4 w1 = st[min(gtid + T * (j + 1), vlast)];
-                        a0 = VecTraits<WT>::dot(w0, &xr[j * XQ], a0);
-                        a1 = VecTraits<WT>::dot(w1, &xr[(j + 1) * XQ], a1);
-                    }
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cnt(&sh.empty[rp.s], G);
-                const float v = warp_sum(a0 + a1);
-                if (lane == 0) part[0] = v;
+                default: p.logits[row] = tot; break;
             }
         }
-        rp.next(sh.S);
-        // End of a row block (or of the phase): reduce the per-warp partials, run the epilogue and publish.
-        const bool last_of_chunk = ti.mat == ti.nmat - 1;
-        const long next_r = ti.r + ti.R;
-        if (last_of_chunk && (next_r >= ti.r1 || next_r - blk0 >= rows_per_block)) {
-            const int nrows = (int)(min(next_r, ti.r1) - blk0);
-            if (!consumer_bar_ok(sh.abort, sh.decision, tid, bk)) return false;
-            if (tid < nrows) {
-                const float *p0 = sh.part + (size_t)tid * kConsumerWarps;
-                float tot = 0.f, tot1 = 0.f;
-#pragma unroll
-                for (int w = 0; w < WG; ++w) tot += p0[w];
-                if (g.nmat == 2) {
-#pragma unroll
-                    for (int w = 0; w < WG; ++w) tot1 += p0[(size_t)kRowBlock * kConsumerWarps + w];
-                }
-                const long row = blk0 + tid;
-                const uint32_t tag = phase_tag(p, ph);
-                switch (g.kind) {
-                    case PH_QKV: st_tagged(p.qkvT + row, tot, tag); break;
-                    case PH_O:      // h = x + attn_out                                   llama.rs:110
-                    case PH_DOWN:   // out = h + mlp_out                                  llama.rs:115
-                        xres = __fadd_rn(xres, tot);  // (these phases have a single row block: see the launcher)
-                        st_tagged(p.xT + row, xres, tag);
-                        break;
-                    case PH_GATEUP: {  // SiLU (activation.rs:143-146) then gate_act * up (llama.rs:61-63)
-                        const float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-tot)));
-                        st_tagged(p.actT + row, __fmul_rn(__fmul_rn(tot, sig), tot1), tag);
-                        break;
-                    }
-                    default: p.logits[row] = tot; break;
-                }
-            }
-            blk0 = next_r;
-            if (next_r < ti.r1) consumer_bar();  // the table is rewritten by the next block
-        }
+        if (cend < chunks) consumer_bar();  // the table is rewritten by the next block
     }
+    rp.n += (uint32_t)(chunks * nmat);
     if ((p.debug_flags & 1) && ti.r0 + tid < ti.r1) {  // debug (no tiles streamed): publish zeros so that the chain runs
         const uint32_t tag = phase_tag(p, ph);
         uint2 *dst = g.kind == PH_QKV ? p.qkvT : g.kind == PH_GATEUP ? p.actT : p.xT;
@@ -723,34 +749,6 @@ __device__ __forceinline__ bool gemv_phase(const MegaParams &p, Shared &sh, cons
     }
     trace_stamp(p, cta, tid, 3 * ph + 2);
     return true;
-}
-
-template <typename WT, int G>
-__device__ __forceinline__ bool gemv_phase_nxv(const MegaParams &p, Shared &sh, const Phase &g, long id, RingPos &rp, int cta,
-                                               int nctas, int tid, int &bk, int ph, float &xres, int need) {
-    if (need <= 4) return gemv_phase<WT, 4, G>(p, sh, g, id, rp, cta, nctas, tid, bk, ph, xres);
-    if (need <= 8) return gemv_phase<WT, 8, G>(p, sh, g, id, rp, cta, nctas, tid, bk, ph, xres);
-    if constexpr (VecTraits<WT>::XPV == 4) {
-        if (need > 12) return gemv_phase<WT, 16, G>(p, sh, g, id, rp, cta, nctas, tid, bk, ph, xres);
-    }
-    return gemv_phase<WT, 12, G>(p, sh, g, id, rp, cta, nctas, tid, bk, ph, xres);  // the launcher rejects more
-}
-
-// Picks the number of warp groups: the most groups whose threads still hold their input slice in
-// registers (<= 16 vectors per thread for f32 weights, <= 8 preferred for bf16 whose vectors are twice
-// as wide in x).
-template <typename WT>
-__device__ __forceinline__ bool gemv_phase_dispatch(const MegaParams &p, Shared &sh, const Phase &g, long id, RingPos &rp, int cta,
-                                                    int nctas, int tid, int &bk, int ph, float &xres) {
-    constexpr int XPV = VecTraits<WT>::XPV;
-    constexpr int kPrefer = XPV == 4 ? 16 : 8;
-    const int nvec = g.K / XPV;
-    const int need4 = (nvec + kConsumers / 4 - 1) / (kConsumers / 4);
-    const int need2 = (nvec + kConsumers / 2 - 1) / (kConsumers / 2);
-    const int need1 = (nvec + kConsumers - 1) / kConsumers;
-    if (need4 <= kPrefer) return gemv_phase_nxv<WT, 4>(p, sh, g, id, rp, cta, nctas, tid, bk, ph, xres, need4);
-    if (need2 <= kPrefer) return gemv_phase_nxv<WT, 2>(p, sh, g, id, rp, cta, nctas, tid, bk, ph, xres, need2);
-    return gemv_phase_nxv<WT, 1>(p, sh, g, id, rp, cta, nctas, tid, bk, ph, xres, need1);
 }
 
 // Sink of an attention work item in the persistent kernel: tagged record {max}, {sum}, ctx[D].
@@ -851,17 +849,17 @@ __device__ __forceinline__ void consumer_loop(const MegaParams &p, Shared &sh, i
         if (r0 + tid < r1) xres = embed_elem(p, id, (int)(r0 + tid));
     }
     const int nphases = 5 * p.L + 1;
-    RingPos rp{0, 0};
+    RingPos rp{0};
     int bk = 0;
     for (int ph = 0; ph < nphases; ++ph) {
-        const Phase g = get_phase(p, ph);
+        const Phase g = get_phase(p, p.layers, ph);
         trace_stamp(p, cta, tid, 3 * ph);
         if (g.kind == PH_ATT) {
             if (!attention_phase(p, sh, g.layer, ph, past, cta, nctas, tid, bk)) return;
             trace_stamp(p, cta, tid, 3 * ph + 1);
             trace_stamp(p, cta, tid, 3 * ph + 2);
         } else {
-            if (!gemv_phase_dispatch<WT>(p, sh, g, id, rp, cta, nctas, tid, bk, ph, xres)) return;
+            if (!gemv_phase<WT>(p, sh, g, id, rp, cta, nctas, tid, bk, ph, xres)) return;
         }
     }
     trace_stamp(p, cta, tid, 3 * nphases);
@@ -887,8 +885,9 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const __grid_c
     sh.stage_bytes = p.stage_bytes;
     sh.stages = smem_raw;
     float *fl = reinterpret_cast<float *>(smem_raw + (size_t)p.stages * p.stage_bytes);
-    sh.part = fl;
-    sh.red = sh.part + mega_table_floats(max(p.H, max(p.qd, p.I)));
+    sh.xs = fl;
+    sh.part = fl + mega_xs_floats(max(p.H, max(p.qd, p.I)));
+    sh.red = fl + mega_table_floats(max(p.H, max(p.qd, p.I)));
     sh.attn = sh.red + kConsumerWarps;
     sh.full = bars;
     sh.empty = bars + kMegaMaxStages;
@@ -909,7 +908,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const __grid_c
     __syncthreads();
     const int cta = blockIdx.x, nctas = gridDim.x;
     if (tid >= kConsumers) {
-        if (tid == kConsumers) producer_loop(p, sh, cta, nctas, (int)sizeof(WT));
+        producer_loop(p, sh, cta, tid - kConsumers);
     } else {
         consumer_loop<WT>(p, sh, cta, nctas, tid);
     }
@@ -923,6 +922,43 @@ size_t decode_mega_smem_bytes(int stages, int stage_bytes, int head_dim, int kma
 }
 
 int decode_mega_max_splits() { return kMaxSplit; }
+
+int decode_mega_debug_flags() {
+    static const int flags = [] {
+        const char *e = getenv("LUMEN_MEGA_DEBUG");
+        return e ? atoi(e) : 0;
+    }();
+    return flags;
+}
+
+void decode_mega_build_schedule(const MegaParams &p_in, const MegaLayer *host_layers, int grid, std::vector<uint4> &entries,
+                                std::vector<int> &counts, int &stride) {
+    MegaParams p = p_in;
+    p.debug_flags = decode_mega_debug_flags();
+    const int esz = p.wbf16 ? 2 : 4, nphases = 5 * p.L + 1;
+    std::vector<std::vector<uint4>> per(grid);
+    for (int cta = 0; cta < grid; ++cta) {
+        for (int ph = 0; ph < nphases; ++ph) {
+            const Phase g = get_phase(p, host_layers, ph);
+            if (g.kind == PH_ATT) continue;
+            for (TileIter ti(g, esz, kMegaStageBytes, cta, grid, (p.debug_flags & 1) != 0); ti.valid(); ti.advance()) {
+                // whole rows are one contiguous block: one copy per tile
+                const unsigned long long a = (unsigned long long)(uintptr_t)((ti.mat == 0 ? g.w0 : g.w1) + (size_t)ti.r * ti.rowbytes);
+                const uint32_t tile_bytes = (uint32_t)ti.rows() * (uint32_t)ti.rowbytes;
+                per[cta].push_back(make_uint4((uint32_t)a, (uint32_t)(a >> 32), tile_bytes | ((uint32_t)ph << 16), tile_bytes));
+            }
+        }
+    }
+    size_t mx = 1;
+    for (auto &v : per) mx = std::max(mx, v.size());
+    stride = (int)((mx + 31) / 32 * 32);
+    entries.assign((size_t)grid * stride, make_uint4(0u, 0u, 0u, 0u));
+    counts.resize(grid);
+    for (int cta = 0; cta < grid; ++cta) {
+        counts[cta] = (int)per[cta].size();
+        std::copy(per[cta].begin(), per[cta].end(), entries.begin() + (size_t)cta * stride);
+    }
+}
 unsigned int decode_mega_epochs_per_launch(int layers) { return 5u * (unsigned)layers + 2u; }
 
 size_t decode_mega_exchange_words(const MegaParams &p) {
@@ -937,9 +973,8 @@ int decode_mega_supported(const MegaParams &p, char *why, size_t why_len) {
             snprintf(why, why_len, "row of %d elements is not a multiple of 16 bytes", k);
             return 0;
         }
-        const int nvec = k * esz / 16;
-        if ((nvec + kConsumers - 1) / kConsumers > (p.wbf16 ? 12 : 16)) {
-            snprintf(why, why_len, "K=%d too large for the register-resident input slice", k);
+        if (k * esz > kMegaStageBytes) {
+            snprintf(why, why_len, "a row of %d elements does not fit one %d-byte ring stage", k, kMegaStageBytes);
             return 0;
         }
     }
@@ -961,17 +996,18 @@ int launch_decode_mega(lumen_ctx *ctx, MegaParams &p, cudaStream_t s) {
         return set_error(ctx, LUMEN_ERR_UNSUPPORTED, "hidden size %d needs more than %d rows per CTA", p.H, kRowBlock);
     // Ring geometry: 32 KB stages (a row of every supported matrix fits), as many as fit beside the
     // scratch areas in the 227 KB a CTA may use.
-    p.stage_bytes = 32 * 1024;
+    p.stage_bytes = kMegaStageBytes;
     const int kmax = std::max(p.H, std::max(p.qd, p.I));
     const size_t budget = 227 * 1024 - 1024;  // static shared (barriers, flags) and alignment slack
     int stages = kMegaMaxStages;
     while (stages > 2 && decode_mega_smem_bytes(stages, p.stage_bytes, p.D, kmax) > budget) --stages;
     p.stages = stages;
-    // L2 look-ahead of the producer, in tiles per CTA (6 x 32 KB x 148 CTAs = 28 MB of the 126 MB L2).
-    p.l2_ahead = 6;
-    p.debug_flags = 0;
-    if (const char *e = getenv("LUMEN_MEGA_DEBUG")) p.debug_flags = atoi(e);
-    if (const char *e = getenv("LUMEN_MEGA_L2_AHEAD")) p.l2_ahead = std::max(0, std::min(64, atoi(e)));
+    p.debug_flags = decode_mega_debug_flags();
+    // L2 look-ahead of the producer in copies per CTA, counted from the copy being issued (the ring itself
+    // holds `stages` of them): 0 = off, at most 56.
+    p.l2_ahead = 8;  // measured: +2 % at 8, no gain at 12, a loss from 20 on (the look-ahead competes with the exchanges)
+    if (const char *e = getenv("LUMEN_MEGA_L2_AHEAD")) p.l2_ahead = std::max(0, std::min(56, atoi(e)));
+    if (!p.sched || !p.sched_count) return set_error(ctx, LUMEN_ERR_INVALID, "persistent decode kernel: no producer schedule");
     const size_t smem = decode_mega_smem_bytes(stages, p.stage_bytes, p.D, kmax);
     if (smem > budget) return set_error(ctx, LUMEN_ERR_UNSUPPORTED, "shared memory: %zu bytes needed", smem);
     const void *kern = p.wbf16 ? (const void *)decode_mega_kernel<__nv_bfloat16> : (const void *)decode_mega_kernel<float>;

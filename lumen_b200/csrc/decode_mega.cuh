@@ -6,6 +6,7 @@
 namespace lumen {
 
 constexpr int kMegaMaxStages = 7;
+constexpr int kMegaStageBytes = 32 * 1024;  // one ring stage: a row (or row segment) of every supported matrix fits
 
 struct MegaLayer {
     const char *wqkv, *wo, *wgate, *wup, *wdown;  // [rows, K] row-major, f32 or bf16
@@ -37,11 +38,28 @@ struct MegaParams {
     int *abort_flag;
     DeviceStatus *status;
     int stages, stage_bytes;            // filled by the launcher
-    // Optional trace: CTA 0 stores a nanosecond timestamp at the start of each phase, after its prologue
-    // and after its last tile (3 per phase), then one at the end.  Null = off.
+    // Optional trace written by CTA 0 (null = off); decode_mega_trace_words() 64-bit words, nph = 5L+1:
+    //   [0, 3nph]        ns timestamps: start of each phase, after its prologue, after its last tile; then
+    //                    one at the end of the token
+    //   [3nph+1, +nph)   producer: ns timestamp of the first copy of each phase
+    //   [4nph+1, +nph)   consumers: ns timestamp when the phase's input vector had arrived
+    //   [5nph+1, +nph)   warp 0: clock cycles spent waiting for weight tiles of the phase
+    //   [6nph+1, +nph)   warp 0: clock cycles spent on the tiles of the phase (loads, FMAs, reductions)
+    //   [7nph+1, +512)   producer: ns timestamp of the issue of each of the first 512 tiles
+    //   [7nph+513, +512) consumers: ns timestamp of the release of each of those tiles
     unsigned long long *trace;
-    int l2_ahead;  // tiles the producer's L2 prefetch cursor runs ahead of the shared-memory ring
-    int debug_flags;  // bit 0: stream no weight tiles (measures the sync + prologue chain alone; results are wrong)
+    // Producer schedule: for CTA c the bulk copies of one token in issue order, sched[c * sched_stride + i],
+    // i < sched_count[c].  Entry = {src address lo, hi, copy bytes | phase << 16, tile bytes}; tile bytes is
+    // non-zero on the first copy of a tile (= the transaction count of its stage) and 0 on the following ones.
+    // The schedule depends only on the model's shapes and addresses, so it is built once on the host
+    // (decode_mega_build_schedule) and the producer does no address arithmetic at all.
+    const uint4 *sched;
+    const int *sched_count;
+    int sched_stride;
+    int l2_ahead;  // copies the producer's L2 prefetch runs ahead of the copy it issues (0 = off)
+    // bit 0: stream no weight tiles (measures the exchange + prologue chain alone; results are wrong)
+    // bit 2: wait for the weight tiles but skip the arithmetic on them
+    int debug_flags;
 };
 
 size_t decode_mega_smem_bytes(int stages, int stage_bytes, int head_dim, int kmax);
@@ -49,6 +67,13 @@ int decode_mega_supported(const MegaParams &p, char *why, size_t why_len);
 unsigned int decode_mega_epochs_per_launch(int layers);
 size_t decode_mega_exchange_words(const MegaParams &p);  // uint2 words of the four exchange buffers
 int decode_mega_max_splits();
+constexpr int kMegaTileTrace = 512;
+inline size_t decode_mega_trace_words(size_t layers) { return 7 * (5 * layers + 1) + 1 + 2 * kMegaTileTrace; }
+int decode_mega_debug_flags();  // from the environment (LUMEN_MEGA_DEBUG), read once
+// Builds the producer schedule for `grid` CTAs from the shapes in p and the HOST copy of the layer table.
+// entries.size() == grid * stride afterwards.
+void decode_mega_build_schedule(const MegaParams &p, const MegaLayer *host_layers, int grid, std::vector<uint4> &entries,
+                                std::vector<int> &counts, int &stride);
 int launch_decode_mega(lumen_ctx *ctx, MegaParams &p, cudaStream_t s);
 
 }  // namespace lumen

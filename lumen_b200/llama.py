@@ -114,12 +114,21 @@ class LlamaModel:
             self.set_param(name, value)
 
     def decode_trace(self) -> np.ndarray:
-        """Phase timestamps (ns) of the last persistent decode step; needs LUMEN_DECODE_TRACE=1."""
-        n = 4 * (5 * self.config.num_hidden_layers + 1) + 1 + 1024
+        """Device trace of the last persistent decode step (needs LUMEN_DECODE_TRACE=1 when the model is
+        created).  With nph = 5 * layers + 1 phases (qkv, attention, o, gate/up, down per layer, then lm_head):
+        `stamps` [nph, 3] ns at phase start / after its prologue / after its last tile, `end` ns,
+        `producer` [nph] ns of the phase's first copy, `input_ready` [nph] ns, `wait_cycles` and
+        `busy_cycles` [nph] of consumer warp 0 on weight tiles, `tile_issue` and `tile_release` [512] ns."""
+        nph = 5 * self.config.num_hidden_layers + 1
+        n = 7 * nph + 1 + 1024
         buf = (C.c_uint64 * n)()
         got = C.c_size_t()
         self.ctx.check(self.ctx._lib.lumen_llama_decode_trace(self.h, buf, n, C.byref(got)))
-        return np.frombuffer(buf, dtype=np.uint64, count=got.value).copy()
+        a = np.frombuffer(buf, dtype=np.uint64, count=got.value).astype(np.int64)
+        return {"stamps": a[:3 * nph].reshape(nph, 3), "end": int(a[3 * nph]),
+                "producer": a[3 * nph + 1:4 * nph + 1], "input_ready": a[4 * nph + 1:5 * nph + 1],
+                "wait_cycles": a[5 * nph + 1:6 * nph + 1], "busy_cycles": a[6 * nph + 1:7 * nph + 1],
+                "tile_issue": a[7 * nph + 1:7 * nph + 513], "tile_release": a[7 * nph + 513:]}
 
     @property
     def weight_bytes_per_step(self) -> int:
