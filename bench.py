@@ -100,8 +100,8 @@ class ClockSampler(threading.Thread):
 
 
 # dram__bytes_read + dram__bytes_write of one persistent-kernel launch divided by its algorithmic bytes,
-# from the ncu capture summarised in profiles/decode_mega_kernel_tinyllama_f32.md (976.5 MB / 967.3 MB).
-MEGA_TRAFFIC_RATIO = 1.0095
+# from the ncu capture summarised in profiles/decode_mega_kernel_tinyllama_f32.md (973.0 MB / 967.3 MB).
+MEGA_TRAFFIC_RATIO = 1.006
 
 
 def tinyllama_cfg(dtype: str, max_seq: int, layers: int = 0):
