@@ -172,6 +172,99 @@ def run_reference(args):
     return 0
 
 
+GEMV_SWEEP = [(2048, 2048), (2048, 256), (2048, 5632), (5632, 2048), (2048, 32000), (4096, 11008), (11008, 4096)]
+ATTN_SWEEP = [(1, 128), (1, 512), (1, 2048), (1, 8192), (16, 128), (16, 512), (16, 2048), (16, 8192)]
+
+
+def _event_time_ms(ctx, stream, fn, iters: int, warm: int = 3) -> float:
+    import torch
+    for _ in range(warm):
+        fn()
+    ctx.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(iters):
+        fn()
+    e1.record(stream)
+    ctx.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def run_micro(args):
+    """Secondary measurements (BASELINE configs 2 and 3): the standalone vector-matrix product over the
+    sweep of shapes, and decode attention over a static KV cache.  One JSON line per case; the working set
+    is rotated over several copies so that it exceeds L2 whenever that takes at most 64 copies."""
+    import torch
+    import lumen_b200 as L
+    torch.cuda.set_device(0)
+    ctx = L.Context(0)
+    stream = torch.cuda.ExternalStream(ctx.stream, device=torch.device("cuda", 0))
+    peak, peak_kind = measured_hbm_peak()
+    rng = np.random.default_rng(2)
+    if args.micro == "gemv":
+        for k, n in GEMV_SWEEP:
+            x = L.Tensor.from_array_no_grad(rng.standard_normal(k, dtype=np.float32), ctx)
+            y = L.Tensor.from_array_no_grad(np.zeros(n, np.float32), ctx)
+            w_nk = rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02)
+            for dt in ("f32", "bf16"):
+                esz = 4 if dt == "f32" else 2
+                copies = int(min(64, max(2, -(-300e6 // (k * n * esz)))))
+                for layout in ("nk", "kn"):
+                    w_host = w_nk if layout == "nk" else np.ascontiguousarray(w_nk.T)
+                    ws = [(L.Tensor.from_bf16(w_host, ctx) if dt == "bf16" else L.Tensor.from_array_no_grad(w_host, ctx))
+                          for _ in range(copies)]
+                    state = {"i": 0}
+
+                    def step():
+                        w = ws[state["i"] % copies]
+                        state["i"] += 1
+                        L.gemv(ctx, x.data_ptr, w.data_ptr, L.BF16 if dt == "bf16" else L.F32, layout == "kn", k, n, y.data_ptr)
+
+                    ms = _event_time_ms(ctx, stream, step, iters=max(20, 3 * copies))
+                    nbytes = esz * k * n + 4 * k + 4 * n
+                    gbs = nbytes / (ms * 1e-3) / 1e9
+                    print(json.dumps({"micro": "gemv", "k": k, "n": n, "weights": dt, "layout": layout, "us": ms * 1e3,
+                                      "algorithmic_bytes": nbytes, "gbs": gbs, "frac_of_measured_peak": gbs / peak,
+                                      "peak_kind": peak_kind, "working_set_mb": copies * k * n * esz / 1e6}), flush=True)
+                    del ws
+    else:
+        hq, hkv, d = 32, 4, 64
+        for b, ctx_len in ATTN_SWEEP:
+            iters = 20
+            kv_bytes = b * hkv * ctx_len * d * 4 * 2
+            copies = int(min(16, max(1, -(-300e6 // kv_bytes))))
+            max_seq = ctx_len + iters + 8
+            rope = L.RotaryEmbedding(d, max_seq, 10000.0, ctx)
+            caches = []
+            for _ in range(copies):
+                c = L.KVCacheInner(b, hkv, max_seq, d, ctx)
+                kk = rng.standard_normal((b, hkv, max_seq, d), dtype=np.float32)
+                vv = rng.standard_normal((b, hkv, max_seq, d), dtype=np.float32)
+                c.write(kk, vv, ctx_len)
+                caches.append(c)
+            q = L.Tensor.from_array_no_grad(rng.standard_normal((b, hq, d), dtype=np.float32), ctx)
+            kn = L.Tensor.from_array_no_grad(rng.standard_normal((b, hkv, d), dtype=np.float32), ctx)
+            vn = L.Tensor.from_array_no_grad(rng.standard_normal((b, hkv, d), dtype=np.float32), ctx)
+            out = L.Tensor.from_array_no_grad(np.zeros((b, hq, d), np.float32), ctx)
+            state = {"i": 0}
+            per_cache = (3 + iters) // copies + 1  # calls each cache receives (each appends one row)
+
+            def step():
+                c = caches[state["i"] % copies]
+                state["i"] += 1
+                L.attention_decode(ctx, q.data_ptr, kn.data_ptr, vn.data_ptr, hq, c, rope, out.data_ptr)
+
+            assert per_cache <= iters + 8
+            ms = _event_time_ms(ctx, stream, step, iters=iters)
+            nbytes = kv_bytes + b * hq * d * 8 + b * hkv * d * 8
+            gbs = nbytes / (ms * 1e-3) / 1e9
+            print(json.dumps({"micro": "attention_decode", "batch": b, "context": ctx_len, "us": ms * 1e3,
+                              "algorithmic_bytes": nbytes, "gbs": gbs, "frac_of_measured_peak": gbs / peak,
+                              "peak_kind": peak_kind, "working_set_mb": copies * kv_bytes / 1e6}), flush=True)
+            del caches
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -184,8 +277,13 @@ def main():
     ap.add_argument("--profile-layers", type=int, default=0,
                     help="profiling aid: truncate the model to this many layers so that a profiler capture stays "
                          "small; the printed line is then marked and is not a benchmark value")
+    ap.add_argument("--micro", choices=["gemv", "attn"], default=None,
+                    help="secondary measurements instead of the decode benchmark: the vector-matrix sweep or "
+                         "decode attention over a static cache (one JSON line per case)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.micro:
+        return run_micro(args)
     if args.impl == "reference":
         return run_reference(args)
 
