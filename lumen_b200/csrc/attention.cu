@@ -173,11 +173,22 @@ size_t attn_decode_scratch_bytes(size_t B, size_t Hq, size_t D, int max_splits) 
 }
 
 int attn_decode_pick_splits(size_t B, size_t Hkv, size_t len, int num_sms) {
-    // Enough CTAs to cover the SMs about twice, but at least 64 rows per split.
-    size_t base = std::max<size_t>(1, B * Hkv);
-    size_t want = ((size_t)num_sms * 2 + base - 1) / base;
-    size_t by_len = std::max<size_t>(1, (len + 63) / 64);
-    return (int)std::max<size_t>(1, std::min<size_t>(std::min(want, by_len), 64));
+    // The grid is (B * Hkv) x splits CTAs and an SM holds about one of them (the 8-head kernel uses the
+    // whole register file), so the step takes waves x rows-per-split: pick the split count that minimises
+    // that product (plus a fixed cost per wave for staging q and merging), with at least 64 rows per split.
+    const size_t base = std::max<size_t>(1, B * Hkv);
+    const size_t max_ns = std::max<size_t>(1, std::min<size_t>(64, (len + 63) / 64));
+    size_t best = 1, best_cost = ~(size_t)0;
+    for (size_t ns = 1; ns <= max_ns; ++ns) {
+        const size_t waves = (base * ns + (size_t)num_sms - 1) / (size_t)num_sms;
+        const size_t rows = (len + ns - 1) / ns;
+        const size_t cost = waves * (rows + 48);
+        if (cost < best_cost) {
+            best_cost = cost;
+            best = ns;
+        }
+    }
+    return (int)best;
 }
 
 int launch_attn_decode(lumen_ctx *ctx, const AttnDecodeArgs &a, cudaStream_t s) {

@@ -114,8 +114,38 @@ struct DecodeParams {
     int nsplit;
 };
 
+// Rows of K and V a warp keeps in flight, as a function of the elements per lane NI = ceil(D / 32).
+__host__ __device__ constexpr int attn_rows_in_flight(int NI) { return NI <= 2 ? 8 : (NI == 4 ? 4 : 2); }
+
 __host__ __device__ inline size_t attn_decode_smem_floats(int GT, int D, int warps = kAttnWarps) {
-    return (size_t)GT * D + D + 2 * warps * GT + (size_t)warps * GT * D;
+    // q heads, rotated new k, per-warp (max, sum), per-warp ctx, per-warp softmax weights of one chunk + rescale factors
+    return (size_t)GT * D + D + 2 * warps * GT + (size_t)warps * GT * D + (size_t)warps * (8 * GT + GT);
+}
+
+// Sums NV values over the 32 lanes at once: at every step a lane keeps half of the values it still
+// carries and trades the other half with its partner, so NV = 64 costs 62 shuffles instead of 320.
+// Afterwards a lane holds the complete sums of values [idx0, idx0 + max(1, NV/32)), idx0 =
+// NV >= 32 ? lane * (NV/32) : lane / (32/NV), in a[0..].
+template <int NV>
+__device__ __forceinline__ void attn_reduce_multi(float (&a)[NV], int lane) {
+    int n = NV;
+#pragma unroll
+    for (int bit = 16; bit > 0; bit >>= 1) {
+        if (n > 1) {
+            const bool up = (lane & bit) != 0;
+#pragma unroll
+            for (int i = 0; i < NV / 2; ++i) {
+                if (i < n / 2) {
+                    const float send = up ? a[i] : a[i + n / 2];
+                    const float keep = up ? a[i + n / 2] : a[i];
+                    a[i] = keep + __shfl_xor_sync(0xffffffffu, send, bit);
+                }
+            }
+            n >>= 1;
+        } else {
+            a[0] += __shfl_xor_sync(0xffffffffu, a[0], bit);
+        }
+    }
 }
 
 // Default sink of an item's result: the plain partial arrays of DecodeParams.
@@ -153,6 +183,7 @@ __device__ __forceinline__ void attn_decode_item(const DecodeParams &p, float *s
     float *wm = knew + D;                    // [warps][GT]
     float *wl = wm + NW * GT;        // [warps][GT]
     float *wctx = wl + NW * GT;      // [warps][GT][D]
+    float *wsoft = wctx + (size_t)NW * GT * D;  // [warps][UN*GT + GT] softmax weights of a chunk, then rescale factors
 
     const int lane = tid & 31, warp = tid >> 5;
     const int G = p.Hq / p.Hkv;
@@ -170,10 +201,12 @@ __device__ __forceinline__ void attn_decode_item(const DecodeParams &p, float *s
     const float *kbase = p.k_cache + ((size_t)b * p.Hkv + hk) * p.max_seq * D;
     const float *vbase = p.v_cache + ((size_t)b * p.Hkv + hk) * p.max_seq * D;
 
-    constexpr int UN = NI <= 2 ? 8 : (NI == 4 ? 4 : 2);  // rows whose K and V loads are in flight together
-    float kr[UN][NI], vr[UN][NI];
+    constexpr int UN = attn_rows_in_flight(NI);  // rows whose K and V loads are in flight together
+    // Two register buffers of UN rows each: the loads of the next chunk are issued before the arithmetic
+    // of the current one, so a warp always has a chunk in flight.
+    float kra[UN][NI], vra[UN][NI], krb[UN][NI], vrb[UN][NI];
     // Rows other than `past` come from the cache (row `past` is patched in from shared memory later).
-    auto load_chunk = [&](int jb) {
+    auto load_chunk = [&](int jb, float (&kr)[UN][NI], float (&vr)[UN][NI]) {
 #pragma unroll
         for (int u = 0; u < UN; ++u) {
             const int j = jb + u;
@@ -187,7 +220,7 @@ __device__ __forceinline__ void attn_decode_item(const DecodeParams &p, float *s
         }
     };
     int jb = j0 + warp * UN;
-    if (jb < j1) load_chunk(jb);
+    if (jb < j1) load_chunk(jb, kra, vra);
     stage();
 
     // Stage and rotate the GT query heads (one warp per head, round robin).
@@ -214,11 +247,23 @@ __device__ __forceinline__ void attn_decode_item(const DecodeParams &p, float *s
     }
     bar();
 
-    float q[GT][NI], ctx[GT][NI], m[GT], l[GT];
+    // A chunk of UN rows x GT heads is handled at once: the UN*GT dot products are summed across the lanes
+    // by one butterfly, after which each score lives in one lane (value g*UN + u in lane idx0 .. ), the
+    // lanes of a head (GS of them) agree on the chunk's maximum with log2(GS) shuffles, every lane
+    // exponentiates only the scores it holds, and the weights reach all lanes through shared memory for the
+    // P.V update.  Same online softmax as the reference's row-by-row form up to rounding.
+    constexpr int NV = UN * GT;
+    constexpr int HELD = NV >= 32 ? NV / 32 : 1;  // scores a lane holds after the butterfly
+    constexpr int DUP = NV >= 32 ? 1 : 32 / NV;   // lanes that hold the same score
+    constexpr int GS = 32 / GT;                   // lanes that hold scores of the same head
+    const int idx0 = NV >= 32 ? lane * HELD : lane / DUP;
+    const int g_l = idx0 / UN;                    // the head whose running (max, sum) this lane carries
+    const bool canonical = (lane % DUP) == 0;
+    float *ws = wsoft + (size_t)warp * (NV + GT);
+    float q[GT][NI], ctx[GT][NI];
+    float m_h = -INFINITY, l_h = 0.f;
 #pragma unroll
     for (int g = 0; g < GT; ++g) {
-        m[g] = -INFINITY;
-        l[g] = 0.f;
 #pragma unroll
         for (int i = 0; i < NI; ++i) {
             int e = lane + 32 * i;
@@ -227,7 +272,7 @@ __device__ __forceinline__ void attn_decode_item(const DecodeParams &p, float *s
         }
     }
 
-    while (jb < j1) {
+    auto do_chunk = [&](int jb, float (&kr)[UN][NI], float (&vr)[UN][NI]) {
         if (past >= jb && past < jb + UN) {  // the row appended by this step: use the staged copies
             const int u_new = past - jb;
 #pragma unroll
@@ -242,36 +287,75 @@ __device__ __forceinline__ void attn_decode_item(const DecodeParams &p, float *s
                 }
             }
         }
+        float d[NV];
 #pragma unroll
-        for (int u = 0; u < UN; ++u) {
-            if (jb + u >= j1) break;
+        for (int g = 0; g < GT; ++g) {
 #pragma unroll
-            for (int g = 0; g < GT; ++g) {
+            for (int u = 0; u < UN; ++u) {
                 float dot = 0.f;
 #pragma unroll
                 for (int i = 0; i < NI; ++i) dot = fmaf(q[g][i], kr[u][i], dot);
-                dot = attn_warp_sum(dot);
-                const float sc = __fmul_rn(dot, p.scale);
-                const float mn = fmaxf(m[g], sc);
-                const float r = expf(m[g] - mn);  // exp(-inf) = 0 on the first row
-                const float w = expf(sc - mn);
-                l[g] = fmaf(l[g], r, w);
-#pragma unroll
-                for (int i = 0; i < NI; ++i) ctx[g][i] = fmaf(w, vr[u][i], ctx[g][i] * r);
-                m[g] = mn;
+                d[g * UN + u] = dot;
             }
         }
-        jb += NW * UN;
-        if (jb < j1) load_chunk(jb);
+        attn_reduce_multi<NV>(d, lane);
+        float sc[HELD];
+        float cmax = -INFINITY;
+#pragma unroll
+        for (int k = 0; k < HELD; ++k) {
+            const int u = (idx0 + k) % UN;
+            sc[k] = (jb + u < j1) ? __fmul_rn(d[k], p.scale) : -INFINITY;  // rows past the range weigh nothing
+            cmax = fmaxf(cmax, sc[k]);
+        }
+#pragma unroll
+        for (int b2 = 1; b2 < GS; b2 <<= 1) cmax = fmaxf(cmax, __shfl_xor_sync(0xffffffffu, cmax, b2));
+        const float mn = fmaxf(m_h, cmax);  // finite: the chunk's first row is always inside the range
+        const float r = expf(m_h - mn);     // exp(-inf) = 0 on the first chunk
+        float wsum = 0.f;
+#pragma unroll
+        for (int k = 0; k < HELD; ++k) {
+            const float w = expf(sc[k] - mn);
+            if (canonical) ws[idx0 + k] = w;
+            wsum += w;
+        }
+        l_h = fmaf(l_h, r, canonical ? wsum : 0.f);
+        m_h = mn;
+        if ((lane & (GS - 1)) == 0) ws[NV + g_l] = r;
+        __syncwarp();
+#pragma unroll
+        for (int g = 0; g < GT; ++g) {
+            const float rg = ws[NV + g];
+#pragma unroll
+            for (int i = 0; i < NI; ++i) ctx[g][i] *= rg;
+#pragma unroll
+            for (int u = 0; u < UN; ++u) {
+                const float w = ws[g * UN + u];
+#pragma unroll
+                for (int i = 0; i < NI; ++i) ctx[g][i] = fmaf(w, vr[u][i], ctx[g][i]);
+            }
+        }
+        __syncwarp();  // the weights are overwritten by the next chunk
+    };
+    constexpr int kStep = NW * UN;
+    while (jb < j1) {
+        if (jb + kStep < j1) load_chunk(jb + kStep, krb, vrb);
+        do_chunk(jb, kra, vra);
+        jb += kStep;
+        if (jb >= j1) break;
+        if (jb + kStep < j1) load_chunk(jb + kStep, kra, vra);
+        do_chunk(jb, krb, vrb);
+        jb += kStep;
     }
 
-    // Merge the warps of this item.
+    // Merge the warps of this item.  The running sum of a head is spread over its GS lanes.
+#pragma unroll
+    for (int b2 = 1; b2 < GS; b2 <<= 1) l_h += __shfl_xor_sync(0xffffffffu, l_h, b2);
+    if ((lane & (GS - 1)) == 0) {
+        wm[warp * GT + g_l] = m_h;
+        wl[warp * GT + g_l] = l_h;
+    }
 #pragma unroll
     for (int g = 0; g < GT; ++g) {
-        if (lane == 0) {
-            wm[warp * GT + g] = m[g];
-            wl[warp * GT + g] = l[g];
-        }
 #pragma unroll
         for (int i = 0; i < NI; ++i) {
             int e = lane + 32 * i;
