@@ -88,6 +88,7 @@ struct lumen_llama {
     const void *mega_key = nullptr;  // first cache's k pointer the layer table was built for
     unsigned long long *d_trace = nullptr;  // phase timestamps of the last persistent step (LUMEN_DECODE_TRACE=1)
     uint2 *d_exchange = nullptr;            // tagged activation exchange buffers of the persistent kernel
+    void *x_peers[8] = {nullptr};           // every rank's d_exchange as seen from this device (tensor parallelism)
 };
 
 namespace {
@@ -340,20 +341,30 @@ int run_mega(lumen_llama *m, lumen_kv_cache **caches) {
     p.cos_t = m->cos_t; p.sin_t = m->sin_t;
     p.eps = m->cfg.rms_norm_eps;
     p.scale = 1.0f / sqrtf((float)m->D);
-    p.ids = w.ids; p.logits = w.logits;
-    // Exchange buffers of tagged words (zeroed once; tag 0 is never used).
+    const bool tp = ctx->tp_size > 1;
+    p.tp_rank = ctx->tp_rank; p.tp_size = ctx->tp_size;
+    p.x_slot_words = (p.H + 1) & ~1;
+    // A rank computes its slice of the vocabulary; the slices are gathered after the kernel.
+    p.ids = w.ids;
+    p.logits = tp ? w.logits_local + (size_t)ctx->tp_rank * m->vocab_l : w.logits;
+    // Exchange buffers of tagged words (zeroed once; tag 0 is never used).  With tensor parallelism the x
+    // buffers at their start are written by every rank: the ranks map each other's buffer once.
     const size_t words = decode_mega_exchange_words(p);
     if (!m->d_exchange) {
         LUMEN_CUDA(ctx, cudaMalloc(&m->d_exchange, words * sizeof(uint2)));
         LUMEN_CUDA(ctx, cudaMemsetAsync(m->d_exchange, 0, words * sizeof(uint2), ctx->stream));
+        LUMEN_TRY(tp_share_buffer(ctx, m->d_exchange, m->x_peers));  // (collective: also orders the memsets)
     }
     const unsigned int per_launch = decode_mega_epochs_per_launch(p.L);
     if (ctx->mega_epoch > 0xf0000000u - per_launch) {  // tags are about to wrap: start over from clean buffers
         LUMEN_CUDA(ctx, cudaMemsetAsync(m->d_exchange, 0, words * sizeof(uint2), ctx->stream));
+        // no rank may write into a peer's buffer before that peer has cleared it
+        if (tp) LUMEN_TRY(tp_allreduce_sum(ctx, w.logits_local, 1, ctx->stream));
         ctx->mega_epoch = 1;
     }
     p.xT = m->d_exchange;
-    p.qkvT = p.xT + ((p.H + 1) & ~1);
+    for (int r = 0; r < ctx->tp_size; ++r) p.x_peer[r] = static_cast<uint2 *>(m->x_peers[r]);
+    p.qkvT = p.xT + decode_mega_x_words(p);
     p.actT = p.qkvT + ((p.qkv_rows + 1) & ~1);
     p.partT = p.actT + ((p.I + 1) & ~1);
     p.epoch_base = ctx->mega_epoch;
@@ -367,11 +378,17 @@ int run_mega(lumen_llama *m, lumen_kv_cache **caches) {
     p.trace = m->d_trace;
     LUMEN_TRY(launch_decode_mega(ctx, p, ctx->stream));
     ctx->mega_epoch += per_launch;
+    if (tp) {
+        // Gather the vocabulary slices.  This collective also keeps the ranks within one token of each other,
+        // which the alternating x buffers rely on.
+        LUMEN_TRY(tp_allgather(ctx, p.logits, w.logits_local, m->vocab_l, ctx->stream));
+        LUMEN_CUDA(ctx, cudaMemcpyAsync(w.logits, w.logits_local, m->V * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
+    }
     return LUMEN_OK;
 }
 
 bool mega_usable(lumen_llama *m, size_t b, size_t s) {
-    if (!m->use_mega || b != 1 || s != 1 || m->ctx->tp_size != 1 || m->L == 0) return false;
+    if (!m->use_mega || b != 1 || s != 1 || m->ctx->tp_size > 8 || m->L == 0) return false;
     MegaParams p{};
     p.H = (int)m->H; p.I = (int)m->inter_l; p.qd = (int)m->qd_l; p.D = (int)m->D;
     p.qkv_rows = (int)m->qkv_rows; p.kvd = (int)m->kvd_l;

@@ -124,6 +124,9 @@ int tp_init(lumen_ctx *ctx, const void *unique_id);
 void tp_shutdown(lumen_ctx *ctx);
 int tp_allreduce_sum(lumen_ctx *ctx, float *buf, size_t n, cudaStream_t s);          // in place
 int tp_allgather(lumen_ctx *ctx, const float *send, float *recv, size_t n_per_rank, cudaStream_t s);
+// Maps a cudaMalloc'ed buffer of every rank into every rank (CUDA IPC, handles traded over NCCL):
+// peers_out[r] = rank r's buffer as seen from this device.
+int tp_share_buffer(lumen_ctx *ctx, void *local, void **peers_out);
 
 // Stream-ordered allocation from the device's default memory pool.
 int dev_alloc(lumen_ctx *ctx, size_t bytes, void **out);

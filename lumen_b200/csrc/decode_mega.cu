@@ -330,6 +330,18 @@ __device__ __forceinline__ uint4 ld_tagged2(const uint4 *src) {
                  : "memory");
     return v;
 }
+// The same at system scope, for words that another GPU writes or reads over NVLink.
+__device__ __forceinline__ void st_tagged_sys(uint2 *dst, float v, uint32_t tag) {
+    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(v)), "r"(tag) : "memory");
+}
+__device__ __forceinline__ uint4 ld_tagged2_sys(const uint4 *src) {
+    uint4 v;
+    asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(src)
+                 : "memory");
+    return v;
+}
 __device__ __forceinline__ uint32_t phase_tag(const MegaParams &p, int ph) { return p.epoch_base + (uint32_t)ph + 1u; }
 
 // Bookkeeping shared by every bounded poll loop: true = keep polling.
@@ -389,6 +401,59 @@ __device__ __forceinline__ bool poll_vector(const MegaParams &p, Shared &sh, con
     else if (per_thread <= 16) poll_vector_pass<16>(p, sh, s4, npairs, 0, tag, xs, tid, site);
     else
         for (int base = 0; base < npairs; base += kConsumers * 24) poll_vector_pass<24>(p, sh, s4, npairs, base, tag, xs, tid, site);
+    return consumer_bar_ok(sh.abort, sh.decision, tid, bk);
+}
+
+// Tensor-parallel form of poll_vector for the residual stream: waits for the T ranks' partial vectors
+// (slots of `n` words, `slot_words` apart) and stages their sum, added in rank order.
+template <int T, int KB>
+__device__ __forceinline__ void poll_x_sum_pass(const MegaParams &p, Shared &sh, const uint2 *src, int slot_words, int npairs, int base,
+                                                uint32_t tag, float *xs, int tid) {
+    uint4 v[T][KB];
+    const long long t0 = clock64();
+    int spins = 0;
+    bool done = false, alive = true;
+    while (!done && alive) {
+        done = true;
+#pragma unroll
+        for (int r = 0; r < T; ++r) {
+            const uint4 *s4 = reinterpret_cast<const uint4 *>(src + (size_t)r * slot_words);
+#pragma unroll
+            for (int u = 0; u < KB; ++u) {
+                const int idx = base + tid + kConsumers * u;
+                v[r][u] = idx < npairs ? ld_tagged2_sys(s4 + idx) : make_uint4(0u, tag, 0u, tag);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < T; ++r)
+#pragma unroll
+            for (int u = 0; u < KB; ++u) done = done && v[r][u].y == tag && v[r][u].w == tag;
+        if (!done) alive = poll_continue(p, sh.abort, spins, t0, 350, base);
+    }
+    if (!done) return;
+#pragma unroll
+    for (int u = 0; u < KB; ++u) {
+        const int idx = base + tid + kConsumers * u;
+        if (idx >= npairs) continue;
+        float a = __uint_as_float(v[0][u].x), b = __uint_as_float(v[0][u].z);
+#pragma unroll
+        for (int r = 1; r < T; ++r) {
+            a = __fadd_rn(a, __uint_as_float(v[r][u].x));
+            b = __fadd_rn(b, __uint_as_float(v[r][u].z));
+        }
+        *reinterpret_cast<float2 *>(xs + 2 * idx) = make_float2(a, b);
+    }
+}
+
+__device__ __forceinline__ bool poll_x_sum(const MegaParams &p, Shared &sh, const uint2 *src, int n, uint32_t tag, float *xs, int tid,
+                                           int &bk) {
+    const int npairs = n / 2, sw = p.x_slot_words;
+    if (p.tp_size == 2)
+        for (int base = 0; base < npairs; base += kConsumers * 8) poll_x_sum_pass<2, 8>(p, sh, src, sw, npairs, base, tag, xs, tid);
+    else if (p.tp_size == 4)
+        for (int base = 0; base < npairs; base += kConsumers * 4) poll_x_sum_pass<4, 4>(p, sh, src, sw, npairs, base, tag, xs, tid);
+    else
+        for (int base = 0; base < npairs; base += kConsumers * 4) poll_x_sum_pass<8, 4>(p, sh, src, sw, npairs, base, tag, xs, tid);
     return consumer_bar_ok(sh.abort, sh.decision, tid, bk);
 }
 
@@ -628,7 +693,11 @@ __device__ __forceinline__ bool gemv_phase(const MegaParams &p, Shared &sh, cons
     const int lane = tid & 31, warp = tid >> 5;
     const MegaLayer *lw = g.layer < p.L ? &p.layers[g.layer] : nullptr;
     const TileIter ti(g, (int)sizeof(WT), sh.stage_bytes, cta, nctas, (p.debug_flags & 1) != 0);
-    if (ti.r0 == ti.r1) return true;  // no rows of this matrix here: nothing to read, nothing to publish
+    // No rows of this matrix here: nothing to read, nothing to publish - except that the phases which stage
+    // the residual stream also refresh the residual value this thread carries for the o_proj / down epilogues.
+    const bool has_rows = ti.r0 != ti.r1;
+    const bool stages_x = g.kind == PH_QKV || g.kind == PH_GATEUP;
+    if (!has_rows && !stages_x) return true;
     const int nvec = g.K / XPV;          // 16-byte weight vectors per row
     const int njl = (nvec + 31) / 32;    // steps of a lane through a row
 
@@ -644,10 +713,24 @@ __device__ __forceinline__ bool gemv_phase(const MegaParams &p, Shared &sh, cons
     } else {
         const uint32_t tag = phase_tag(p, ph - 1);  // every phase consumes what the phase before it published
         bool ok;
+        // o_proj outputs travel in x buffer 0 (read by gate/up), down outputs in buffer 1 (read by qkv, lm_head)
+        const uint2 *xsrc = p.xT + (size_t)(g.kind == PH_GATEUP ? 0 : 1) * p.tp_size * p.x_slot_words;
         if (g.kind == PH_O) ok = poll_attention(p, sh, tag, xs, tid, bk);
-        else ok = poll_vector(p, sh, g.kind == PH_DOWN ? p.actT : p.xT, g.K, tag, xs, tid, bk, 330 + g.kind);
+        else if (g.kind == PH_DOWN) ok = poll_vector(p, sh, p.actT, g.K, tag, xs, tid, bk, 330 + g.kind);
+        else if (p.tp_size == 1) ok = poll_vector(p, sh, xsrc, g.K, tag, xs, tid, bk, 330 + g.kind);
+        else ok = poll_x_sum(p, sh, xsrc, g.K, tag, xs, tid, bk);
         if (!ok) return false;
         if (p.trace && cta == 0 && tid == 0) p.trace[4 * (5 * p.L + 1) + 1 + ph] = globaltimer_ns();
+    }
+    if (stages_x) {
+        // xs holds the whole residual stream (all ranks' partial sums added): keep this thread's row of it
+        const long r0h = (long)p.H * cta / nctas, r1h = (long)p.H * (cta + 1) / nctas;
+        if (tid < r1h - r0h) xres = xs[r0h + tid];
+        if (!has_rows) {
+            trace_stamp(p, cta, tid, 3 * ph + 1);
+            trace_stamp(p, cta, tid, 3 * ph + 2);
+            return true;
+        }
     }
     const float *norm_w = nullptr;
     if (g.kind == PH_QKV) norm_w = lw->norm1;
@@ -726,10 +809,18 @@ __device__ __forceinline__ bool gemv_phase(const MegaParams &p, Shared &sh, cons
             switch (g.kind) {
                 case PH_QKV: st_tagged(p.qkvT + row, tot, tag); break;
                 case PH_O:      // h = x + attn_out                                   llama.rs:110
-                case PH_DOWN:   // out = h + mlp_out                                  llama.rs:115
-                    xres = __fadd_rn(xres, tot);  // (these phases have a single row block: see the launcher)
-                    st_tagged(p.xT + row, xres, tag);
+                case PH_DOWN: { // out = h + mlp_out                                  llama.rs:115
+                    // (these phases have a single row block: see the launcher)
+                    const size_t slot = (size_t)((g.kind == PH_O ? 0 : 1) * p.tp_size + p.tp_rank) * p.x_slot_words + row;
+                    if (p.tp_size == 1) {
+                        st_tagged(p.xT + slot, __fadd_rn(xres, tot), tag);
+                    } else {
+                        // this rank's partial sum (rank 0 adds the residual) goes to every rank's copy
+                        const float val = p.tp_rank == 0 ? __fadd_rn(xres, tot) : tot;
+                        for (int r = 0; r < p.tp_size; ++r) st_tagged_sys(p.x_peer[r] + slot, val, tag);
+                    }
                     break;
+                }
                 case PH_GATEUP: {  // SiLU (activation.rs:143-146) then gate_act * up (llama.rs:61-63)
                     const float up = sh.part[((size_t)kRowBlock + tid) * kConsumerWarps];
                     const float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-tot)));
@@ -744,7 +835,7 @@ __device__ __forceinline__ bool gemv_phase(const MegaParams &p, Shared &sh, cons
     rp.n += (uint32_t)(chunks * nmat);
     if ((p.debug_flags & 1) && ti.r0 + tid < ti.r1) {  // debug (no tiles streamed): publish zeros so that the chain runs
         const uint32_t tag = phase_tag(p, ph);
-        uint2 *dst = g.kind == PH_QKV ? p.qkvT : g.kind == PH_GATEUP ? p.actT : p.xT;
+        uint2 *dst = g.kind == PH_QKV ? p.qkvT : g.kind == PH_GATEUP ? p.actT : p.xT + (size_t)(g.kind == PH_O ? 0 : 1) * p.x_slot_words;
         if (g.kind != PH_LMHEAD) st_tagged(dst + ti.r0 + tid, 0.f, tag);
     }
     trace_stamp(p, cta, tid, 3 * ph + 2);
@@ -961,8 +1052,10 @@ void decode_mega_build_schedule(const MegaParams &p_in, const MegaLayer *host_la
 }
 unsigned int decode_mega_epochs_per_launch(int layers) { return 5u * (unsigned)layers + 2u; }
 
+size_t decode_mega_x_words(const MegaParams &p) { return 2 * (size_t)p.tp_size * (size_t)((p.H + 1) & ~1); }
+
 size_t decode_mega_exchange_words(const MegaParams &p) {
-    return (size_t)p.H + p.qkv_rows + p.I + (size_t)p.Hq * kMaxSplit * (2 + p.D) + 8;
+    return decode_mega_x_words(p) + p.qkv_rows + p.I + (size_t)p.Hq * kMaxSplit * (2 + p.D) + 8;
 }
 
 int decode_mega_supported(const MegaParams &p, char *why, size_t why_len) {

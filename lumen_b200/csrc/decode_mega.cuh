@@ -29,7 +29,16 @@ struct MegaParams {
     // Activations that cross CTAs are exchanged as 8-byte {f32 bits, epoch tag} words: a consumer polls the
     // words it needs until they carry the tag of the producing phase, so the data is its own signal and no
     // grid barrier is needed.  tag(phase) = epoch_base + phase + 1; epoch_base grows with every launch.
-    uint2 *xT;                // [H]          residual stream (o_proj and down outputs)
+    // Tensor parallelism: the o_proj and down outputs are partial sums over this rank's heads / intermediate
+    // rows.  A rank stores its partial row values into slot tp_rank of EVERY rank's x buffer (plain peer
+    // stores over NVLink; rank 0's partial carries the residual), and every CTA of every rank sums the
+    // tp_size slots in rank order when it stages x: the all-reduce is part of the exchange the kernel does
+    // anyway, and all ranks compute bit-identical sums.  Two buffers alternate between the two exchanges of a
+    // layer so that a fast rank cannot overwrite a value a slow rank has not read yet.
+    int tp_rank, tp_size;
+    uint2 *x_peer[8];         // x_peer[r] = rank r's xT as seen from this device (x_peer[tp_rank] == xT)
+    int x_slot_words;         // words per slot: H rounded up to even
+    uint2 *xT;                // [2][tp_size][x_slot_words]  residual stream (o_proj -> buffer 0, down -> buffer 1)
     uint2 *qkvT;              // [qkv_rows]   q | k | v projections
     uint2 *actT;              // [I]          SiLU(gate) * up
     uint2 *partT;             // [Hq, nsplit, 2 + D]: {max}, {sum}, ctx[D] of every attention work item
@@ -66,6 +75,7 @@ size_t decode_mega_smem_bytes(int stages, int stage_bytes, int head_dim, int kma
 int decode_mega_supported(const MegaParams &p, char *why, size_t why_len);
 unsigned int decode_mega_epochs_per_launch(int layers);
 size_t decode_mega_exchange_words(const MegaParams &p);  // uint2 words of the four exchange buffers
+size_t decode_mega_x_words(const MegaParams &p);         // of which the x buffers, at the start (needs tp_size, H)
 int decode_mega_max_splits();
 constexpr int kMegaTileTrace = 512;
 inline size_t decode_mega_trace_words(size_t layers) { return 7 * (5 * layers + 1) + 1 + 2 * kMegaTileTrace; }

@@ -89,6 +89,46 @@ int tp_allgather(lumen_ctx *ctx, const float *send, float *recv, size_t n_per_ra
     return LUMEN_OK;
 }
 
+// Makes `local` (a cudaMalloc'ed buffer of this rank) addressable by every rank of the group: the ranks
+// trade CUDA IPC handles through an NCCL all-gather and map each other's buffer.  peers_out[r] is a
+// pointer valid on THIS device to rank r's buffer (peers_out[tp_rank] == local).  One process per GPU.
+// Synchronises the stream.  The mappings stay open for the life of the process.
+int tp_share_buffer(lumen_ctx *ctx, void *local, void **peers_out) {
+    const int T = ctx->tp_size;
+    if (T == 1) {
+        peers_out[0] = local;
+        return LUMEN_OK;
+    }
+    if (T > 8) return set_error(ctx, LUMEN_ERR_UNSUPPORTED, "peer sharing supports at most 8 ranks, got %d", T);
+    cudaIpcMemHandle_t mine;
+    LUMEN_CUDA(ctx, cudaIpcGetMemHandle(&mine, local));
+    static_assert(sizeof(cudaIpcMemHandle_t) % 4 == 0, "handle is gathered as f32 words");
+    constexpr size_t kWords = sizeof(cudaIpcMemHandle_t) / 4;
+    float *d_all = nullptr;
+    LUMEN_CUDA(ctx, cudaMalloc(&d_all, T * sizeof(cudaIpcMemHandle_t)));
+    LUMEN_CUDA(ctx, cudaMemcpyAsync(reinterpret_cast<char *>(d_all) + ctx->tp_rank * sizeof(cudaIpcMemHandle_t), &mine,
+                                    sizeof(mine), cudaMemcpyHostToDevice, ctx->stream));
+    int rc = tp_allgather(ctx, d_all + ctx->tp_rank * kWords, d_all, kWords, ctx->stream);
+    std::vector<cudaIpcMemHandle_t> all(T);
+    cudaError_t e = cudaSuccess;
+    if (rc == LUMEN_OK) e = cudaMemcpyAsync(all.data(), d_all, T * sizeof(cudaIpcMemHandle_t), cudaMemcpyDeviceToHost, ctx->stream);
+    if (rc == LUMEN_OK && e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    cudaFree(d_all);
+    if (rc != LUMEN_OK) return rc;
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "exchange of IPC handles");
+    for (int r = 0; r < T; ++r) {
+        if (r == ctx->tp_rank) {
+            peers_out[r] = local;
+            continue;
+        }
+        void *p = nullptr;
+        e = cudaIpcOpenMemHandle(&p, all[r], cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaIpcOpenMemHandle (peer access between the ranks' GPUs is required)");
+        peers_out[r] = p;
+    }
+    return LUMEN_OK;
+}
+
 }  // namespace lumen
 
 extern "C" int lumen_nccl_unique_id(void *id_out_128_bytes) {
