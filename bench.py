@@ -104,19 +104,27 @@ class ClockSampler(threading.Thread):
 MEGA_TRAFFIC_RATIO = 1.006
 
 
-def tinyllama_cfg(dtype: str, max_seq: int, layers: int = 0):
+WORKLOADS = {  # name -> (synth config, label, default weight dtype)
+    "tinyllama": ("TINYLLAMA", "tinyllama_1.1b", "f32"),    # BASELINE config 1: the metric's configuration
+    "llama2_7b": ("LLAMA2_7B", "llama2_7b", "bf16"),        # BASELINE config 4 shape (tensor-parallel scaling)
+    "qwen3_8b": ("QWEN3_8B", "qwen3_8b", "bf16"),           # BASELINE config 5 shape at batch 1
+}
+
+
+def tinyllama_cfg(dtype: str, max_seq: int, layers: int = 0, workload: str = "tinyllama"):
     from lumen_b200 import synth
-    cfg = dict(synth.TINYLLAMA)
+    cfg = dict(getattr(synth, WORKLOADS[workload][0]))
     cfg["max_seq_len"] = max_seq
     if layers:
         cfg["num_hidden_layers"] = layers
     return cfg
 
 
-def gen_params(cfg: dict, dtype: str):
+def gen_params(cfg: dict, dtype: str, workload: str = "tinyllama"):
     from lumen_b200 import synth
     from lumen_b200.llama import LlamaConfig
-    return synth.iter_params(LlamaConfig(**cfg), 0, std=0.02, round_bf16=(dtype == "bf16"))
+    gen = synth.iter_params if workload == "tinyllama" else synth.iter_params_tiled
+    return gen(LlamaConfig(**cfg), 0, std=0.02, round_bf16=(dtype == "bf16"))
 
 
 def algorithmic_bytes_per_step(cfg: dict, weight_bytes: int, ctx_len_mean: float, tp: int) -> float:
@@ -270,7 +278,9 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
-    ap.add_argument("--dtype", choices=["f32", "bf16"], default="f32")
+    ap.add_argument("--dtype", choices=["f32", "bf16"], default=None, help="weight storage (default: the workload's)")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="tinyllama",
+                    help="model shape; the default is the configuration the metric is quoted on")
     ap.add_argument("--impl", choices=["lumen", "reference"], default="lumen")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-budget-s", type=float, default=12.0)
@@ -282,6 +292,8 @@ def main():
                          "decode attention over a static cache (one JSON line per case)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.dtype is None:
+        args.dtype = WORKLOADS[args.workload][2]
     if args.micro:
         return run_micro(args)
     if args.impl == "reference":
@@ -307,7 +319,8 @@ def main():
     max_seq = 2048
     if total > max_seq:
         raise SystemExit(f"prompt + warmup + steps = {total} exceeds max_seq_len {max_seq}")
-    cfg = tinyllama_cfg(args.dtype, max_seq, args.profile_layers)
+    cfg = tinyllama_cfg(args.dtype, max_seq, args.profile_layers, args.workload)
+    big = args.workload != "tinyllama"
 
     nccl_id = None
     if world > 1:
@@ -316,9 +329,9 @@ def main():
         nccl_id = box[0]
     ctx = L.Context(local_rank, rank, world, nccl_id)
     model = L.LlamaModel(L.LlamaConfig(**cfg, weight_dtype=args.dtype), ctx)
-    keep_params = (rank == 0 and world == 1 and not args.no_cpu_baseline)
+    keep_params = (rank == 0 and world == 1 and not args.no_cpu_baseline and not big)
     params = {}
-    for name, w in gen_params(cfg, args.dtype):
+    for name, w in gen_params(cfg, args.dtype, args.workload):
         model.set_param(name, w)
         if keep_params:
             params[name] = w
@@ -402,7 +415,7 @@ def main():
         "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"tinyllama_1.1b_{args.dtype}_batch1_decode", "weights": args.dtype, "batch": 1,
+        "config": {"workload": f"{WORKLOADS[args.workload][1]}_{args.dtype}_batch1_decode", "weights": args.dtype, "batch": 1,
                    "prompt_len": PROMPT_LEN, "max_seq_len": max_seq, "parallelism": f"tp{world}",
                    "l2": "inputs larger than L2: every step streams %.2f GB of weights" % (weight_bytes / 1e9)},
         "e2e": {"value": e2e_tps, "unit": UNIT, "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4 * cfg["vocab_size"],

@@ -40,5 +40,21 @@ def iter_params(cfg: LlamaConfig, seed: int, std: float = 0.02, round_bf16: bool
         yield name, w
 
 
+def iter_params_tiled(cfg: LlamaConfig, seed: int, std: float = 0.02, round_bf16: bool = False, block: int = 1 << 22):
+    """Like `iter_params`, for the multi-billion-parameter shapes where drawing every value would take
+    minutes per rank: each matrix repeats one seeded block of `block` N(0, std) draws (rolled by a
+    per-tensor offset).  Same shapes, dtype and value distribution; only throughput runs use it."""
+    rng = np.random.default_rng(seed)
+    base = rng.standard_normal(block, dtype=np.float32) * np.float32(std)
+    if round_bf16:
+        base = bf16_bits_to_f32(f32_to_bf16_bits(base)).reshape(-1)
+    for i, (name, shape) in enumerate(sorted(cfg.param_shapes().items())):
+        if len(shape) == 1:
+            yield name, np.ones(shape, np.float32)
+            continue
+        n = int(np.prod(shape))
+        yield name, np.resize(np.roll(base, 7919 * i), n).reshape(shape)
+
+
 def token_ids(seed: int, n: int, vocab: int) -> np.ndarray:
     return np.random.default_rng(seed).integers(0, vocab, size=n).astype(np.float32)
