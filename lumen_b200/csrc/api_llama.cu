@@ -213,7 +213,7 @@ int enqueue_forward(lumen_llama *m, const StepPlan &p, lumen_kv_cache **caches, 
             a.B = p.B; a.Hq = m->hq_l; a.Hkv = m->hkv_l; a.D = m->D; a.max_seq = c->max_seq;
             a.cos_t = m->cos_t; a.sin_t = m->sin_t;
             a.q_norm = lw.qn; a.k_norm = lw.kn; a.norm_eps = eps;
-            a.scale = scale; a.out = w.att; a.part = w.part; a.max_splits = p.nsplit;
+            a.scale = scale; a.out = w.att; a.part = w.part; a.max_splits = p.nsplit; a.len_hint = c->len;
             LUMEN_TRY(launch_attn_decode(ctx, a, s));
         } else {
             AttnPrefillArgs a;

@@ -368,6 +368,7 @@ int lumen_attention_decode(lumen_ctx *ctx, const float *q_dev, const float *k_ne
     a.scale = 1.0f / sqrtf((float)cache->d);
     a.out = out_dev;
     a.max_splits = attn_decode_pick_splits(a.B, a.Hkv, cache->len + 1, ctx->num_sms);
+    a.len_hint = cache->len;
     void *part = nullptr;
     LUMEN_TRY(dev_alloc(ctx, attn_decode_scratch_bytes(a.B, a.Hq, a.D, a.max_splits), &part));
     a.part = static_cast<float *>(part);
@@ -459,6 +460,7 @@ int lumen_self_attention_forward(lumen_self_attention *attn, const lumen_tensor 
         a.cos_t = attn->rope->cos_t; a.sin_t = attn->rope->sin_t;
         a.scale = attn->scale; a.out = (float *)ab;
         a.max_splits = attn_decode_pick_splits(B, Hkv, past + 1, ctx->num_sms);
+        a.len_hint = past;
         const size_t need = attn_decode_scratch_bytes(B, Hq, D, a.max_splits);
         void *part = nullptr;
         rc = dev_alloc(ctx, need, &part);

@@ -143,6 +143,317 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_kernel(PrefillParams p)
     }
 }
 
+// ---- decode, long contexts: tiled kernel ------------------------------------------------------------
+// For GQA groups of 4 or 8 query heads and head dimensions 64 / 128.  A CTA still owns (batch row, KV head,
+// context split) and serves the whole query group from one read of K and V, but the work of a warp is
+// organised as two small register-tiled products per tile of TR cached rows instead of one shuffle-reduced
+// dot product per row and head:
+//   - the warp brings a K tile and a V tile (TR rows = 8 KB each, contiguous in the cache) into shared
+//     memory with one TMA bulk copy each (cp.async.bulk + an mbarrier per warp and stage, three stages:
+//     two tiles in flight behind the one in use; bounded waits);
+//   - scores S[GT][TR] = q . K^T: lane (hg, rg) accumulates HT = GT/2 heads x RPL = TR/16 rows over the D/4
+//     chunks, each lane walking the chunks in an order rotated by rg so that the 16 rows read by one load
+//     fall into different banks;
+//   - online softmax per tile: the tile maximum of a head needs 4 shuffles, every score is exponentiated
+//     once, the weights go to a TR x GT table in shared memory;
+//   - ctx[GT][D] += P^T . V: lane (hg, dg) accumulates HT heads x D/16 dimensions over the TR rows (one
+//     128-bit load of V per D/64 and one broadcast load of the HT weights per row).
+// About 90 instructions per KB of cache read instead of 150, almost all independent FMAs.  The partial
+// results leave through the same (max, sum, ctx) records as the other kernel, so the merge is shared.
+constexpr int kTiledStages = 3;  // tiles of K and of V per warp in shared memory: two in flight behind the one in use
+
+template <int D>
+__host__ __device__ constexpr int tiled_rows() { return 2048 / D; }  // rows per tile: 8 KB of K, 8 KB of V
+template <int D>
+__host__ __device__ constexpr int tiled_warps() { return 4; }
+
+template <int D, int GT>
+__host__ __device__ constexpr size_t tiled_smem_floats() {
+    // q heads | rotated new k | per warp: K and V tiles of every stage and the weight table | per-warp (max, sum)
+    return (size_t)GT * D + D + (size_t)tiled_warps<D>() * (2 * kTiledStages * tiled_rows<D>() * D + tiled_rows<D>() * GT) +
+           2 * tiled_warps<D>() * GT;
+}
+
+__device__ __forceinline__ uint32_t smem_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void tile_bar_init(uint64_t *bar) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void tile_bar_expect(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool tile_bar_try(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// 1-D bulk copy global -> shared (TMA), completion counted in bytes on `bar`.
+__device__ __forceinline__ void tile_bulk_load(void *smem_dst, const void *gsrc, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_addr(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_addr(bar)) : "memory");
+}
+// Bounded wait: gives up after ~0.1 s of clock cycles and reports it (the kernel then finishes with whatever
+// it has; the host sees LUMEN_ERR_TIMEOUT at its next synchronising call).
+__device__ __forceinline__ bool tile_bar_wait(uint64_t *bar, uint32_t parity, DeviceStatus *status) {
+    if (tile_bar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!tile_bar_try(bar, parity)) {
+        if (clock64() - t0 > 200000000LL) {
+            if (status && atomicCAS(&status->code, 0, LUMEN_ERR_TIMEOUT) == 0) status->detail0 = 400;
+            return false;
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ float dot4(const float4 a, const float4 b, float acc) {
+    acc = fmaf(a.x, b.x, acc);
+    acc = fmaf(a.y, b.y, acc);
+    acc = fmaf(a.z, b.z, acc);
+    acc = fmaf(a.w, b.w, acc);
+    return acc;
+}
+
+// grid (nsplit, Hkv * (G/GT), B), (tiled_warps<D>() * 32) threads
+template <int D, int GT>
+__global__ void __launch_bounds__((tiled_warps<D>() * 32), 1) attn_decode_tiled_kernel(DecodeParams p) {
+    constexpr int NW = tiled_warps<D>();
+    constexpr int TR = tiled_rows<D>();  // 32 (D = 64) or 16 (D = 128)
+    constexpr int CH = D / 4;            // 16-byte chunks per row
+    constexpr int HT = GT / 2;           // heads per lane
+    constexpr int RPL = TR / 16;         // rows per lane in the score product
+    constexpr int DQ = D / 64;           // float4s of ctx per lane and head
+    extern __shared__ __align__(16) float smem[];
+    float *qs = smem;                          // [GT][D]
+    float *knew = qs + GT * D;                 // [D]
+    float *wbase = knew + D;                   // per warp: K tiles, V tiles, P
+    constexpr int NS = kTiledStages;
+    constexpr int kPerWarp = 2 * NS * TR * D + TR * GT;
+    float *wm = wbase + NW * kPerWarp;         // [NW][GT]
+    float *wl = wm + NW * GT;                  // [NW][GT]
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int hg = lane >> 4, rg = lane & 15;
+    const int b = blockIdx.z, ygroup = blockIdx.y, split = blockIdx.x;
+    const int past = *p.d_len;
+    const int G = p.Hq / p.Hkv;
+    const int groups_per_kv = G / GT;
+    const int hk = ygroup / groups_per_kv;
+    const int h0 = hk * G + (ygroup % groups_per_kv) * GT;
+    const int total = past + 1;
+    const int chunk = (total + p.nsplit - 1) / p.nsplit;
+    const int j0 = split * chunk;
+    const int j1 = min(total, j0 + chunk);
+    const int half = D / 2;
+    const float *cos_row = p.cos_t ? p.cos_t + (size_t)past * half : nullptr;
+    const float *sin_row = p.sin_t ? p.sin_t + (size_t)past * half : nullptr;
+    const float *kbase = p.k_cache + ((size_t)b * p.Hkv + hk) * p.max_seq * D;
+    const float *vbase = p.v_cache + ((size_t)b * p.Hkv + hk) * p.max_seq * D;
+    float *ktile = wbase + warp * kPerWarp;             // [NS][TR][D], chunks swizzled
+    float *vtile = ktile + NS * TR * D;                 // [NS][TR][D]
+    float *pt = vtile + NS * TR * D;                    // [TR][GT]
+
+    // Tiles arrive by TMA: the TR rows of a tile are contiguous in the cache, so a tile is one bulk copy for K
+    // and one for V, counted on the (warp, stage) mbarrier.  The last tile of the range copies only its valid
+    // rows.  Issued by lane 0 of the warp that will consume the tile.
+    __shared__ uint64_t bars[NW * NS];
+    if (tid == 0) {
+        for (int i = 0; i < NW * NS; ++i) tile_bar_init(&bars[i]);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    auto load_tile = [&](int jt, int buf) {
+        if (jt < j1 && lane == 0) {
+            const uint32_t bytes = (uint32_t)min(TR, j1 - jt) * D * sizeof(float);
+            uint64_t *bar = &bars[warp * NS + buf];
+            tile_bar_expect(bar, 2 * bytes);
+            tile_bulk_load(ktile + buf * TR * D, kbase + (size_t)jt * D, bytes, bar);
+            tile_bulk_load(vtile + buf * TR * D, vbase + (size_t)jt * D, bytes, bar);
+        }
+    };
+    const int jw0 = j0 + warp * TR;  // first tile of this warp; the next ones follow every NW * TR rows
+    constexpr int kStep = NW * TR;
+#pragma unroll
+    for (int st = 0; st < NS - 1; ++st) load_tile(jw0 + st * kStep, st);
+
+    // Stage and rotate the query heads and this step's k (as in the other kernel).
+    for (int g = warp; g < GT; g += NW) {
+        const float *src = p.q + (size_t)b * p.q_stride + (size_t)(h0 + g) * D;
+        load_norm_rope<false>(qs + g * D, src, D, p.q_norm, p.norm_eps, cos_row, sin_row, lane);
+    }
+    const bool owns_new = (past >= j0 && past < j1);
+    const float *vnew_src = p.v_new + (size_t)b * p.kv_stride + (size_t)hk * D;
+    if (owns_new && warp == NW - 1) {
+        const float *ksrc = p.k_new + (size_t)b * p.kv_stride + (size_t)hk * D;
+        load_norm_rope<false>(knew, ksrc, D, p.k_norm, p.norm_eps, cos_row, sin_row, lane);
+        if (ygroup % groups_per_kv == 0) {
+            float *k_row = p.k_cache + (((size_t)b * p.Hkv + hk) * p.max_seq + past) * D;
+            float *v_row = p.v_cache + (((size_t)b * p.Hkv + hk) * p.max_seq + past) * D;
+            for (int i = lane; i < D; i += 32) {
+                k_row[i] = knew[i];
+                v_row[i] = __ldcg(vnew_src + i);
+            }
+        }
+    }
+    __syncthreads();
+
+    float m[HT], l[HT];
+    float4 ctx[HT][DQ];
+#pragma unroll
+    for (int i = 0; i < HT; ++i) {
+        m[i] = -INFINITY;
+        l[i] = 0.f;
+#pragma unroll
+        for (int q4 = 0; q4 < DQ; ++q4) ctx[i][q4] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    const float4 *qs4 = reinterpret_cast<const float4 *>(qs);
+
+    int buf = 0, it = 0;
+    bool alive = true;
+    for (int jt = jw0; jt < j1 && alive; jt += kStep, buf = (buf + 1 == NS ? 0 : buf + 1), ++it) {
+        load_tile(jt + (NS - 1) * kStep, buf == 0 ? NS - 1 : buf - 1);  // into the stage released by the previous iteration
+        alive = tile_bar_wait(&bars[warp * NS + buf], (uint32_t)(it / NS) & 1u, p.status);
+        float4 *k4 = reinterpret_cast<float4 *>(ktile + buf * TR * D);
+        float4 *v4 = reinterpret_cast<float4 *>(vtile + buf * TR * D);
+        const int nvalid = min(TR, j1 - jt);
+        // Rows past the range weigh nothing, but what they are multiplied with must be finite: clear V there.
+        for (int i = nvalid * CH + lane; i < TR * CH; i += 32) v4[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (past >= jt && past < jt + TR) {  // the row appended by this step: take it from the staged copies
+            const int r = past - jt;
+            if (lane < CH) {
+                k4[r * CH + lane] = reinterpret_cast<const float4 *>(knew)[lane];
+                v4[r * CH + lane] = __ldcg(reinterpret_cast<const float4 *>(vnew_src) + lane);
+            }
+        }
+        __syncwarp();
+        // ---- scores ------------------------------------------------------------------------------------
+        float s[RPL][HT];
+#pragma unroll
+        for (int rr = 0; rr < RPL; ++rr)
+#pragma unroll
+            for (int i = 0; i < HT; ++i) s[rr][i] = 0.f;
+        // The 16 row lanes of a load read 16 different rows, whose chunks of equal index share their banks:
+        // every lane therefore walks the chunks in an order rotated by its own index (a sum does not care).
+#pragma unroll 4
+        for (int cc = 0; cc < CH; ++cc) {
+            const int c = (cc + rg) & (CH - 1);
+            float4 qv[HT];
+#pragma unroll
+            for (int i = 0; i < HT; ++i) qv[i] = qs4[(HT * hg + i) * CH + c];
+#pragma unroll
+            for (int rr = 0; rr < RPL; ++rr) {
+                const int r = RPL * rg + rr;
+                const float4 kv = k4[r * CH + c];
+#pragma unroll
+                for (int i = 0; i < HT; ++i) s[rr][i] = dot4(kv, qv[i], s[rr][i]);
+            }
+        }
+        // ---- online softmax of the tile -----------------------------------------------------------------
+        float rs[HT];
+#pragma unroll
+        for (int i = 0; i < HT; ++i) {
+            float tmax = -INFINITY;
+#pragma unroll
+            for (int rr = 0; rr < RPL; ++rr) {
+                const bool ok = jt + RPL * rg + rr < j1;
+                s[rr][i] = ok ? __fmul_rn(s[rr][i], p.scale) : -INFINITY;
+                tmax = fmaxf(tmax, s[rr][i]);
+            }
+#pragma unroll
+            for (int o = 1; o < 16; o <<= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, o));
+            const float mn = fmaxf(m[i], tmax);  // finite: the tile's first row is inside the range
+            rs[i] = expf(m[i] - mn);
+            float wsum = 0.f;
+#pragma unroll
+            for (int rr = 0; rr < RPL; ++rr) {
+                const float w = expf(s[rr][i] - mn);
+                s[rr][i] = w;
+                wsum += w;
+            }
+            l[i] = fmaf(l[i], rs[i], wsum);
+            m[i] = mn;
+        }
+#pragma unroll
+        for (int rr = 0; rr < RPL; ++rr)
+#pragma unroll
+            for (int i = 0; i < HT; ++i) pt[(RPL * rg + rr) * GT + HT * hg + i] = s[rr][i];
+        __syncwarp();
+        // ---- ctx = ctx * r + P^T . V ----------------------------------------------------------------------
+#pragma unroll
+        for (int i = 0; i < HT; ++i)
+#pragma unroll
+            for (int q4 = 0; q4 < DQ; ++q4) {
+                ctx[i][q4].x *= rs[i]; ctx[i][q4].y *= rs[i]; ctx[i][q4].z *= rs[i]; ctx[i][q4].w *= rs[i];
+            }
+#pragma unroll 4
+        for (int r = 0; r < TR; ++r) {
+            float w[HT];
+            if (HT == 4) {
+                const float4 w4 = *reinterpret_cast<const float4 *>(pt + r * GT + 4 * hg);
+                w[0] = w4.x; w[1] = w4.y; w[HT - 2] = w4.z; w[HT - 1] = w4.w;
+            } else {
+                const float2 w2 = *reinterpret_cast<const float2 *>(pt + r * GT + 2 * hg);
+                w[0] = w2.x; w[HT - 1] = w2.y;
+            }
+#pragma unroll
+            for (int q4 = 0; q4 < DQ; ++q4) {
+                const float4 vv = v4[r * CH + q4 * 16 + rg];  // dimensions 4 * (q4 * 16 + rg) ..
+#pragma unroll
+                for (int i = 0; i < HT; ++i) {
+                    ctx[i][q4].x = fmaf(w[i], vv.x, ctx[i][q4].x);
+                    ctx[i][q4].y = fmaf(w[i], vv.y, ctx[i][q4].y);
+                    ctx[i][q4].z = fmaf(w[i], vv.z, ctx[i][q4].z);
+                    ctx[i][q4].w = fmaf(w[i], vv.w, ctx[i][q4].w);
+                }
+            }
+        }
+        __syncwarp();  // the weight table and this tile's buffers are rewritten by the next iterations
+    }
+
+    // Merge the warps of this CTA.  A head's running sum is spread over its 16 row lanes.
+#pragma unroll
+    for (int i = 0; i < HT; ++i) {
+#pragma unroll
+        for (int o = 1; o < 16; o <<= 1) l[i] += __shfl_xor_sync(0xffffffffu, l[i], o);
+        if (rg == 0) {
+            wm[warp * GT + HT * hg + i] = m[i];
+            wl[warp * GT + HT * hg + i] = l[i];
+        }
+    }
+    if (!alive) {  // a wait gave up: let this warp's copies that are still in flight land before the CTA exits
+        for (int sb = 0; sb < NS; ++sb) {
+            const long long t0 = clock64();
+            while (!tile_bar_try(&bars[warp * NS + sb], 0) && !tile_bar_try(&bars[warp * NS + sb], 1) && clock64() - t0 < 200000000LL) {}
+        }
+    }
+    float *wctx = ktile;  // this warp's first K tile is free now: [GT][D]
+#pragma unroll
+    for (int i = 0; i < HT; ++i)
+#pragma unroll
+        for (int q4 = 0; q4 < DQ; ++q4)
+            reinterpret_cast<float4 *>(wctx)[(HT * hg + i) * CH + q4 * 16 + rg] = ctx[i][q4];
+    __syncthreads();
+    for (int idx = tid; idx < GT * D; idx += (tiled_warps<D>() * 32)) {
+        const int g = idx / D, e = idx % D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) M = fmaxf(M, wm[w * GT + g]);
+        float L = 0.f, c = 0.f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) {
+            const float mw = wm[w * GT + g];
+            const float f = (mw == -INFINITY) ? 0.f : expf(mw - M);
+            L = fmaf(wl[w * GT + g], f, L);
+            c = fmaf(wbase[w * kPerWarp + g * D + e], f, c);
+        }
+        const size_t o = ((size_t)b * p.Hq + h0 + g) * p.nsplit + split;
+        p.part_ctx[o * D + e] = c;
+        if (e == 0) {
+            p.part_m[o] = M;
+            p.part_l[o] = L;
+        }
+    }
+}
+
 int pick_gt(int G) { return (G % 8 == 0) ? 8 : (G % 4 == 0) ? 4 : (G % 2 == 0) ? 2 : 1; }
 int pick_ni(size_t D) { return D <= 32 ? 1 : D <= 64 ? 2 : D <= 128 ? 4 : 8; }
 
@@ -166,6 +477,21 @@ int launch_decode_gt(lumen_ctx *ctx, const DecodeParams &p, int ni, dim3 grid, s
     return LUMEN_OK;
 }
 
+template <int D, int GT>
+int launch_decode_tiled(lumen_ctx *ctx, const DecodeParams &p, dim3 grid, cudaStream_t s) {
+    auto kern = attn_decode_tiled_kernel<D, GT>;
+    constexpr size_t smem = tiled_smem_floats<D, GT>() * sizeof(float);
+    static bool attr_set[64] = {false};  // per device ordinal
+    const int dev = ctx->device >= 0 && ctx->device < 64 ? ctx->device : 0;
+    if (!attr_set[dev]) {
+        LUMEN_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_set[dev] = true;
+    }
+    kern<<<grid, (tiled_warps<D>() * 32), smem, s>>>(p);
+    LUMEN_LAUNCHED(ctx);
+    return LUMEN_OK;
+}
+
 }  // namespace
 
 size_t attn_decode_scratch_bytes(size_t B, size_t Hq, size_t D, int max_splits) {
@@ -178,11 +504,15 @@ int attn_decode_pick_splits(size_t B, size_t Hkv, size_t len, int num_sms) {
     // that product (plus a fixed cost per wave for staging q and merging), with at least 64 rows per split.
     const size_t base = std::max<size_t>(1, B * Hkv);
     const size_t max_ns = std::max<size_t>(1, std::min<size_t>(64, (len + 63) / 64));
+    static const size_t wave_rows = [] {
+        const char *e = getenv("LUMEN_ATTN_WAVE_ROWS");
+        return e ? (size_t)atoi(e) : (size_t)256;
+    }();
     size_t best = 1, best_cost = ~(size_t)0;
     for (size_t ns = 1; ns <= max_ns; ++ns) {
         const size_t waves = (base * ns + (size_t)num_sms - 1) / (size_t)num_sms;
         const size_t rows = (len + ns - 1) / ns;
-        const size_t cost = waves * (rows + 48);
+        const size_t cost = waves * (rows + wave_rows);
         if (cost < best_cost) {
             best_cost = cost;
             best = ns;
@@ -204,6 +534,7 @@ int launch_attn_decode(lumen_ctx *ctx, const AttnDecodeArgs &a, cudaStream_t s) 
     p.cos_t = a.cos_t; p.sin_t = a.sin_t; p.q_norm = a.q_norm; p.k_norm = a.k_norm;
     p.norm_eps = a.norm_eps; p.scale = a.scale;
     p.nsplit = nsplit;
+    p.status = ctx->d_status;
     const size_t rows = a.B * a.Hq * (size_t)nsplit;
     p.part_m = a.part;
     p.part_l = a.part + rows;
@@ -211,6 +542,13 @@ int launch_attn_decode(lumen_ctx *ctx, const AttnDecodeArgs &a, cudaStream_t s) 
     dim3 grid(nsplit, (unsigned)(a.Hkv * (G / GT)), (unsigned)a.B);
     size_t smem = attn_decode_smem_floats(GT, (int)a.D) * sizeof(float);
     int rc;
+    // Long contexts of grouped-query models take the tiled kernel (at least four tiles of rows per split).
+    const size_t rows_per_split = (a.len_hint + 1 + nsplit - 1) / nsplit;
+    const bool tiled = (GT == 8 || GT == 4) && (a.D == 64 || a.D == 128) && rows_per_split >= 128 && !getenv("LUMEN_NO_TILED_ATTN");
+    if (tiled) {
+        if (a.D == 64) rc = GT == 8 ? launch_decode_tiled<64, 8>(ctx, p, grid, s) : launch_decode_tiled<64, 4>(ctx, p, grid, s);
+        else rc = GT == 8 ? launch_decode_tiled<128, 8>(ctx, p, grid, s) : launch_decode_tiled<128, 4>(ctx, p, grid, s);
+    } else
     switch (GT) {
         case 8: rc = launch_decode_gt<8>(ctx, p, ni, grid, smem, s); break;
         case 4: rc = launch_decode_gt<4>(ctx, p, ni, grid, smem, s); break;

@@ -112,6 +112,7 @@ struct DecodeParams {
     float norm_eps, scale;
     float *part_m, *part_l, *part_ctx;  // [B,Hq,nsplit], [B,Hq,nsplit], [B,Hq,nsplit,D]
     int nsplit;
+    DeviceStatus *status = nullptr;  // where a bounded wait that gave up is recorded (may be null)
 };
 
 // Rows of K and V a warp keeps in flight, as a function of the elements per lane NI = ceil(D / 32).

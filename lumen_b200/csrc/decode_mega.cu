@@ -400,7 +400,7 @@ __device__ __forceinline__ bool poll_vector(const MegaParams &p, Shared &sh, con
     else if (per_thread <= 8) poll_vector_pass<8>(p, sh, s4, npairs, 0, tag, xs, tid, site);
     else if (per_thread <= 16) poll_vector_pass<16>(p, sh, s4, npairs, 0, tag, xs, tid, site);
     else
-        for (int base = 0; base < npairs; base += kConsumers * 24) poll_vector_pass<24>(p, sh, s4, npairs, base, tag, xs, tid, site);
+        for (int base = 0; base < npairs; base += kConsumers * 16) poll_vector_pass<16>(p, sh, s4, npairs, base, tag, xs, tid, site);
     return consumer_bar_ok(sh.abort, sh.decision, tid, bk);
 }
 
@@ -453,7 +453,7 @@ __device__ __forceinline__ bool poll_x_sum(const MegaParams &p, Shared &sh, cons
     else if (p.tp_size == 4)
         for (int base = 0; base < npairs; base += kConsumers * 4) poll_x_sum_pass<4, 4>(p, sh, src, sw, npairs, base, tag, xs, tid);
     else
-        for (int base = 0; base < npairs; base += kConsumers * 4) poll_x_sum_pass<8, 4>(p, sh, src, sw, npairs, base, tag, xs, tid);
+        for (int base = 0; base < npairs; base += kConsumers * 2) poll_x_sum_pass<8, 2>(p, sh, src, sw, npairs, base, tag, xs, tid);
     return consumer_bar_ok(sh.abort, sh.decision, tid, bk);
 }
 
@@ -704,6 +704,23 @@ __device__ __forceinline__ bool gemv_phase(const MegaParams &p, Shared &sh, cons
     // ---- prologue: the input vector, in shared memory ---------------------------------------------------
     float *xs = sh.xs;
     float4 *xs4 = reinterpret_cast<float4 *>(xs);
+    // RMSNorm gains of the phase are requested before the wait for x, so that their trip to L2 is not added
+    // to the critical path (up to 4 vectors per thread: K <= 2048; longer rows fetch them afterwards).
+    const float *norm_w = nullptr;
+    if (g.kind == PH_QKV) norm_w = lw->norm1;
+    else if (g.kind == PH_GATEUP) norm_w = lw->norm2;
+    else if (g.kind == PH_LMHEAD) norm_w = p.final_norm;
+    constexpr int kEarlyGains = 4;
+    const int n4s = g.K / 4;
+    const bool early = norm_w != nullptr && n4s <= kEarlyGains * kConsumers;
+    float4 gains[kEarlyGains];
+    if (early) {
+#pragma unroll
+        for (int u = 0; u < kEarlyGains; ++u) {
+            const int i = tid + kConsumers * u;
+            gains[u] = i < n4s ? __ldg(reinterpret_cast<const float4 *>(norm_w) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
     const int njl4 = (njl + 3) & ~3;     // the inner loop takes four steps at a time
     for (int k = g.K + tid; k < njl4 * 32 * XPV; k += kConsumers) xs[k] = 0.f;  // zero padding up to whole steps
     if (g.kind == PH_QKV && g.layer == 0) {
@@ -732,14 +749,9 @@ __device__ __forceinline__ bool gemv_phase(const MegaParams &p, Shared &sh, cons
             return true;
         }
     }
-    const float *norm_w = nullptr;
-    if (g.kind == PH_QKV) norm_w = lw->norm1;
-    else if (g.kind == PH_GATEUP) norm_w = lw->norm2;
-    else if (g.kind == PH_LMHEAD) norm_w = p.final_norm;
     if (norm_w) {
         // RMSNorm::forward (rms_norm.rs:49-56): rms = sqrt(ss/dim + eps); x = (x * (1/rms)) * w, in place
         const float4 *n4 = reinterpret_cast<const float4 *>(norm_w);
-        const int n4s = g.K / 4;
         float ss = 0.f;
         for (int i = tid; i < n4s; i += kConsumers) {
             const float4 v = xs4[i];
@@ -753,14 +765,22 @@ __device__ __forceinline__ bool gemv_phase(const MegaParams &p, Shared &sh, cons
         consumer_bar();
         const float tot = (sh.red[0] + sh.red[1]) + (sh.red[2] + sh.red[3]);
         const float inv = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(tot, (float)g.K), p.eps)));
-        for (int i = tid; i < n4s; i += kConsumers) {
+        auto rescale = [&](int i, const float4 w) {
             float4 v = xs4[i];
-            const float4 w = __ldg(n4 + i);
             v.x = __fmul_rn(__fmul_rn(v.x, inv), w.x);
             v.y = __fmul_rn(__fmul_rn(v.y, inv), w.y);
             v.z = __fmul_rn(__fmul_rn(v.z, inv), w.z);
             v.w = __fmul_rn(__fmul_rn(v.w, inv), w.w);
             xs4[i] = v;
+        };
+        if (early) {
+#pragma unroll
+            for (int u = 0; u < kEarlyGains; ++u) {
+                const int i = tid + kConsumers * u;
+                if (i < n4s) rescale(i, gains[u]);
+            }
+        } else {
+            for (int i = tid; i < n4s; i += kConsumers) rescale(i, __ldg(n4 + i));
         }
         consumer_bar();
     }

@@ -65,6 +65,15 @@ def test_decode_attention_split_boundaries(L, oracle, ctx, ctx_len):
     assert err < 2e-5, err
 
 
+@pytest.mark.parametrize("hq,hkv,d", [(16, 4, 128), (16, 2, 128), (16, 4, 64), (32, 4, 64)])
+def test_decode_attention_tiled_kernel_geometries(L, oracle, ctx, hq, hkv, d):
+    """Long contexts of grouped-query models (groups of 4 and 8, head_dim 64 and 128) at a batch large enough
+    that each split holds several tiles of rows: the TMA-fed tiled kernel.  The context is not a multiple of
+    the tile, the appended row falls inside a tile, and the second step crosses into a new row."""
+    err = _decode_case(L, oracle, ctx, 8, hq, hkv, d, 1499, 1536, seed=hq + hkv + d, steps=2, theta=1e6)
+    assert err < 2e-5, err
+
+
 @pytest.mark.parametrize("hq,hkv,d", [(32, 32, 128), (32, 8, 128), (6, 2, 32), (4, 4, 16), (5, 1, 48), (2, 1, 256)])
 def test_decode_attention_head_geometries(L, oracle, ctx, hq, hkv, d):
     err = _decode_case(L, oracle, ctx, 2, hq, hkv, d, 200, 256, seed=hq + d, steps=2, theta=1e6)
