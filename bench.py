@@ -181,6 +181,7 @@ def run_reference(args):
 
 
 GEMV_SWEEP = [(2048, 2048), (2048, 256), (2048, 5632), (5632, 2048), (2048, 32000), (4096, 11008), (11008, 4096)]
+GEMM_SWEEP = [(32, 2048, 5632), (512, 4096, 4096), (512, 4096, 11008), (512, 11008, 4096), (4096, 4096, 12288), (4096, 4096, 4096)]
 ATTN_SWEEP = [(1, 128), (1, 512), (1, 2048), (1, 8192), (16, 128), (16, 512), (16, 2048), (16, 8192)]
 
 
@@ -235,6 +236,30 @@ def run_micro(args):
                                       "algorithmic_bytes": nbytes, "gbs": gbs, "frac_of_measured_peak": gbs / peak,
                                       "peak_kind": peak_kind, "working_set_mb": copies * k * n * esz / 1e6}), flush=True)
                     del ws
+    elif args.micro == "gemm":
+        # M > 8 branch of matmul with bf16 weights (prefill / batched decode): tensor-core roofline
+        try:
+            tpeak = float(json.loads((ROOT / "MEASURED_PEAKS.json").read_text())["bf16_tflops"])
+            tkind = "measured"
+        except Exception:
+            tpeak, tkind = 1590.0, "fallback"
+        for m, k, n in GEMM_SWEEP:
+            a = L.Tensor.from_array_no_grad(rng.standard_normal((m, k), dtype=np.float32), ctx)
+            w = L.Tensor.from_bf16(rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02), ctx)
+            keep = []
+
+            def step():
+                keep.append(L.matmul(a, w))
+                if len(keep) > 4:
+                    keep.pop(0)
+
+            ms = _event_time_ms(ctx, stream, step, iters=20)
+            tf = 2.0 * m * k * n / (ms * 1e-3) / 1e12
+            print(json.dumps({"micro": "gemm_bf16_weights", "m": m, "k": k, "n": n, "us": ms * 1e3, "tflops": tf,
+                              "frac_of_peak": tf / tpeak, "peak_tflops": tpeak, "peak_kind": tkind,
+                              "note": "algorithmic flops 2*M*K*N; the kernel issues twice that (activations as hi+lo bf16)"}),
+                  flush=True)
+            del keep
     else:
         hq, hkv, d = 32, 4, 64
         for b, ctx_len in ATTN_SWEEP:
@@ -287,7 +312,7 @@ def main():
     ap.add_argument("--profile-layers", type=int, default=0,
                     help="profiling aid: truncate the model to this many layers so that a profiler capture stays "
                          "small; the printed line is then marked and is not a benchmark value")
-    ap.add_argument("--micro", choices=["gemv", "attn"], default=None,
+    ap.add_argument("--micro", choices=["gemv", "attn", "gemm"], default=None,
                     help="secondary measurements instead of the decode benchmark: the vector-matrix sweep or "
                          "decode attention over a static cache (one JSON line per case)")
     args = ap.parse_args()

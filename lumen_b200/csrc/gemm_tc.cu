@@ -1,0 +1,284 @@
+// C[M,N] = A[M,K] . W[N,K]^T (+ residual) on the 5th-generation tensor cores, for the M > 8 branch of
+// ops::matmul (src/ops/matmul.rs:70-92: prefill and batched decode) when W is stored as bf16.
+//
+// sm_100a structure: one CTA per 128 x 128 output tile; thread 0 is the TMA producer (2-D tiled copies
+// with 128-byte swizzle into a 4-stage shared-memory ring, mbarrier transaction counts), thread 32 issues
+// tcgen05.mma (kind::f16, bf16 operands, f32 accumulation) with the accumulator in tensor memory (128
+// lanes x 128 columns) and releases each stage with tcgen05.commit; afterwards the four warps read the
+// accumulator back with tcgen05.ld (32 lanes each) and store f32 rows.
+//
+// The activations are f32 in the reference.  They are split into two bf16 matrices, hi = bf16(a) and
+// lo = bf16(a - hi), and both products accumulate into the same tensor-memory tile: a = hi + lo to about
+// 2^-17 relative, so the result stays within ~1e-5 of the f32 product instead of the ~4e-3 a single bf16
+// rounding of the activations would cost, at twice the (cheap) tensor-core work.
+//
+// Every wait is bounded; a wait that gives up records LUMEN_ERR_TIMEOUT, the CTA stops issuing, lets the
+// copies in flight land, frees its tensor memory and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace lumen {
+namespace {
+
+constexpr int kBM = 128, kBN = 128, kBK = 64;  // tile; kBK bf16 = one 128-byte swizzle row
+constexpr int kStages = 4;
+constexpr int kTcThreads = 128;
+constexpr uint32_t kABytes = kBM * kBK * 2, kBBytes = kBN * kBK * 2;
+constexpr uint32_t kStageBytes = 2 * kABytes + kBBytes;  // A hi, A lo, B
+constexpr long long kTcWaitCycles = 200000000LL;         // ~0.1 s
+
+__device__ __forceinline__ uint32_t saddr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void bar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(saddr(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void bar_expect(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(saddr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool bar_try(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(saddr(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool bar_wait(uint64_t *bar, uint32_t parity, DeviceStatus *status, int site) {
+    if (bar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!bar_try(bar, parity)) {
+        if (clock64() - t0 > kTcWaitCycles) {
+            if (status && atomicCAS(&status->code, 0, LUMEN_ERR_TIMEOUT) == 0) status->detail0 = site;
+            return false;
+        }
+    }
+    return true;
+}
+// 2-D tiled TMA load: box (kBK elements, rows) at element coordinates (x = k, y = row).  x is a multiple of
+// 64 bf16 elements = 128 bytes, so the 16-byte start rule of TMA holds.
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(saddr(dst)), "l"(map), "r"(x), "r"(y), "r"(saddr(bar)) : "memory");
+}
+// Shared-memory matrix descriptor of a K-major bf16 tile stored as rows of 128 bytes with the 128-byte
+// swizzle (what the TMA box above produces): start address, leading offset 1 (unused with swizzle), 1024
+// bytes between groups of 8 rows, descriptor version 1, layout type 2 = 128-byte swizzle.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+           ((uint64_t)2 << 61);
+}
+// Instruction descriptor: f32 accumulator, bf16 A and B, both K-major, N and M of the tile.
+constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+                 " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}"
+                 ::"r"(tmem_d), "l"(da), "l"(db), "r"(kIdesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(saddr(bar)) : "memory");
+}
+
+struct TcParams {
+    float *c;
+    const float *residual;
+    int M, N, K;
+    DeviceStatus *status;
+};
+
+__global__ void __launch_bounds__(kTcThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constant__ CUtensorMap map_alo,
+               const __grid_constant__ CUtensorMap map_b, const TcParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    // the 128-byte swizzle pattern repeats every 1024 bytes: tiles must start on that boundary
+    unsigned char *tiles = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    __shared__ uint64_t full[kStages], empty[kStages], done;
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int failed;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int m0 = blockIdx.y * kBM, n0 = blockIdx.x * kBN;
+    const int nkb = (p.K + kBK - 1) / kBK;
+
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            bar_init(&full[s], 1);
+            bar_init(&empty[s], 1);
+        }
+        bar_init(&done, 1);
+        failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {  // tensor memory: kBN columns of 128 lanes x 32 bits
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(saddr(&tmem_base_s)), "r"(kBN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_s;
+
+    if (tid == 0) {
+        // ---- producer ----
+        for (int kb = 0; kb < nkb; ++kb) {
+            const int s = kb % kStages;
+            if (kb >= kStages && !bar_wait(&empty[s], (uint32_t)((kb / kStages - 1) & 1), p.status, 500)) {
+                failed = 1;
+                break;
+            }
+            unsigned char *st = tiles + (size_t)s * kStageBytes;
+            bar_expect(&full[s], kStageBytes);
+            tma_load_2d(st, &map_ahi, kb * kBK, m0, &full[s]);
+            tma_load_2d(st + kABytes, &map_alo, kb * kBK, m0, &full[s]);
+            tma_load_2d(st + 2 * kABytes, &map_b, kb * kBK, n0, &full[s]);
+        }
+    } else if (tid == 32) {
+        // ---- MMA issuer ----
+        bool ok = true;
+        for (int kb = 0; kb < nkb && ok; ++kb) {
+            const int s = kb % kStages;
+            ok = bar_wait(&full[s], (uint32_t)((kb / kStages) & 1), p.status, 510);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t st = saddr(tiles + (size_t)s * kStageBytes);
+            const uint64_t dhi = smem_desc(st), dlo = smem_desc(st + kABytes), db = smem_desc(st + 2 * kABytes);
+#pragma unroll
+            for (int kk = 0; kk < kBK / 16; ++kk) {  // UMMA K = 16 bf16 = 32 bytes = 2 descriptor units
+                umma_bf16(tmem_base, dhi + 2 * kk, db + 2 * kk, (kb > 0 || kk > 0) ? 1u : 0u);
+                umma_bf16(tmem_base, dlo + 2 * kk, db + 2 * kk, 1u);
+            }
+            umma_commit(&empty[s]);  // arrives when the MMAs above have finished reading the stage
+        }
+        if (!ok) failed = 1;
+        umma_commit(&done);  // arrives when every MMA issued so far has completed
+    }
+    __syncwarp();
+    // ---- epilogue: all four warps ----
+    const bool have = bar_wait(&done, 0, p.status, 520);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (have && !failed) {
+        const int row = m0 + warp * 32 + lane;
+#pragma unroll 1
+        for (int c0 = 0; c0 < kBN; c0 += 32) {
+            uint32_t v[32];
+            const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0;
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, "
+                "%19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+                  "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
+                  "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+                  "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                : "r"(taddr)
+                : "memory");
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (row < p.M) {
+                float *crow = p.c + (size_t)row * p.N + n0 + c0;
+                const float *rrow = p.residual ? p.residual + (size_t)row * p.N + n0 + c0 : nullptr;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    if (n0 + c0 + j < p.N) {
+                        float x = __uint_as_float(v[j]);
+                        if (rrow) x = __fadd_rn(rrow[j], x);  // x + residual as `Tensor + Tensor` (arithmetic.rs:48-52)
+                        crow[j] = x;
+                    }
+                }
+            }
+        }
+    } else if (tid == 0) {
+        // A wait gave up: let the copies that are still in flight land before the CTA exits (bounded).
+        for (int s = 0; s < kStages; ++s) {
+            const long long t0 = clock64();
+            while (!bar_try(&full[s], 0) && !bar_try(&full[s], 1) && clock64() - t0 < kTcWaitCycles) {}
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kBN) : "memory");
+}
+
+// hi = bf16(a), lo = bf16(a - hi)
+__global__ void split_bf16_kernel(const float *__restrict__ a, __nv_bfloat16 *__restrict__ hi, __nv_bfloat16 *__restrict__ lo, size_t n) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float x = a[i];
+    const __nv_bfloat16 h = __float2bfloat16_rn(x);
+    hi[i] = h;
+    lo[i] = __float2bfloat16_rn(x - __bfloat162float(h));
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// Row-major bf16 matrix [rows, K] -> map with box (kBK, box_rows), 128-byte swizzle, zero fill out of bounds.
+int make_map(lumen_ctx *ctx, CUtensorMap *map, const void *base, size_t rows, size_t K, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return set_error(ctx, LUMEN_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return set_error(ctx, LUMEN_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
+    return LUMEN_OK;
+}
+
+}  // namespace
+
+bool gemm_tc_usable(lumen_dtype wdt, size_t M, size_t K, size_t N, const void *w) {
+    static const bool off = [] {
+        const char *e = getenv("LUMEN_NO_TC");
+        return e && e[0] == '1';
+    }();
+    // TMA: 16-byte aligned base and row pitch (K * 2 bytes)
+    return !off && wdt == LUMEN_BF16 && M > 8 && N >= 8 && K % 8 == 0 && K >= 8 && (reinterpret_cast<uintptr_t>(w) & 15) == 0;
+}
+
+int launch_gemm_tc(lumen_ctx *ctx, const float *a, const void *w, float *c, size_t M, size_t K, size_t N, const float *residual,
+                   cudaStream_t s) {
+    void *split = nullptr;
+    const size_t n = M * K;
+    LUMEN_TRY(dev_alloc(ctx, 2 * n * sizeof(__nv_bfloat16) + 32, &split));
+    __nv_bfloat16 *hi = static_cast<__nv_bfloat16 *>(split);
+    __nv_bfloat16 *lo = hi + ((n + 7) & ~(size_t)7);  // keeps the second matrix 16-byte aligned
+    split_bf16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(a, hi, lo, n);
+    LUMEN_LAUNCHED(ctx);
+    CUtensorMap map_hi, map_lo, map_b;
+    int rc = make_map(ctx, &map_hi, hi, M, K, kBM);
+    if (rc == LUMEN_OK) rc = make_map(ctx, &map_lo, lo, M, K, kBM);
+    if (rc == LUMEN_OK) rc = make_map(ctx, &map_b, w, N, K, kBN);
+    if (rc == LUMEN_OK) {
+        constexpr size_t smem = (size_t)kStages * kStageBytes + 1024;  // + slack for the 1024-byte alignment
+        static bool attr_set[64] = {false};
+        const int dev = ctx->device >= 0 && ctx->device < 64 ? ctx->device : 0;
+        if (!attr_set[dev]) {
+            cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) rc = cuda_fail(ctx, e, "cudaFuncSetAttribute(gemm_tc_kernel)");
+            attr_set[dev] = true;
+        }
+        if (rc == LUMEN_OK) {
+            TcParams p{c, residual, (int)M, (int)N, (int)K, ctx->d_status};
+            dim3 grid((unsigned)((N + kBN - 1) / kBN), (unsigned)((M + kBM - 1) / kBM));
+            gemm_tc_kernel<<<grid, kTcThreads, smem, s>>>(map_hi, map_lo, map_b, p);
+            cudaError_t e = cudaGetLastError();
+            if (e != cudaSuccess) rc = cuda_fail(ctx, e, "gemm_tc_kernel launch");
+            else ctx->launches += 1;
+        }
+    }
+    int rc2 = dev_free(ctx, split);
+    return rc != LUMEN_OK ? rc : rc2;
+}
+
+}  // namespace lumen
