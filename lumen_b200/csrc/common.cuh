@@ -167,11 +167,11 @@ int launch_gemv_kn(lumen_ctx *ctx, const float *x, const void *w, lumen_dtype wd
 // C[M,N] = A[M,K] . W[N,K]^T, any M (f32 SIMT tiles; bf16 weights are widened on load).
 int launch_gemm_nk(lumen_ctx *ctx, const float *a, const void *w, lumen_dtype wdt, float *c, size_t M, size_t K,
                    size_t N, const float *residual, cudaStream_t s);
-// The same product on the tensor cores (tcgen05, accumulator in tensor memory) for bf16 weights and M > 8;
+// The same product on the tensor cores (tcgen05, accumulator in tensor memory) for M > 8;
 // launch_gemm_nk takes this path whenever gemm_tc_usable says so.
 bool gemm_tc_usable(lumen_dtype wdt, size_t M, size_t K, size_t N, const void *w);
-int launch_gemm_tc(lumen_ctx *ctx, const float *a, const void *w, float *c, size_t M, size_t K, size_t N, const float *residual,
-                   cudaStream_t s);
+int launch_gemm_tc(lumen_ctx *ctx, const float *a, const void *w, lumen_dtype wdt, float *c, size_t M, size_t K, size_t N,
+                   const float *residual, cudaStream_t s);
 
 int launch_rmsnorm(lumen_ctx *ctx, const float *x, const float *w, float eps, float *out, size_t rows, size_t dim,
                    cudaStream_t s);

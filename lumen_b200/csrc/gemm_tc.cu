@@ -1,5 +1,5 @@
 // C[M,N] = A[M,K] . W[N,K]^T (+ residual) on the 5th-generation tensor cores, for the M > 8 branch of
-// ops::matmul (src/ops/matmul.rs:70-92: prefill and batched decode) when W is stored as bf16.
+// ops::matmul (src/ops/matmul.rs:70-92: prefill and batched decode), for bf16 and for f32 weights.
 //
 // sm_100a structure: one CTA per 128 x 128 output tile; thread 0 is the TMA producer (2-D tiled copies
 // with 128-byte swizzle into a 4-stage shared-memory ring, mbarrier transaction counts), thread 32 issues
@@ -10,7 +10,9 @@
 // The activations are f32 in the reference.  They are split into two bf16 matrices, hi = bf16(a) and
 // lo = bf16(a - hi), and both products accumulate into the same tensor-memory tile: a = hi + lo to about
 // 2^-17 relative, so the result stays within ~1e-5 of the f32 product instead of the ~4e-3 a single bf16
-// rounding of the activations would cost, at twice the (cheap) tensor-core work.
+// rounding of the activations would cost, at twice the (cheap) tensor-core work.  f32 weights (the
+// reference's own dtype) are split the same way on the fly and three cross products are accumulated
+// (a_hi.w_hi + a_lo.w_hi + a_hi.w_lo; the dropped a_lo.w_lo term is ~2^-18).
 //
 // Every wait is bounded; a wait that gives up records LUMEN_ERR_TIMEOUT, the CTA stops issuing, lets the
 // copies in flight land, frees its tensor memory and returns.
@@ -22,10 +24,15 @@ namespace lumen {
 namespace {
 
 constexpr int kBM = 128, kBN = 128, kBK = 64;  // tile; kBK bf16 = one 128-byte swizzle row
-constexpr int kStages = 4;
 constexpr int kTcThreads = 128;
 constexpr uint32_t kABytes = kBM * kBK * 2, kBBytes = kBN * kBK * 2;
-constexpr uint32_t kStageBytes = 2 * kABytes + kBBytes;  // A hi, A lo, B
+// WSPLIT = false: bf16 weights, a stage holds A hi, A lo, B (48 KB, 4 stages).
+// WSPLIT = true : f32 weights split like the activations, a stage holds A hi, A lo, B hi, B lo (64 KB, 3 stages).
+template <bool WSPLIT>
+struct TcGeom {
+    static constexpr int kStages = WSPLIT ? 3 : 4;
+    static constexpr uint32_t kStageBytes = 2 * kABytes + (WSPLIT ? 2 : 1) * kBBytes;
+};
 constexpr long long kTcWaitCycles = 200000000LL;         // ~0.1 s
 
 __device__ __forceinline__ uint32_t saddr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -84,9 +91,12 @@ struct TcParams {
     DeviceStatus *status;
 };
 
+template <bool WSPLIT>
 __global__ void __launch_bounds__(kTcThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constant__ CUtensorMap map_alo,
-               const __grid_constant__ CUtensorMap map_b, const TcParams p) {
+               const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_blo, const TcParams p) {
+    constexpr int kStages = TcGeom<WSPLIT>::kStages;
+    constexpr uint32_t kStageBytes = TcGeom<WSPLIT>::kStageBytes;
     extern __shared__ unsigned char smem_raw[];
     // the 128-byte swizzle pattern repeats every 1024 bytes: tiles must start on that boundary
     unsigned char *tiles = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -128,6 +138,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constan
             tma_load_2d(st, &map_ahi, kb * kBK, m0, &full[s]);
             tma_load_2d(st + kABytes, &map_alo, kb * kBK, m0, &full[s]);
             tma_load_2d(st + 2 * kABytes, &map_b, kb * kBK, n0, &full[s]);
+            if (WSPLIT) tma_load_2d(st + 2 * kABytes + kBBytes, &map_blo, kb * kBK, n0, &full[s]);
         }
     } else if (tid == 32) {
         // ---- MMA issuer ----
@@ -139,10 +150,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constan
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t st = saddr(tiles + (size_t)s * kStageBytes);
             const uint64_t dhi = smem_desc(st), dlo = smem_desc(st + kABytes), db = smem_desc(st + 2 * kABytes);
+            const uint64_t dblo = smem_desc(st + 2 * kABytes + kBBytes);
 #pragma unroll
             for (int kk = 0; kk < kBK / 16; ++kk) {  // UMMA K = 16 bf16 = 32 bytes = 2 descriptor units
                 umma_bf16(tmem_base, dhi + 2 * kk, db + 2 * kk, (kb > 0 || kk > 0) ? 1u : 0u);
                 umma_bf16(tmem_base, dlo + 2 * kk, db + 2 * kk, 1u);
+                if (WSPLIT) umma_bf16(tmem_base, dhi + 2 * kk, dblo + 2 * kk, 1u);  // (a_lo . w_lo ~ 2^-18: dropped)
             }
             umma_commit(&empty[s]);  // arrives when the MMAs above have finished reading the stage
         }
@@ -238,44 +251,68 @@ int make_map(lumen_ctx *ctx, CUtensorMap *map, const void *base, size_t rows, si
 }  // namespace
 
 bool gemm_tc_usable(lumen_dtype wdt, size_t M, size_t K, size_t N, const void *w) {
-    static const bool off = [] {
+    static const int mode = [] {  // LUMEN_NO_TC=1: never; LUMEN_NO_TC=f32: bf16 weights only
         const char *e = getenv("LUMEN_NO_TC");
-        return e && e[0] == '1';
+        return !e ? 0 : (e[0] == '1' ? 1 : 2);
     }();
+    if (mode == 1 || (mode == 2 && wdt == LUMEN_F32)) return false;
     // TMA: 16-byte aligned base and row pitch (K * 2 bytes)
-    return !off && wdt == LUMEN_BF16 && M > 8 && N >= 8 && K % 8 == 0 && K >= 8 && (reinterpret_cast<uintptr_t>(w) & 15) == 0;
+    return M > 8 && N >= 8 && K % 8 == 0 && K >= 8 && (reinterpret_cast<uintptr_t>(w) & 15) == 0;
 }
 
-int launch_gemm_tc(lumen_ctx *ctx, const float *a, const void *w, float *c, size_t M, size_t K, size_t N, const float *residual,
-                   cudaStream_t s) {
-    void *split = nullptr;
-    const size_t n = M * K;
-    LUMEN_TRY(dev_alloc(ctx, 2 * n * sizeof(__nv_bfloat16) + 32, &split));
-    __nv_bfloat16 *hi = static_cast<__nv_bfloat16 *>(split);
-    __nv_bfloat16 *lo = hi + ((n + 7) & ~(size_t)7);  // keeps the second matrix 16-byte aligned
-    split_bf16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(a, hi, lo, n);
+namespace {
+
+template <bool WSPLIT>
+int launch_tc_kernel(lumen_ctx *ctx, const CUtensorMap &mhi, const CUtensorMap &mlo, const CUtensorMap &mb, const CUtensorMap &mblo,
+                     const TcParams &p, size_t M, size_t N, cudaStream_t s) {
+    constexpr size_t smem = (size_t)TcGeom<WSPLIT>::kStages * TcGeom<WSPLIT>::kStageBytes + 1024;  // + slack for the alignment
+    static bool attr_set[64] = {false};
+    const int dev = ctx->device >= 0 && ctx->device < 64 ? ctx->device : 0;
+    if (!attr_set[dev]) {
+        LUMEN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<WSPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_set[dev] = true;
+    }
+    dim3 grid((unsigned)((N + kBN - 1) / kBN), (unsigned)((M + kBM - 1) / kBM));
+    gemm_tc_kernel<WSPLIT><<<grid, kTcThreads, smem, s>>>(mhi, mlo, mb, mblo, p);
     LUMEN_LAUNCHED(ctx);
-    CUtensorMap map_hi, map_lo, map_b;
-    int rc = make_map(ctx, &map_hi, hi, M, K, kBM);
+    return LUMEN_OK;
+}
+
+}  // namespace
+
+// wdt == LUMEN_F32: the weights are split into hi + lo bf16 matrices on the fly as well (one streaming pass
+// over W per call) and three of the four cross products are accumulated.
+int launch_gemm_tc(lumen_ctx *ctx, const float *a, const void *w, lumen_dtype wdt, float *c, size_t M, size_t K, size_t N,
+                   const float *residual, cudaStream_t s) {
+    const bool wsplit = wdt == LUMEN_F32;
+    void *split = nullptr;
+    const size_t na = M * K, nap = (na + 7) & ~(size_t)7, nw = wsplit ? N * K : 0, nwp = (nw + 7) & ~(size_t)7;
+    LUMEN_TRY(dev_alloc(ctx, (2 * nap + 2 * nwp) * sizeof(__nv_bfloat16) + 32, &split));
+    __nv_bfloat16 *hi = static_cast<__nv_bfloat16 *>(split);
+    __nv_bfloat16 *lo = hi + nap;  // every matrix stays 16-byte aligned
+    __nv_bfloat16 *whi = lo + nap, *wlo = whi + nwp;
+    split_bf16_kernel<<<(unsigned)((na + 255) / 256), 256, 0, s>>>(a, hi, lo, na);
+    int rc = LUMEN_OK;
+    {
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) rc = cuda_fail(ctx, e, "split_bf16_kernel launch");
+        else ctx->launches += 1;
+    }
+    if (rc == LUMEN_OK && wsplit) {
+        split_bf16_kernel<<<(unsigned)((nw + 255) / 256), 256, 0, s>>>(static_cast<const float *>(w), whi, wlo, nw);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) rc = cuda_fail(ctx, e, "split_bf16_kernel launch");
+        else ctx->launches += 1;
+    }
+    CUtensorMap map_hi, map_lo, map_b, map_blo;
+    if (rc == LUMEN_OK) rc = make_map(ctx, &map_hi, hi, M, K, kBM);
     if (rc == LUMEN_OK) rc = make_map(ctx, &map_lo, lo, M, K, kBM);
-    if (rc == LUMEN_OK) rc = make_map(ctx, &map_b, w, N, K, kBN);
+    if (rc == LUMEN_OK) rc = make_map(ctx, &map_b, wsplit ? (const void *)whi : w, N, K, kBN);
+    if (rc == LUMEN_OK) rc = make_map(ctx, &map_blo, wsplit ? (const void *)wlo : w, N, K, kBN);
     if (rc == LUMEN_OK) {
-        constexpr size_t smem = (size_t)kStages * kStageBytes + 1024;  // + slack for the 1024-byte alignment
-        static bool attr_set[64] = {false};
-        const int dev = ctx->device >= 0 && ctx->device < 64 ? ctx->device : 0;
-        if (!attr_set[dev]) {
-            cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (e != cudaSuccess) rc = cuda_fail(ctx, e, "cudaFuncSetAttribute(gemm_tc_kernel)");
-            attr_set[dev] = true;
-        }
-        if (rc == LUMEN_OK) {
-            TcParams p{c, residual, (int)M, (int)N, (int)K, ctx->d_status};
-            dim3 grid((unsigned)((N + kBN - 1) / kBN), (unsigned)((M + kBM - 1) / kBM));
-            gemm_tc_kernel<<<grid, kTcThreads, smem, s>>>(map_hi, map_lo, map_b, p);
-            cudaError_t e = cudaGetLastError();
-            if (e != cudaSuccess) rc = cuda_fail(ctx, e, "gemm_tc_kernel launch");
-            else ctx->launches += 1;
-        }
+        TcParams p{c, residual, (int)M, (int)N, (int)K, ctx->d_status};
+        rc = wsplit ? launch_tc_kernel<true>(ctx, map_hi, map_lo, map_b, map_blo, p, M, N, s)
+                    : launch_tc_kernel<false>(ctx, map_hi, map_lo, map_b, map_blo, p, M, N, s);
     }
     int rc2 = dev_free(ctx, split);
     return rc != LUMEN_OK ? rc : rc2;

@@ -62,20 +62,23 @@ def test_matmul_m_gt_1(L, oracle, m, bf16):
         w = oracle.round_bf16(w)
     wt = L.Tensor.from_bf16(w) if bf16 else L.Tensor.from_array_no_grad(w)
     got = L.matmul(L.Tensor.from_array_no_grad(a), wt).data()
-    # bf16 weights with M > 8 run on the tensor cores with the activations split into two bf16 terms
-    # (a = hi + lo to ~2^-17), f32 accumulation: a few 1e-6 instead of f32 rounding
-    assert rel_err(got, oracle.matmul(a, w, "f64")) < (2e-5 if (bf16 and m > 8) else 2e-6)
+    # M > 8 runs on the tensor cores with the f32 operands split into two bf16 terms each
+    # (x = hi + lo to ~2^-17), f32 accumulation: a few 1e-6 instead of f32 rounding
+    assert rel_err(got, oracle.matmul(a, w, "f64")) < (2e-5 if m > 8 else 2e-6)
 
 
+@pytest.mark.parametrize("bf16", [True, False])
 @pytest.mark.parametrize("m,k,n", [(9, 64, 8), (32, 2048, 2560), (130, 200, 150), (512, 4096, 1000), (257, 5632, 2048), (64, 72, 136)])
-def test_tensor_core_gemm_shapes(L, oracle, m, k, n):
+def test_tensor_core_gemm_shapes(L, oracle, m, k, n, bf16):
     """tcgen05 path (bf16 weights, M > 8): tile edges in M, N and K (K not a multiple of the 64-element block,
     M and N not multiples of 128), several K blocks more than ring stages, and against the SIMT path."""
     import os
     rng = np.random.default_rng(m + k + n)
     a = rng.standard_normal((m, k), dtype=np.float32)
-    w = oracle.round_bf16(rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.05))
-    wt = L.Tensor.from_bf16(w)
+    w = rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.05)
+    if bf16:
+        w = oracle.round_bf16(w)
+    wt = L.Tensor.from_bf16(w) if bf16 else L.Tensor.from_array_no_grad(w)  # f32 weights are split on the fly
     got = L.matmul(L.Tensor.from_array_no_grad(a), wt).data()
     want = a.astype(np.float64) @ w.astype(np.float64).T
     assert got.shape == (m, n)
