@@ -827,7 +827,11 @@ __device__ __forceinline__ bool gemv_phase(const MegaParams &p, Shared &sh, cons
             const long row = ti.r0 + row0_blk + tid;
             const uint32_t tag = phase_tag(p, ph);
             switch (g.kind) {
-                case PH_QKV: st_tagged(p.qkvT + row, tot, tag); break;
+                case PH_QKV:
+                    // debug bit 3: the first phase of the token publishes nothing, so that every wait on it
+                    // runs into its limit (used to test the time-out path; nothing faults or hangs)
+                    if (!((p.debug_flags & 8) && ph == 0)) st_tagged(p.qkvT + row, tot, tag);
+                    break;
                 case PH_O:      // h = x + attn_out                                   llama.rs:110
                 case PH_DOWN: { // out = h + mlp_out                                  llama.rs:115
                     // (these phases have a single row block: see the launcher)

@@ -68,6 +68,7 @@ struct MegaParams {
     int l2_ahead;  // copies the producer's L2 prefetch runs ahead of the copy it issues (0 = off)
     // bit 0: stream no weight tiles (measures the exchange + prologue chain alone; results are wrong)
     // bit 2: wait for the weight tiles but skip the arithmetic on them
+    // bit 3: the first phase publishes nothing: every wait on it gives up after its limit (time-out test)
     int debug_flags;
 };
 
