@@ -428,6 +428,24 @@ def main():
         barrier()
         e2e_wall_ms = (time.perf_counter() - t0) * 1000.0
         e2e_ms = max_over_ranks(max(e0.elapsed_time(e1), e2e_wall_ms))
+
+        # ---- the same steps with the sampler on the device: only a token id comes back (single GPU) --------
+        sampled_ms = None
+        if world == 1:
+            prefill()
+            pos = PROMPT_LEN
+            recent = [int(t) for t in ids[:PROMPT_LEN]]
+            urand = np.random.default_rng(7).random(args.warmup + args.steps)
+            for i in range(args.warmup):
+                model.forward_sample(ids[None, pos:pos + 1], caches, 0.8, 0.9, 1.1, recent[-96:], float(urand[i]))
+                pos += 1
+            barrier()
+            t0 = time.perf_counter()
+            for i in range(args.steps):  # teacher-forced like the other loops: the sampled id is read but not fed back
+                model.forward_sample(ids[None, pos:pos + 1], caches, 0.8, 0.9, 1.1, recent[-96:], float(urand[args.warmup + i]))
+                pos += 1
+            barrier()
+            sampled_ms = (time.perf_counter() - t0) * 1000.0
     sampler.stop()
 
     tps = args.steps / (dev_ms / 1000.0)
@@ -445,6 +463,11 @@ def main():
                    "l2": "inputs larger than L2: every step streams %.2f GB of weights" % (weight_bytes / 1e9)},
         "e2e": {"value": e2e_tps, "unit": UNIT, "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4 * cfg["vocab_size"],
                 "ms_per_step": e2e_ms / args.steps},
+        "e2e_sampled": (None if sampled_ms is None else
+                        {"value": args.steps / (sampled_ms / 1000.0), "unit": UNIT, "h2d_bytes_per_step": 4 + 4 * 96,
+                         "d2h_bytes_per_step": 4, "ms_per_step": sampled_ms / args.steps,
+                         "note": "forward + top-p sampling on the device (temperature 0.8, top_p 0.9, repetition penalty 1.1 "
+                                 "over 96 tokens): the reference samples on the host from the full logits"}),
         "gpu_launches": int(launches),
         "clocks": sampler.summary(),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,

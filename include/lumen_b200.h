@@ -226,6 +226,26 @@ int lumen_llama_forward_last(lumen_llama *m, const float *ids_host, size_t b, si
                              size_t n_caches, size_t pos, float *logits_host);
 int lumen_llama_forward_device(lumen_llama *m, const float *ids_dev, size_t b, size_t s, lumen_kv_cache **caches,
                                size_t n_caches, float *logits_dev);
+/* sample_top_p of the reference's chat loop (src/main.rs:74-137) on the device: repetition penalty over
+ * `recent_tokens` (one division per occurrence, only when the penalty is > 1), temperature (floored at 1e-5),
+ * softmax, stable descending sort, nucleus cut at top_p, inverse-CDF walk with `uniform` in [0,1) (the
+ * reference draws it from its thread RNG, :69-72; here the caller supplies it so that runs can be repeated).
+ * recent_tokens is a HOST array of at most 256 ids.
+ * lumen_sample_top_p        : logits_dev[vocab] (device) -> *token_out (host); synchronises.
+ * lumen_llama_forward_sample: LlamaModel::forward on ids[1,S] followed by the sampler on the last position's
+ *                             logits, as main.rs:334-372 does on the host; only the token id is copied back. */
+typedef struct {
+    float temperature;
+    float top_p;
+    float repetition_penalty;
+    const int32_t *recent_tokens;
+    size_t n_recent;
+    float uniform;
+} lumen_sample_params;
+int lumen_sample_top_p(lumen_ctx *ctx, const float *logits_dev, size_t vocab, const lumen_sample_params *params,
+                       int32_t *token_out);
+int lumen_llama_forward_sample(lumen_llama *m, const float *ids_host, size_t s, lumen_kv_cache **caches, size_t n_caches,
+                               const lumen_sample_params *params, int32_t *token_out);
 int lumen_llama_free(lumen_llama *m);
 /* Bytes of weights one decode step streams on this rank (for roofline accounting). */
 size_t lumen_llama_weight_bytes(const lumen_llama *m);

@@ -17,6 +17,13 @@ F32, BF16 = 0, 1
 NCCL_ID_BYTES = 128
 
 
+class SampleParamsC(C.Structure):
+    """`lumen_sample_params` (arguments of sample_top_p, src/main.rs:74-80, plus the uniform draw)."""
+
+    _fields_ = [("temperature", C.c_float), ("top_p", C.c_float), ("repetition_penalty", C.c_float),
+                ("recent_tokens", C.POINTER(C.c_int32)), ("n_recent", C.c_size_t), ("uniform", C.c_float)]
+
+
 class LlamaConfigC(C.Structure):
     """`lumen_llama_config` (LlamaConfig, src/models/llama.rs:11-21, + head_dim, qk_norm, weight_dtype)."""
 
@@ -95,6 +102,8 @@ PROTOTYPES = {
     "lumen_llama_forward": (_I, [_P, _FP, _SZ, _SZ, _PP, _SZ, _SZ, _FP]),
     "lumen_llama_forward_last": (_I, [_P, _FP, _SZ, _SZ, _PP, _SZ, _SZ, _FP]),
     "lumen_llama_forward_device": (_I, [_P, _FP, _SZ, _SZ, _PP, _SZ, _FP]),
+    "lumen_sample_top_p": (_I, [_P, _FP, _SZ, C.POINTER(SampleParamsC), C.POINTER(C.c_int32)]),
+    "lumen_llama_forward_sample": (_I, [_P, _FP, _SZ, _PP, _SZ, C.POINTER(SampleParamsC), C.POINTER(C.c_int32)]),
     "lumen_llama_free": (_I, [_P]),
     "lumen_llama_weight_bytes": (_SZ, [_P]),
     "lumen_llama_decode_trace": (_I, [_P, C.POINTER(C.c_uint64), _SZ, _SZP]),

@@ -666,6 +666,32 @@ int lumen_llama_forward_last(lumen_llama *m, const float *ids_host, size_t b, si
     return forward_host(m, ids_host, b, s, caches, n_caches, logits_host, true);
 }
 
+int lumen_llama_forward_sample(lumen_llama *m, const float *ids_host, size_t s, lumen_kv_cache **caches, size_t n_caches,
+                               const lumen_sample_params *sp, int32_t *token_out) {
+    if (!m || !ids_host || !sp || !token_out || (sp->n_recent && !sp->recent_tokens)) return LUMEN_ERR_INVALID;
+    lumen_ctx *ctx = m->ctx;
+    if (m->is_set.size() < m->n_expected) return set_error(ctx, LUMEN_ERR_MISSING_PARAM, "%zu of %zu parameters set", m->is_set.size(), m->n_expected);
+    if (s == 0) return set_error(ctx, LUMEN_ERR_SHAPE, "forward_sample: empty input");
+    LUMEN_TRY(check_caches(m, 1, s, caches, n_caches));
+    for (size_t i = 0; i < s; ++i) {
+        const float f = ids_host[i];
+        if (f >= (float)m->V && f == f) return set_error(ctx, LUMEN_ERR_EMBED_RANGE, "Embedding index out of bounds: %.0f >= %zu", (double)f, m->V);
+    }
+    LUMEN_TRY(ensure_workspace(m, s));
+    Workspace &w = m->ws;
+    LUMEN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // the pinned staging buffer is reused every step
+    memcpy(w.h_ids, ids_host, s * sizeof(float));
+    LUMEN_CUDA(ctx, cudaMemcpyAsync(w.ids, w.h_ids, s * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+    LUMEN_TRY(run_forward(m, 1, s, caches, true));  // last position's logits in w.logits[V]
+    int *token_dev = reinterpret_cast<int *>(w.ids);  // the id buffer is free again once the forward is enqueued behind it
+    LUMEN_TRY(launch_sample_top_p(ctx, w.logits, m->V, sp->temperature, sp->top_p, sp->repetition_penalty, sp->recent_tokens,
+                                  sp->n_recent, sp->uniform, token_dev, ctx->stream));
+    LUMEN_CUDA(ctx, cudaMemcpyAsync(w.h_ids, token_dev, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    LUMEN_TRY(check_device_status(ctx));
+    memcpy(token_out, w.h_ids, sizeof(int));
+    return LUMEN_OK;
+}
+
 int lumen_llama_forward_device(lumen_llama *m, const float *ids_dev, size_t b, size_t s, lumen_kv_cache **caches, size_t n_caches,
                                float *logits_dev) {
     if (!m || !ids_dev || !logits_dev) return LUMEN_ERR_INVALID;

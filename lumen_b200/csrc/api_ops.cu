@@ -185,6 +185,24 @@ int lumen_gemv(lumen_ctx *ctx, const float *x_dev, const void *w_dev, lumen_dtyp
     return rc != LUMEN_OK ? rc : rc2;
 }
 
+int lumen_sample_top_p(lumen_ctx *ctx, const float *logits_dev, size_t vocab, const lumen_sample_params *sp, int32_t *token_out) {
+    if (!ctx || !logits_dev || !sp || !token_out || (sp->n_recent && !sp->recent_tokens))
+        return set_error(ctx, LUMEN_ERR_INVALID, "sample_top_p: null argument");
+    void *tok = nullptr;
+    LUMEN_TRY(dev_alloc(ctx, 256, &tok));
+    int rc = launch_sample_top_p(ctx, logits_dev, vocab, sp->temperature, sp->top_p, sp->repetition_penalty, sp->recent_tokens,
+                                 sp->n_recent, sp->uniform, static_cast<int *>(tok), ctx->stream);
+    int32_t host = 0;
+    if (rc == LUMEN_OK) {
+        cudaError_t e = cudaMemcpyAsync(&host, tok, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream);
+        if (e != cudaSuccess) rc = cuda_fail(ctx, e, "cudaMemcpyAsync(token)");
+    }
+    if (rc == LUMEN_OK) rc = check_device_status(ctx);  // synchronises
+    int rc2 = dev_free(ctx, tok);
+    if (rc == LUMEN_OK) *token_out = host;
+    return rc != LUMEN_OK ? rc : rc2;
+}
+
 // ---- RotaryEmbedding ---------------------------------------------------------------------------------
 int lumen_rope_new(lumen_ctx *ctx, size_t dim, size_t max_seq_len, float theta, lumen_rope **out) {
     if (!ctx || !out) return LUMEN_ERR_INVALID;

@@ -228,6 +228,10 @@ struct AttnPrefillArgs {
 };
 int launch_attn_prefill(lumen_ctx *ctx, const AttnPrefillArgs &a, cudaStream_t s);
 
+// Nucleus sampling of one logits vector on the device (sampler.cu); *token_dev is a device int.
+int launch_sample_top_p(lumen_ctx *ctx, const float *logits_dev, size_t vocab, float temperature, float top_p, float penalty,
+                        const int *recent_host, size_t n_recent, float r, int *token_dev, cudaStream_t s);
+
 // LlamaKVCache::update: dst[h, start+s, :] = src[h, s, :].
 int launch_kv_slab_copy(lumen_ctx *ctx, const float *src, float *dst, size_t heads, size_t s_len, size_t d,
                         size_t dst_seq_stride_rows, size_t start, int to_slab, cudaStream_t s);

@@ -205,6 +205,16 @@ class SelfAttention:
         return Tensor(out, self.ctx), cache
 
 
+def sample_top_p(ctx: Context, logits_ptr: int, vocab: int, temperature: float, top_p: float, repetition_penalty: float,
+                 recent_tokens, uniform: float) -> int:
+    """`sample_top_p` (src/main.rs:74-137) on a device logits vector (`lumen_sample_top_p`)."""
+    rec = np.ascontiguousarray(recent_tokens, dtype=np.int32)
+    sp = _lib.SampleParamsC(temperature, top_p, repetition_penalty, rec.ctypes.data_as(C.POINTER(C.c_int32)), rec.size, uniform)
+    tok = C.c_int32()
+    ctx.check(ctx._lib.lumen_sample_top_p(ctx.h, logits_ptr, vocab, C.byref(sp), C.byref(tok)))
+    return int(tok.value)
+
+
 def attention_decode(ctx: Context, q_ptr: int, k_new_ptr: int, v_new_ptr: int, n_head: int, cache: KVCacheInner,
                      rope: RotaryEmbedding | None, out_ptr: int, causal: bool = True) -> None:
     """`lumen_attention_decode` on raw device pointers."""

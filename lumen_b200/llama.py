@@ -167,6 +167,20 @@ class LlamaModel:
         self.ctx.check(fn(self.h, ids.ctypes.data, b, s, self._cache_array(caches), len(caches), _pos, logits.ctypes.data))
         return logits
 
+    def forward_sample(self, input_ids, caches: list, temperature: float, top_p: float, repetition_penalty: float,
+                       recent_tokens, uniform: float) -> int:
+        """`forward` on ids [1,S] followed by `sample_top_p` (src/main.rs:74-137) on the device; returns the
+        sampled token id.  `uniform` is the draw in [0,1) the reference takes from its RNG."""
+        require_no_grad("LlamaModel::forward")
+        from ._lib import SampleParamsC
+        ids = np.ascontiguousarray(input_ids, dtype=np.float32).reshape(-1)
+        rec = np.ascontiguousarray(recent_tokens, dtype=np.int32)
+        sp = SampleParamsC(temperature, top_p, repetition_penalty, rec.ctypes.data_as(C.POINTER(C.c_int32)), rec.size, uniform)
+        tok = C.c_int32()
+        self.ctx.check(self.ctx._lib.lumen_llama_forward_sample(self.h, ids.ctypes.data, ids.size, self._cache_array(caches),
+                                                                len(caches), C.byref(sp), C.byref(tok)))
+        return int(tok.value)
+
     def forward_device(self, ids_ptr: int, b: int, s: int, caches: list, logits_ptr: int) -> None:
         """Same step with device-resident ids and logits, asynchronous on the context's stream."""
         require_no_grad("LlamaModel::forward")

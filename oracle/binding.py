@@ -154,6 +154,16 @@ def fused_softmax(x, scale, causal, prec="f32"):
     return out
 
 
+def sample_top_p(logits, temperature, top_p, repetition_penalty, recent_tokens, r) -> int:
+    """`sample_top_p` of src/main.rs:74-137 with the uniform draw `r` given."""
+    x = _f32(logits).ravel()
+    rec = np.ascontiguousarray(recent_tokens, dtype=np.int64)
+    f = lib().lo_sample_top_p
+    f.restype = C.c_long
+    return int(f(_p(x), C.c_long(x.size), C.c_float(temperature), C.c_float(top_p), C.c_float(repetition_penalty),
+                 rec.ctypes.data_as(C.c_void_p), C.c_long(rec.size), C.c_float(r)))
+
+
 def round_bf16(x):
     x = _f32(x)
     out = np.empty_like(x)

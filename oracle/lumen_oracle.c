@@ -91,6 +91,55 @@ void lo_round_bf16(const float *x, long n, float *out) {
     }
 }
 
+/* sample_top_p (src/main.rs:74-137) with the uniform draw `r` passed in (the reference draws it from its
+ * thread RNG, :69-72): repetition penalty over the recent tokens (one division per occurrence), temperature
+ * (floored at 1e-5), softmax with sequential f32 sums and 1/(sum + 1e-9), stable descending sort, nucleus cut
+ * at the first rank where the sequential cumulative sum reaches top_p (clamped to [1e-6, 1]), then the
+ * inverse-CDF walk over probs[i] / cumulative. */
+typedef struct { float p; long i; } lo_pi;
+static int lo_pi_cmp(const void *a, const void *b) {
+    const lo_pi *x = (const lo_pi *)a, *y = (const lo_pi *)b;
+    if (x->p > y->p) return -1;
+    if (x->p < y->p) return 1;
+    return (x->i > y->i) - (x->i < y->i); /* stable: ties keep index order */
+}
+long lo_sample_top_p(const float *logits, long n, float temperature, float top_p, float repetition_penalty,
+                     const long *recent, long n_recent, float r) {
+    float *adj = (float *)malloc(sizeof(float) * (size_t)n);
+    lo_pi *idx = (lo_pi *)malloc(sizeof(lo_pi) * (size_t)n);
+    for (long i = 0; i < n; ++i) adj[i] = logits[i];
+    if (repetition_penalty > 1.0f)
+        for (long k = 0; k < n_recent; ++k)
+            if (recent[k] >= 0 && recent[k] < n) adj[recent[k]] /= repetition_penalty;
+    const float temp = temperature > 1e-5f ? temperature : 1e-5f;
+    float maxv = -INFINITY;
+    for (long i = 0; i < n; ++i) { adj[i] /= temp; if (adj[i] > maxv) maxv = adj[i]; }
+    float sum = 0.0f;
+    for (long i = 0; i < n; ++i) { adj[i] = expf(adj[i] - maxv); sum += adj[i]; }
+    const float inv = 1.0f / (sum + 1e-9f);
+    for (long i = 0; i < n; ++i) { adj[i] *= inv; idx[i].p = adj[i]; idx[i].i = i; }
+    qsort(idx, (size_t)n, sizeof(lo_pi), lo_pi_cmp);
+    float target = top_p < 0.0f ? 0.0f : (top_p > 1.0f ? 1.0f : top_p);
+    if (target < 1e-6f) target = 1e-6f;
+    float cumulative = 0.0f;
+    long cut = 0;
+    for (long k = 0; k < n; ++k) {
+        cumulative += idx[k].p;
+        cut = k + 1;
+        if (cumulative >= target) break;
+    }
+    if (cut < 1) cut = 1;
+    float acc = 0.0f;
+    long out = idx[cut - 1].i;
+    for (long k = 0; k < cut; ++k) {
+        acc += idx[k].p / cumulative;
+        if (r <= acc) { out = idx[k].i; break; }
+    }
+    free(adj);
+    free(idx);
+    return out;
+}
+
 int lo_num_threads(void) {
     int n = 1;
 #ifdef _OPENMP
