@@ -467,7 +467,9 @@ def main():
                         {"value": args.steps / (sampled_ms / 1000.0), "unit": UNIT, "h2d_bytes_per_step": 4 + 4 * 96,
                          "d2h_bytes_per_step": 4, "ms_per_step": sampled_ms / args.steps,
                          "note": "forward + top-p sampling on the device (temperature 0.8, top_p 0.9, repetition penalty 1.1 "
-                                 "over 96 tokens): the reference samples on the host from the full logits"}),
+                                 "over 96 tokens): the reference samples on the host from the full logits.  Random weights give a flat "
+                                 "distribution whose nucleus holds ~90 % of the vocabulary, the worst case for the sequential "
+                                 "cumulative sum the sampler keeps for parity"}),
         "gpu_launches": int(launches),
         "clocks": sampler.summary(),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,

@@ -87,72 +87,61 @@ sample_prep_kernel(const float *__restrict__ logits, int n, float temperature, f
     }
 }
 
-// One warp: walks the sorted probabilities in chunks staged through shared memory; lane 0 adds them
-// sequentially (the reference's rounding), first to find the cut, then to find the drawn token.
+// The reference adds the sorted probabilities one by one in f32 and stops at the first index where the
+// running sum reaches a threshold (main.rs:113-121 and :126-134).  With a flat distribution the rounding of
+// that sequential sum decides the index, so the order of the additions is kept: the warp stages 1024 values at a
+// time in shared memory (dividing by `scale` on the way: 1 for the cumulative probability, the nucleus mass
+// for the inverse-CDF walk) and lane 0 adds them in order, eight per test of the threshold; the block of
+// eight that crosses is then walked value by value.  Returns the first index < n whose running sum is >=
+// threshold (n if none) and that running sum (the total if none).
+__device__ __forceinline__ int first_reaching(const float *__restrict__ vals, int n, float scale, float threshold, float *buf,
+                                              float *sum_out) {
+    constexpr int kChunk = 1024;
+    const int lane = threadIdx.x;
+    float run = 0.f;
+    int found = n;
+    for (int c0 = 0; c0 < n && found == n; c0 += kChunk) {
+        const int m = min(kChunk, n - c0);
+        for (int i = lane; i < kChunk; i += 32) buf[i] = i < m ? __fdiv_rn(vals[c0 + i], scale) : 0.f;  // zeros change no sum
+        __syncwarp();
+        if (lane == 0) {
+            for (int i = 0; i < m; i += 8) {
+                float t = run;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) t = __fadd_rn(t, buf[i + j]);
+                if (t >= threshold) {  // the sums only grow: the crossing is inside these eight
+                    for (int j = 0; j < 8 && i + j < m; ++j) {
+                        run = __fadd_rn(run, buf[i + j]);
+                        if (run >= threshold) {
+                            found = c0 + i + j;
+                            break;
+                        }
+                    }
+                    if (found != n) break;
+                    continue;  // (only the zero padding pushed t over the line: cannot happen, t == run then)
+                }
+                run = t;
+            }
+        }
+        found = __shfl_sync(0xffffffffu, found, 0);
+        __syncwarp();
+    }
+    *sum_out = __shfl_sync(0xffffffffu, run, 0);
+    return found;
+}
+
 __global__ void __launch_bounds__(32)
 sample_pick_kernel(const float *__restrict__ sorted_p, const int *__restrict__ sorted_i, int n, float top_p, float r,
                    int *__restrict__ token_out) {
-    constexpr int kChunk = 1024;
-    __shared__ float buf[kChunk];
-    __shared__ int s_cut, s_done;
-    __shared__ float s_cum;
-    const int lane = threadIdx.x;
+    __shared__ float buf[1024];
     const float target = fmaxf(fminf(fmaxf(top_p, 0.f), 1.f), 1e-6f);
-    if (lane == 0) {
-        s_cut = 0;
-        s_done = 0;
-        s_cum = 0.f;
-    }
-    __syncwarp();
-    for (int base = 0; base < n && !s_done; base += kChunk) {
-        const int m = min(kChunk, n - base);
-        for (int i = lane; i < m; i += 32) buf[i] = sorted_p[base + i];
-        __syncwarp();
-        if (lane == 0) {
-            float cum = s_cum;
-            int cut = s_cut;
-            for (int i = 0; i < m; ++i) {
-                cum = __fadd_rn(cum, buf[i]);
-                cut = base + i + 1;
-                if (cum >= target) {
-                    s_done = 1;
-                    break;
-                }
-            }
-            s_cum = cum;
-            s_cut = cut;
-        }
-        __syncwarp();
-    }
-    const int cut = max(s_cut, 1);
-    const float cumulative = s_cum;
-    if (lane == 0) s_done = 0;
-    __shared__ int s_pick;
-    __shared__ float s_acc;
-    if (lane == 0) {
-        s_pick = cut - 1;  // `*idxs.last()` when the walk never reaches r
-        s_acc = 0.f;
-    }
-    __syncwarp();
-    for (int base = 0; base < cut && !s_done; base += kChunk) {
-        const int m = min(kChunk, cut - base);
-        for (int i = lane; i < m; i += 32) buf[i] = sorted_p[base + i];
-        __syncwarp();
-        if (lane == 0) {
-            float acc = s_acc;
-            for (int i = 0; i < m; ++i) {
-                acc = __fadd_rn(acc, __fdiv_rn(buf[i], cumulative));
-                if (r <= acc) {
-                    s_pick = base + i;
-                    s_done = 1;
-                    break;
-                }
-            }
-            s_acc = acc;
-        }
-        __syncwarp();
-    }
-    if (lane == 0) *token_out = sorted_i[s_pick];
+    float cumulative;
+    const int at = first_reaching(sorted_p, n, 1.0f, target, buf, &cumulative);  // main.rs:113-121
+    const int cut = max(1, min(n, at + 1));
+    float acc;
+    // main.rs:126-134: acc += probs[i] / cumulative; the first i with r <= acc, else the last of the nucleus
+    const int pick = first_reaching(sorted_p, cut, cumulative, r, buf, &acc);
+    if (threadIdx.x == 0) *token_out = sorted_i[min(pick, cut - 1)];
 }
 
 }  // namespace
