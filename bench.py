@@ -100,8 +100,8 @@ class ClockSampler(threading.Thread):
 
 
 # dram__bytes_read + dram__bytes_write of one persistent-kernel launch divided by its algorithmic bytes,
-# from the ncu capture summarised in profiles/decode_mega_kernel_tinyllama_f32.md (973.0 MB / 967.3 MB).
-MEGA_TRAFFIC_RATIO = 1.006
+# from the ncu capture summarised in profiles/decode_mega_kernel_tinyllama_f32.md (973.6 MB / 967.3 MB).
+MEGA_TRAFFIC_RATIO = 1.0065
 
 
 WORKLOADS = {  # name -> (synth config, label, default weight dtype)
@@ -315,7 +315,11 @@ def main():
     ap.add_argument("--micro", choices=["gemv", "attn", "gemm"], default=None,
                     help="secondary measurements instead of the decode benchmark: the vector-matrix sweep or "
                          "decode attention over a static cache (one JSON line per case)")
+    ap.add_argument("--prompt-len", type=int, default=32,
+                    help="tokens of the (untimed) prefill; 32 is the metric's configuration, 512 BASELINE config 4's")
     args = ap.parse_args()
+    global PROMPT_LEN
+    PROMPT_LEN = args.prompt_len
     args.warmup = max(args.warmup, 3)
     if args.dtype is None:
         args.dtype = WORKLOADS[args.workload][2]
