@@ -127,12 +127,12 @@ def gen_params(cfg: dict, dtype: str, workload: str = "tinyllama"):
     return gen(LlamaConfig(**cfg), 0, std=0.02, round_bf16=(dtype == "bf16"))
 
 
-def algorithmic_bytes_per_step(cfg: dict, weight_bytes: int, ctx_len_mean: float, tp: int) -> float:
-    """Weights of this rank once + K/V rows of the context once per KV head + the embedding row + logits."""
-    d = cfg["hidden_size"] // cfg["num_attention_heads"]
+def algorithmic_bytes_per_step(cfg: dict, weight_bytes: int, ctx_len_mean: float, tp: int, batch: int = 1) -> float:
+    """Weights of this rank once + per sequence: K/V rows of the context once per KV head, the embedding row, logits."""
+    d = cfg.get("head_dim") or cfg["hidden_size"] // cfg["num_attention_heads"]
     hkv_local = max(1, cfg["num_key_value_heads"] // tp)
     kv = cfg["num_hidden_layers"] * 2 * hkv_local * d * 4 * (ctx_len_mean + 1)
-    return weight_bytes + kv + cfg["hidden_size"] * 4 + cfg["vocab_size"] * 4 / tp
+    return weight_bytes + batch * (kv + cfg["hidden_size"] * 4 + cfg["vocab_size"] * 4 / tp)
 
 
 def cpu_decode(cfg: dict, params: dict, ids: np.ndarray, budget_s: float, max_steps: int):
@@ -315,6 +315,9 @@ def main():
     ap.add_argument("--micro", choices=["gemv", "attn", "gemm"], default=None,
                     help="secondary measurements instead of the decode benchmark: the vector-matrix sweep or "
                          "decode attention over a static cache (one JSON line per case)")
+    ap.add_argument("--batch", type=int, default=1,
+                    help="independent sequences decoded per step (1 is the metric's configuration; larger batches run the "
+                         "per-operator kernels: tensor-core GEMMs and the tiled attention kernel)")
     ap.add_argument("--prompt-len", type=int, default=32,
                     help="tokens of the (untimed) prefill; 32 is the metric's configuration, 512 BASELINE config 4's")
     args = ap.parse_args()
@@ -358,13 +361,16 @@ def main():
         nccl_id = box[0]
     ctx = L.Context(local_rank, rank, world, nccl_id)
     model = L.LlamaModel(L.LlamaConfig(**cfg, weight_dtype=args.dtype), ctx)
-    keep_params = (rank == 0 and world == 1 and not args.no_cpu_baseline and not big)
+    B = max(1, args.batch)
+    keep_params = (rank == 0 and world == 1 and not args.no_cpu_baseline and not big and B == 1)
     params = {}
     for name, w in gen_params(cfg, args.dtype, args.workload):
         model.set_param(name, w)
         if keep_params:
             params[name] = w
-    ids = synth.token_ids(1, total + 1, cfg["vocab_size"])
+    # step-major ids [total + 1, B]: the B ids of one step are contiguous (B == 1: the plain stream)
+    ids_all = synth.token_ids(1, (total + 1) * B, cfg["vocab_size"]).reshape(total + 1, B)
+    ids = ids_all[:, 0].copy()
     weight_bytes = model.weight_bytes_per_step
     stream = torch.cuda.ExternalStream(ctx.stream, device=torch.device("cuda", local_rank))
     sampler = ClockSampler(local_rank)
@@ -383,21 +389,21 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    caches = model.init_kv_caches(1)
-    d_ids = L.Tensor.from_array_no_grad(ids, ctx)
-    d_logits = L.Tensor.from_array_no_grad(np.zeros(cfg["vocab_size"], np.float32), ctx)
+    caches = model.init_kv_caches(B)
+    d_ids = L.Tensor.from_array_no_grad(ids_all, ctx)
+    d_logits = L.Tensor.from_array_no_grad(np.zeros(B * cfg["vocab_size"], np.float32), ctx)
 
     def prefill():
         model.reset_kv_caches(caches)
         with L.no_grad():
-            model.forward(ids[None, :PROMPT_LEN], caches, 0, last_only=True)
+            model.forward(np.ascontiguousarray(ids_all[:PROMPT_LEN].T), caches, 0, last_only=True)
 
     # ---- device-resident throughput --------------------------------------------------------------------
     with L.no_grad():
         prefill()
         pos = PROMPT_LEN
         for _ in range(args.warmup):
-            model.forward_device(d_ids.data_ptr + 4 * pos, 1, 1, caches, d_logits.data_ptr)
+            model.forward_device(d_ids.data_ptr + 4 * B * pos, B, 1, caches, d_logits.data_ptr)
             pos += 1
         barrier()
         launches0 = ctx.launch_count
@@ -405,7 +411,7 @@ def main():
         sampler.active = True
         e0.record(stream)
         for _ in range(args.steps):
-            model.forward_device(d_ids.data_ptr + 4 * pos, 1, 1, caches, d_logits.data_ptr)
+            model.forward_device(d_ids.data_ptr + 4 * B * pos, B, 1, caches, d_logits.data_ptr)
             pos += 1
         e1.record(stream)
         barrier()
@@ -418,13 +424,13 @@ def main():
         pos = PROMPT_LEN
         host_logits = []
         for _ in range(args.warmup):
-            model.forward(ids[None, pos:pos + 1], caches)
+            model.forward(ids_all[pos][:, None], caches)
             pos += 1
         barrier()
         t0 = time.perf_counter()
         e0.record(stream)
         for _ in range(args.steps):
-            lg = model.forward(ids[None, pos:pos + 1], caches)
+            lg = model.forward(ids_all[pos][:, None], caches)
             if len(host_logits) < 4:
                 host_logits.append(lg[0, 0].copy())
             pos += 1
@@ -435,7 +441,7 @@ def main():
 
         # ---- the same steps with the sampler on the device: only a token id comes back (single GPU) --------
         sampled_ms = None
-        if world == 1:
+        if world == 1 and B == 1:
             prefill()
             pos = PROMPT_LEN
             recent = [int(t) for t in ids[:PROMPT_LEN]]
@@ -452,20 +458,20 @@ def main():
             sampled_ms = (time.perf_counter() - t0) * 1000.0
     sampler.stop()
 
-    tps = args.steps / (dev_ms / 1000.0)
-    e2e_tps = args.steps / (e2e_ms / 1000.0)
+    tps = B * args.steps / (dev_ms / 1000.0)
+    e2e_tps = B * args.steps / (e2e_ms / 1000.0)
     ctx_mean = PROMPT_LEN + args.warmup + (args.steps - 1) / 2.0
-    bytes_step = algorithmic_bytes_per_step(cfg, weight_bytes, ctx_mean, world)
+    bytes_step = algorithmic_bytes_per_step(cfg, weight_bytes, ctx_mean, world, B)
     peak, peak_kind = measured_hbm_peak()
     achieved = bytes_step / (dev_ms / args.steps / 1000.0) / 1e9
     line = {
         "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"{WORKLOADS[args.workload][1]}_{args.dtype}_batch1_decode", "weights": args.dtype, "batch": 1,
+        "config": {"workload": f"{WORKLOADS[args.workload][1]}_{args.dtype}_batch{B}_decode", "weights": args.dtype, "batch": B,
                    "prompt_len": PROMPT_LEN, "max_seq_len": max_seq, "parallelism": f"tp{world}",
                    "l2": "inputs larger than L2: every step streams %.2f GB of weights" % (weight_bytes / 1e9)},
-        "e2e": {"value": e2e_tps, "unit": UNIT, "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4 * cfg["vocab_size"],
+        "e2e": {"value": e2e_tps, "unit": UNIT, "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B * cfg["vocab_size"],
                 "ms_per_step": e2e_ms / args.steps},
         "e2e_sampled": (None if sampled_ms is None else
                         {"value": args.steps / (sampled_ms / 1000.0), "unit": UNIT, "h2d_bytes_per_step": 4 + 4 * 96,

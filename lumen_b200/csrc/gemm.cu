@@ -4,6 +4,8 @@
 // hands the product to ndarray's general_mat_mul.  That routine's summation order is third-party and
 // unpinned, so parity is to f32 rounding.  Used for prefill and for batches too large for the
 // vector-matrix kernel when the weights are f32 (bf16 weights are widened on load).
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace lumen {

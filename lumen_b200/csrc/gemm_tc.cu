@@ -23,15 +23,20 @@
 namespace lumen {
 namespace {
 
-constexpr int kBM = 128, kBN = 128, kBK = 64;  // tile; kBK bf16 = one 128-byte swizzle row
+constexpr int kBM = 128, kBK = 64;  // tile rows of A; kBK bf16 = one 128-byte swizzle row
 constexpr int kTcThreads = 128;
-constexpr uint32_t kABytes = kBM * kBK * 2, kBBytes = kBN * kBK * 2;
-// WSPLIT = false: bf16 weights, a stage holds A hi, A lo, B (48 KB, 4 stages).
-// WSPLIT = true : f32 weights split like the activations, a stage holds A hi, A lo, B hi, B lo (64 KB, 3 stages).
-template <bool WSPLIT>
+constexpr uint32_t kABytes = kBM * kBK * 2;
+// The tile is 128 x BN: BN = 128, or 64 / 32 for outputs narrower than that.
+// WSPLIT = false: bf16 weights, a stage holds A hi, A lo, B.
+// WSPLIT = true : f32 weights split like the activations, a stage holds A hi, A lo, B hi, B lo.
+template <bool WSPLIT, int BN>
 struct TcGeom {
-    static constexpr int kStages = WSPLIT ? 3 : 4;
+    static constexpr uint32_t kBBytes = BN * kBK * 2;
     static constexpr uint32_t kStageBytes = 2 * kABytes + (WSPLIT ? 2 : 1) * kBBytes;
+    static constexpr int kStages = (200 * 1024 / kStageBytes) > 6 ? 6 : (200 * 1024 / kStageBytes);
+    static constexpr int kTmemCols = BN < 32 ? 32 : BN;
+    // Instruction descriptor: f32 accumulator, bf16 A and B, both K-major, N and M of the tile.
+    static constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
 };
 constexpr long long kTcWaitCycles = 200000000LL;         // ~0.1 s
 
@@ -72,13 +77,10 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
     return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
            ((uint64_t)2 << 61);
 }
-// Instruction descriptor: f32 accumulator, bf16 A and B, both K-major, N and M of the tile.
-constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
-
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate) {
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
     asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
                  " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}"
-                 ::"r"(tmem_d), "l"(da), "l"(db), "r"(kIdesc), "r"(accumulate), "r"(0u) : "memory");
+                 ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(saddr(bar)) : "memory");
@@ -91,12 +93,13 @@ struct TcParams {
     DeviceStatus *status;
 };
 
-template <bool WSPLIT>
+template <bool WSPLIT, int BN>
 __global__ void __launch_bounds__(kTcThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constant__ CUtensorMap map_alo,
                const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_blo, const TcParams p) {
-    constexpr int kStages = TcGeom<WSPLIT>::kStages;
-    constexpr uint32_t kStageBytes = TcGeom<WSPLIT>::kStageBytes;
+    using Geom = TcGeom<WSPLIT, BN>;
+    constexpr int kStages = Geom::kStages, kBN = BN, kTmemCols = Geom::kTmemCols;
+    constexpr uint32_t kStageBytes = Geom::kStageBytes, kBBytes = Geom::kBBytes, kIdesc = Geom::kIdesc;
     extern __shared__ unsigned char smem_raw[];
     // the 128-byte swizzle pattern repeats every 1024 bytes: tiles must start on that boundary
     unsigned char *tiles = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -116,8 +119,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constan
         failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 0) {  // tensor memory: kBN columns of 128 lanes x 32 bits
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(saddr(&tmem_base_s)), "r"(kBN) : "memory");
+    if (warp == 0) {  // tensor memory: kBN (at least 32) columns of 128 lanes x 32 bits
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(saddr(&tmem_base_s)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -153,9 +156,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constan
             const uint64_t dblo = smem_desc(st + 2 * kABytes + kBBytes);
 #pragma unroll
             for (int kk = 0; kk < kBK / 16; ++kk) {  // UMMA K = 16 bf16 = 32 bytes = 2 descriptor units
-                umma_bf16(tmem_base, dhi + 2 * kk, db + 2 * kk, (kb > 0 || kk > 0) ? 1u : 0u);
-                umma_bf16(tmem_base, dlo + 2 * kk, db + 2 * kk, 1u);
-                if (WSPLIT) umma_bf16(tmem_base, dhi + 2 * kk, dblo + 2 * kk, 1u);  // (a_lo . w_lo ~ 2^-18: dropped)
+                umma_bf16(tmem_base, dhi + 2 * kk, db + 2 * kk, kIdesc, (kb > 0 || kk > 0) ? 1u : 0u);
+                umma_bf16(tmem_base, dlo + 2 * kk, db + 2 * kk, kIdesc, 1u);
+                if (WSPLIT) umma_bf16(tmem_base, dhi + 2 * kk, dblo + 2 * kk, kIdesc, 1u);  // (a_lo . w_lo ~ 2^-18: dropped)
             }
             umma_commit(&empty[s]);  // arrives when the MMAs above have finished reading the stage
         }
@@ -205,7 +208,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constan
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kBN) : "memory");
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
 }
 
 // hi = bf16(a), lo = bf16(a - hi)
@@ -262,20 +265,28 @@ bool gemm_tc_usable(lumen_dtype wdt, size_t M, size_t K, size_t N, const void *w
 
 namespace {
 
-template <bool WSPLIT>
+template <bool WSPLIT, int BN>
 int launch_tc_kernel(lumen_ctx *ctx, const CUtensorMap &mhi, const CUtensorMap &mlo, const CUtensorMap &mb, const CUtensorMap &mblo,
                      const TcParams &p, size_t M, size_t N, cudaStream_t s) {
-    constexpr size_t smem = (size_t)TcGeom<WSPLIT>::kStages * TcGeom<WSPLIT>::kStageBytes + 1024;  // + slack for the alignment
+    constexpr size_t smem = (size_t)TcGeom<WSPLIT, BN>::kStages * TcGeom<WSPLIT, BN>::kStageBytes + 1024;  // + slack for the alignment
     static bool attr_set[64] = {false};
     const int dev = ctx->device >= 0 && ctx->device < 64 ? ctx->device : 0;
     if (!attr_set[dev]) {
-        LUMEN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<WSPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        LUMEN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<WSPLIT, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attr_set[dev] = true;
     }
-    dim3 grid((unsigned)((N + kBN - 1) / kBN), (unsigned)((M + kBM - 1) / kBM));
-    gemm_tc_kernel<WSPLIT><<<grid, kTcThreads, smem, s>>>(mhi, mlo, mb, mblo, p);
+    dim3 grid((unsigned)((N + BN - 1) / BN), (unsigned)((M + kBM - 1) / kBM));
+    gemm_tc_kernel<WSPLIT, BN><<<grid, kTcThreads, smem, s>>>(mhi, mlo, mb, mblo, p);
     LUMEN_LAUNCHED(ctx);
     return LUMEN_OK;
+}
+
+// 128-wide tiles measured fastest even when they leave SMs without a CTA (M = 512, N = 4096: 331 TFLOP/s
+// with 128 CTAs of 128 x 128 against 228 with 256 CTAs of 128 x 64); narrower tiles only for narrow outputs.
+int pick_bn(size_t M, size_t N, int num_sms) {
+    (void)M;
+    (void)num_sms;
+    return N > 64 ? 128 : (N > 32 ? 64 : 32);
 }
 
 }  // namespace
@@ -307,12 +318,15 @@ int launch_gemm_tc(lumen_ctx *ctx, const float *a, const void *w, lumen_dtype wd
     CUtensorMap map_hi, map_lo, map_b, map_blo;
     if (rc == LUMEN_OK) rc = make_map(ctx, &map_hi, hi, M, K, kBM);
     if (rc == LUMEN_OK) rc = make_map(ctx, &map_lo, lo, M, K, kBM);
-    if (rc == LUMEN_OK) rc = make_map(ctx, &map_b, wsplit ? (const void *)whi : w, N, K, kBN);
-    if (rc == LUMEN_OK) rc = make_map(ctx, &map_blo, wsplit ? (const void *)wlo : w, N, K, kBN);
+    const int bn = pick_bn(M, N, ctx->num_sms);
+    if (rc == LUMEN_OK) rc = make_map(ctx, &map_b, wsplit ? (const void *)whi : w, N, K, bn);
+    if (rc == LUMEN_OK) rc = make_map(ctx, &map_blo, wsplit ? (const void *)wlo : w, N, K, bn);
     if (rc == LUMEN_OK) {
         TcParams p{c, residual, (int)M, (int)N, (int)K, ctx->d_status};
-        rc = wsplit ? launch_tc_kernel<true>(ctx, map_hi, map_lo, map_b, map_blo, p, M, N, s)
-                    : launch_tc_kernel<false>(ctx, map_hi, map_lo, map_b, map_blo, p, M, N, s);
+#define LUMEN_TC(WS, BN_) launch_tc_kernel<WS, BN_>(ctx, map_hi, map_lo, map_b, map_blo, p, M, N, s)
+        if (wsplit) rc = bn == 128 ? LUMEN_TC(true, 128) : bn == 64 ? LUMEN_TC(true, 64) : LUMEN_TC(true, 32);
+        else rc = bn == 128 ? LUMEN_TC(false, 128) : bn == 64 ? LUMEN_TC(false, 64) : LUMEN_TC(false, 32);
+#undef LUMEN_TC
     }
     int rc2 = dev_free(ctx, split);
     return rc != LUMEN_OK ? rc : rc2;

@@ -68,7 +68,8 @@ def test_matmul_m_gt_1(L, oracle, m, bf16):
 
 
 @pytest.mark.parametrize("bf16", [True, False])
-@pytest.mark.parametrize("m,k,n", [(9, 64, 8), (32, 2048, 2560), (130, 200, 150), (512, 4096, 1000), (257, 5632, 2048), (64, 72, 136)])
+@pytest.mark.parametrize("m,k,n", [(9, 64, 8), (32, 2048, 2560), (130, 200, 150), (512, 4096, 1000), (257, 5632, 2048), (64, 72, 136),
+                                   (64, 128, 40), (33, 64, 24)])
 def test_tensor_core_gemm_shapes(L, oracle, m, k, n, bf16):
     """tcgen05 path (bf16 weights, M > 8): tile edges in M, N and K (K not a multiple of the 64-element block,
     M and N not multiples of 128), several K blocks more than ring stages, and against the SIMT path."""
