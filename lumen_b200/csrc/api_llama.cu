@@ -185,7 +185,10 @@ int enqueue_forward(lumen_llama *m, const StepPlan &p, lumen_kv_cache **caches, 
     Workspace &w = m->ws;
     const size_t M = p.M, H = m->H, qkvd = m->qkv_rows;
     const lumen_dtype wdt = m->cfg.weight_dtype;
-    const bool vec = M <= 8 && M * std::max(H, std::max(m->inter_l, m->qd_l)) * 4 <= 200 * 1024;
+    // Row counts that take the streaming vector-matrix kernels: up to 8 rows over f32 weights, a single row over
+    // bf16 weights (from two rows on the tensor-core kernel with split K is faster there).
+    const size_t vec_rows = (wdt == LUMEN_BF16 && gemm_tc_usable(wdt, 2, H, H, m->lm_head)) ? 1 : 8;
+    const bool vec = M <= vec_rows && M * std::max(H, std::max(m->inter_l, m->qd_l)) * 4 <= 200 * 1024;
     const bool tp = ctx->tp_size > 1;
     const float eps = m->cfg.rms_norm_eps;
     const float scale = 1.0f / sqrtf((float)m->D);  // (head_dim as f32).sqrt().recip(), self_attention.rs:89
@@ -250,7 +253,7 @@ int enqueue_forward(lumen_llama *m, const StepPlan &p, lumen_kv_cache **caches, 
         rows = p.B;
     }
     float *lg = tp ? w.logits_local + (size_t)ctx->tp_rank * rows * m->vocab_l : w.logits;
-    if (rows <= 8 && rows * H * 4 <= 200 * 1024) {
+    if (rows <= vec_rows && rows * H * 4 <= 200 * 1024) {
         GemvArgs g;
         g.x = xin; g.w = m->lm_head; g.wdt = wdt; g.y = lg; g.M = (int)rows; g.K = H; g.N = m->vocab_l; g.ldy = m->vocab_l;
         g.norm_w = m->final_norm; g.norm_eps = eps;

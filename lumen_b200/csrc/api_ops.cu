@@ -29,7 +29,10 @@ namespace lumen {
 int matmul_dispatch(lumen_ctx *ctx, const float *a, const void *w, lumen_dtype wdt, float *y, size_t M, size_t K,
                     size_t N, const float *residual, cudaStream_t s) {
     if (M == 0 || N == 0) return LUMEN_OK;
-    if (M <= 8 && M * K * 4 <= 200 * 1024) {
+    // The streaming vector-matrix kernel takes up to 8 rows over f32 weights; over bf16 weights only a single row
+    // (from two rows on, the tensor-core kernel with split K is faster).
+    const size_t vec_rows = (wdt == LUMEN_BF16 && gemm_tc_usable(wdt, M, K, N, w)) ? 1 : 8;
+    if (M <= vec_rows && M * K * 4 <= 200 * 1024) {
         GemvArgs g;
         g.x = a; g.w = w; g.wdt = wdt; g.y = y; g.M = (int)M; g.K = K; g.N = N; g.ldy = N; g.residual = residual;
         return launch_gemv_nk(ctx, g, s);

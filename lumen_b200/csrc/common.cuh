@@ -167,7 +167,8 @@ int launch_gemv_kn(lumen_ctx *ctx, const float *x, const void *w, lumen_dtype wd
 // C[M,N] = A[M,K] . W[N,K]^T, any M (f32 SIMT tiles; bf16 weights are widened on load).
 int launch_gemm_nk(lumen_ctx *ctx, const float *a, const void *w, lumen_dtype wdt, float *c, size_t M, size_t K,
                    size_t N, const float *residual, cudaStream_t s);
-// The same product on the tensor cores (tcgen05, accumulator in tensor memory) for M > 8;
+// The same product on the tensor cores (tcgen05, accumulator in tensor memory) for M >= 2 (callers keep up to 8
+// rows over f32 weights on the streaming kernel);
 // launch_gemm_nk takes this path whenever gemm_tc_usable says so.
 bool gemm_tc_usable(lumen_dtype wdt, size_t M, size_t K, size_t N, const void *w);
 int launch_gemm_tc(lumen_ctx *ctx, const float *a, const void *w, lumen_dtype wdt, float *c, size_t M, size_t K, size_t N,

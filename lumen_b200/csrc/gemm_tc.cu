@@ -18,6 +18,8 @@
 // copies in flight land, frees its tensor memory and returns.
 #include <cuda.h>
 
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace lumen {
@@ -87,9 +89,10 @@ __device__ __forceinline__ void umma_commit(uint64_t *bar) {
 }
 
 struct TcParams {
-    float *c;
-    const float *residual;
+    float *c;               // output, or the [splits][M][N] partial sums when the K range is split over blockIdx.z
+    const float *residual;  // added in the epilogue (null with split K: the reduction kernel adds it)
     int M, N, K;
+    int kb_per_split;       // 64-element K blocks per blockIdx.z
     DeviceStatus *status;
 };
 
@@ -108,7 +111,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constan
     __shared__ int failed;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int m0 = blockIdx.y * kBM, n0 = blockIdx.x * kBN;
-    const int nkb = (p.K + kBK - 1) / kBK;
+    // This CTA's range of 64-element K blocks: all of them, or slice blockIdx.z when K is split over the grid
+    // (few output tiles and a long K: more CTAs stream the weights).  kb below counts from the slice's start.
+    const int kb_all = (p.K + kBK - 1) / kBK;
+    const int kb0 = (int)blockIdx.z * p.kb_per_split;
+    const int nkb = max(0, min(kb_all, kb0 + p.kb_per_split) - kb0);
 
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -138,10 +145,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constan
             }
             unsigned char *st = tiles + (size_t)s * kStageBytes;
             bar_expect(&full[s], kStageBytes);
-            tma_load_2d(st, &map_ahi, kb * kBK, m0, &full[s]);
-            tma_load_2d(st + kABytes, &map_alo, kb * kBK, m0, &full[s]);
-            tma_load_2d(st + 2 * kABytes, &map_b, kb * kBK, n0, &full[s]);
-            if (WSPLIT) tma_load_2d(st + 2 * kABytes + kBBytes, &map_blo, kb * kBK, n0, &full[s]);
+            const int kx = (kb0 + kb) * kBK;
+            tma_load_2d(st, &map_ahi, kx, m0, &full[s]);
+            tma_load_2d(st + kABytes, &map_alo, kx, m0, &full[s]);
+            tma_load_2d(st + 2 * kABytes, &map_b, kx, n0, &full[s]);
+            if (WSPLIT) tma_load_2d(st + 2 * kABytes + kBBytes, &map_blo, kx, n0, &full[s]);
         }
     } else if (tid == 32) {
         // ---- MMA issuer ----
@@ -172,6 +180,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constan
     __syncthreads();
     if (have && !failed) {
         const int row = m0 + warp * 32 + lane;
+        const bool empty_slice = nkb == 0;  // nothing was accumulated: the tile's contribution is zero
 #pragma unroll 1
         for (int c0 = 0; c0 < kBN; c0 += 32) {
             uint32_t v[32];
@@ -187,12 +196,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constan
                 : "memory");
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             if (row < p.M) {
-                float *crow = p.c + (size_t)row * p.N + n0 + c0;
+                float *crow = p.c + ((size_t)blockIdx.z * p.M + row) * p.N + n0 + c0;
                 const float *rrow = p.residual ? p.residual + (size_t)row * p.N + n0 + c0 : nullptr;
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                     if (n0 + c0 + j < p.N) {
-                        float x = __uint_as_float(v[j]);
+                        float x = empty_slice ? 0.f : __uint_as_float(v[j]);
                         if (rrow) x = __fadd_rn(rrow[j], x);  // x + residual as `Tensor + Tensor` (arithmetic.rs:48-52)
                         crow[j] = x;
                     }
@@ -209,6 +218,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constan
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+}
+
+// c[m, n] = sum over splits of part[s][m][n] (+ residual), splits added in order
+__global__ void splitk_reduce_kernel(const float *__restrict__ part, const float *__restrict__ residual, float *__restrict__ c,
+                                     size_t mn, int splits) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= mn) return;
+    float s = part[i];
+    for (int k = 1; k < splits; ++k) s = __fadd_rn(s, part[(size_t)k * mn + i]);
+    c[i] = residual ? __fadd_rn(residual[i], s) : s;
 }
 
 // hi = bf16(a), lo = bf16(a - hi)
@@ -260,7 +279,7 @@ bool gemm_tc_usable(lumen_dtype wdt, size_t M, size_t K, size_t N, const void *w
     }();
     if (mode == 1 || (mode == 2 && wdt == LUMEN_F32)) return false;
     // TMA: 16-byte aligned base and row pitch (K * 2 bytes)
-    return M > 8 && N >= 8 && K % 8 == 0 && K >= 8 && (reinterpret_cast<uintptr_t>(w) & 15) == 0;
+    return M > 1 && N >= 8 && K % 8 == 0 && K >= 8 && (reinterpret_cast<uintptr_t>(w) & 15) == 0;
 }
 
 namespace {
@@ -275,7 +294,9 @@ int launch_tc_kernel(lumen_ctx *ctx, const CUtensorMap &mhi, const CUtensorMap &
         LUMEN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<WSPLIT, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attr_set[dev] = true;
     }
-    dim3 grid((unsigned)((N + BN - 1) / BN), (unsigned)((M + kBM - 1) / kBM));
+    const int kb_all = (p.K + kBK - 1) / kBK;
+    const int splits = (kb_all + p.kb_per_split - 1) / p.kb_per_split;
+    dim3 grid((unsigned)((N + BN - 1) / BN), (unsigned)((M + kBM - 1) / kBM), (unsigned)splits);
     gemm_tc_kernel<WSPLIT, BN><<<grid, kTcThreads, smem, s>>>(mhi, mlo, mb, mblo, p);
     LUMEN_LAUNCHED(ctx);
     return LUMEN_OK;
@@ -321,12 +342,36 @@ int launch_gemm_tc(lumen_ctx *ctx, const float *a, const void *w, lumen_dtype wd
     const int bn = pick_bn(M, N, ctx->num_sms);
     if (rc == LUMEN_OK) rc = make_map(ctx, &map_b, wsplit ? (const void *)whi : w, N, K, bn);
     if (rc == LUMEN_OK) rc = make_map(ctx, &map_blo, wsplit ? (const void *)wlo : w, N, K, bn);
+    // Few output tiles (one row of tiles: M <= 128) and many K blocks: split K over blockIdx.z so that about
+    // every SM streams a share of W; the slices' partial tiles are summed in slice order by a second kernel.
+    const int kb_all = (int)((K + kBK - 1) / kBK);
+    int splits = 1;
+    if (M <= (size_t)kBM) {
+        const int tiles = (int)((N + bn - 1) / bn);
+        splits = std::max(1, std::min(std::min(ctx->num_sms / std::max(tiles, 1), kb_all / 4), 16));
+    }
+    const int kb_per_split = (kb_all + splits - 1) / splits;
+    splits = (kb_all + kb_per_split - 1) / kb_per_split;
+    void *partial = nullptr;
+    if (rc == LUMEN_OK && splits > 1) rc = dev_alloc(ctx, (size_t)splits * M * N * sizeof(float), &partial);
     if (rc == LUMEN_OK) {
-        TcParams p{c, residual, (int)M, (int)N, (int)K, ctx->d_status};
+        TcParams p{splits > 1 ? static_cast<float *>(partial) : c, splits > 1 ? nullptr : residual, (int)M, (int)N, (int)K,
+                   kb_per_split, ctx->d_status};
 #define LUMEN_TC(WS, BN_) launch_tc_kernel<WS, BN_>(ctx, map_hi, map_lo, map_b, map_blo, p, M, N, s)
         if (wsplit) rc = bn == 128 ? LUMEN_TC(true, 128) : bn == 64 ? LUMEN_TC(true, 64) : LUMEN_TC(true, 32);
         else rc = bn == 128 ? LUMEN_TC(false, 128) : bn == 64 ? LUMEN_TC(false, 64) : LUMEN_TC(false, 32);
 #undef LUMEN_TC
+        if (rc == LUMEN_OK && splits > 1) {
+            const size_t mn = M * N;
+            splitk_reduce_kernel<<<(unsigned)((mn + 255) / 256), 256, 0, s>>>(static_cast<const float *>(partial), residual, c, mn, splits);
+            cudaError_t e = cudaGetLastError();
+            if (e != cudaSuccess) rc = cuda_fail(ctx, e, "splitk_reduce_kernel launch");
+            else ctx->launches += 1;
+        }
+    }
+    if (partial) {
+        int rc3 = dev_free(ctx, partial);
+        if (rc == LUMEN_OK) rc = rc3;
     }
     int rc2 = dev_free(ctx, split);
     return rc != LUMEN_OK ? rc : rc2;
