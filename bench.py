@@ -5,7 +5,7 @@
 
 One "step" is one teacher-forced decode token (one pass over all the weights).  Synthetic data:
 weights N(0, 0.02) from seed 0 with RMSNorm gains 1.0, a 32-token prompt and the forced ids from
-seed 1 (BASELINE config 1); the static KV cache is sized to max_seq_len 2048.
+seed 1 (benchmark configuration 1); the static KV cache is sized to max_seq_len 2048.
 
 Own arm (default): prints ONE JSON line with
   value     device-resident throughput (ids and logits stay in HBM), CUDA events on the library's stream
@@ -100,14 +100,15 @@ class ClockSampler(threading.Thread):
 
 
 # dram__bytes_read + dram__bytes_write of one persistent-kernel launch divided by its algorithmic bytes,
-# from the ncu capture summarised in profiles/decode_mega_kernel_tinyllama_f32.md (973.6 MB / 967.3 MB).
+# from an ncu capture of a 4-layer truncation of the same model (973.6 MB / 967.3 MB); its summary is committed
+# with the other profiler summaries.
 MEGA_TRAFFIC_RATIO = 1.0065
 
 
 WORKLOADS = {  # name -> (synth config, label, default weight dtype)
-    "tinyllama": ("TINYLLAMA", "tinyllama_1.1b", "f32"),    # BASELINE config 1: the metric's configuration
-    "llama2_7b": ("LLAMA2_7B", "llama2_7b", "bf16"),        # BASELINE config 4 shape (tensor-parallel scaling)
-    "qwen3_8b": ("QWEN3_8B", "qwen3_8b", "bf16"),           # BASELINE config 5 shape at batch 1
+    "tinyllama": ("TINYLLAMA", "tinyllama_1.1b", "f32"),    # configuration 1: the one the metric is quoted on
+    "llama2_7b": ("LLAMA2_7B", "llama2_7b", "bf16"),        # configuration 4's shape (tensor-parallel scaling)
+    "qwen3_8b": ("QWEN3_8B", "qwen3_8b", "bf16"),           # configuration 5's shape
 }
 
 
@@ -200,7 +201,7 @@ def _event_time_ms(ctx, stream, fn, iters: int, warm: int = 3) -> float:
 
 
 def run_micro(args):
-    """Secondary measurements (BASELINE configs 2 and 3): the standalone vector-matrix product over the
+    """Secondary measurements (benchmark configurations 2 and 3): the standalone vector-matrix product over the
     sweep of shapes, and decode attention over a static KV cache.  One JSON line per case; the working set
     is rotated over several copies so that it exceeds L2 whenever that takes at most 64 copies."""
     import torch
@@ -319,7 +320,7 @@ def main():
                     help="independent sequences decoded per step (1 is the metric's configuration; larger batches run the "
                          "per-operator kernels: tensor-core GEMMs and the tiled attention kernel)")
     ap.add_argument("--prompt-len", type=int, default=32,
-                    help="tokens of the (untimed) prefill; 32 is the metric's configuration, 512 BASELINE config 4's")
+                    help="tokens of the (untimed) prefill; 32 is the metric's configuration, 512 configuration 4's")
     args = ap.parse_args()
     global PROMPT_LEN
     PROMPT_LEN = args.prompt_len
@@ -484,7 +485,7 @@ def main():
         "clocks": sampler.summary(),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": (bytes_step * MEGA_TRAFFIC_RATIO if launches == args.steps else None),
-                     "traffic_note": "ncu dram bytes of a 4-layer capture (profiles/decode_mega_kernel_tinyllama_f32.md), "
+                     "traffic_note": "ncu dram bytes of a capture of the same kernel on a 4-layer truncation of the model, "
                                      "scaled by algorithmic bytes", "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
                      "kernel": ("decode_mega_kernel: one persistent launch runs the whole token"
                                 if launches == args.steps else

@@ -49,7 +49,7 @@ def _decode_case(L, oracle, ctx, b, hq, hkv, d, ctx_len, max_seq, seed, steps=1,
     return worst
 
 
-# BASELINE config 3: 32 q heads, 4 KV heads, head_dim 64; contexts 128..8192; batch 1 and 16
+# Benchmark configuration 3: 32 q heads, 4 KV heads, head_dim 64; contexts 128..8192; batch 1 and 16
 @pytest.mark.parametrize("ctx_len", [128, 512, 2048, 8192])
 @pytest.mark.parametrize("b", [1, 16])
 def test_decode_attention_config3(L, oracle, ctx, ctx_len, b):

@@ -188,7 +188,7 @@ def test_error_conditions(L):
 
 @pytest.mark.parametrize("wdt,prompt,steps", [("f32", 32, 128), ("bf16", 32, 24)])
 def test_tinyllama_config1_teacher_forced(L, oracle, wdt, prompt, steps):
-    """BASELINE config 1 at full size: TinyLlama-1.1B shape, weights N(0,0.02) seed 0 (gains 1.0), 32
+    """Benchmark configuration 1 at full size: TinyLlama-1.1B shape, weights N(0,0.02) seed 0 (gains 1.0), 32
     prompt ids from seed 1 and teacher-forced decode steps at batch 1, cache sized to 2048.  The bf16
     variant rounds the same weights to bf16 and runs fewer steps to bound the CPU oracle's time."""
     from lumen_b200 import synth

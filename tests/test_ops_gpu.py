@@ -11,7 +11,7 @@ from helpers import rel_err
 
 pytestmark = pytest.mark.gpu
 
-# BASELINE config 2: (K, N) of the standalone M = 1 sweep
+# Benchmark configuration 2: (K, N) of the standalone M = 1 sweep
 SWEEP = [(2048, 2048), (2048, 256), (2048, 5632), (5632, 2048), (2048, 32000), (4096, 11008), (11008, 4096)]
 
 
@@ -105,7 +105,7 @@ def test_matmul_batched_leading_dims_and_errors(L, oracle):
 @pytest.mark.parametrize("k,n", [(2048, 2048), (2048, 256), (5632, 2048), (2048, 32000), (100, 37), (33, 5)])
 @pytest.mark.parametrize("bf16", [False, True])
 def test_gemv_kn_layout_raw_pointers(L, oracle, ctx, k, n, bf16):
-    """`lumen_gemv` with W stored [K,N] row-major (the layout BASELINE config 2 names), on raw device
+    """`lumen_gemv` with W stored [K,N] row-major (the layout benchmark configuration 2 names), on raw device
     pointers, with canaries around y."""
     rng = np.random.default_rng(9)
     x = rng.standard_normal(k, dtype=np.float32)
