@@ -8,6 +8,8 @@
 // Bandwidth design: each lane issues 128-bit streaming loads (ld.global.cs) and keeps
 // kUnroll x kRowsPerWarp of them in flight; the activation vector is staged once per CTA in
 // shared memory and read back as conflict-free 128-bit words.
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace lumen {
@@ -147,6 +149,59 @@ __device__ __forceinline__ void row_dot(const WT *__restrict__ wrow, const float
     }
 }
 
+// RR rows of W against MB staged vectors at once: every 16 bytes of x read from shared memory feed RR rows, so
+// the shared-memory traffic per weight byte is MB / RR instead of MB (with MB = 8 and one row at a time the
+// kernel was bound by shared memory, not by HBM).  Vector path only (K % VEC == 0, 16-byte aligned rows).
+template <typename WT, int MB, int RR>
+__device__ __forceinline__ void rows_dot(const WT *const (&rows)[RR], const float *xs, size_t K, int lane, float (&acc)[RR][MB]) {
+    constexpr int VEC = 16 / sizeof(WT);
+    constexpr int kUnroll = 4;
+    const size_t nv = K / VEC;
+    for (size_t base = 0; base < nv; base += 32 * kUnroll) {
+        uint4 wv[RR][kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const size_t i = base + (size_t)u * 32 + lane;
+#pragma unroll
+            for (int r = 0; r < RR; ++r)
+                wv[r][u] = (i < nv) ? ld_stream_u4(reinterpret_cast<const uint4 *>(rows[r]) + i) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const size_t i = base + (size_t)u * 32 + lane;
+            if (i < nv) {
+#pragma unroll
+                for (int m = 0; m < MB; ++m) {
+                    const float4 *xp = reinterpret_cast<const float4 *>(xs + (size_t)m * K + i * VEC);
+                    const float4 x0 = xp[0];
+                    if constexpr (sizeof(WT) == 4) {
+#pragma unroll
+                        for (int r = 0; r < RR; ++r) {
+                            acc[r][m] = fmaf(__uint_as_float(wv[r][u].x), x0.x, acc[r][m]);
+                            acc[r][m] = fmaf(__uint_as_float(wv[r][u].y), x0.y, acc[r][m]);
+                            acc[r][m] = fmaf(__uint_as_float(wv[r][u].z), x0.z, acc[r][m]);
+                            acc[r][m] = fmaf(__uint_as_float(wv[r][u].w), x0.w, acc[r][m]);
+                        }
+                    } else {
+                        const float4 x1 = xp[1];
+#pragma unroll
+                        for (int r = 0; r < RR; ++r) {
+                            acc[r][m] = fmaf(bf16_lo(wv[r][u].x), x0.x, acc[r][m]);
+                            acc[r][m] = fmaf(bf16_hi(wv[r][u].x), x0.y, acc[r][m]);
+                            acc[r][m] = fmaf(bf16_lo(wv[r][u].y), x0.z, acc[r][m]);
+                            acc[r][m] = fmaf(bf16_hi(wv[r][u].y), x0.w, acc[r][m]);
+                            acc[r][m] = fmaf(bf16_lo(wv[r][u].z), x1.x, acc[r][m]);
+                            acc[r][m] = fmaf(bf16_hi(wv[r][u].z), x1.y, acc[r][m]);
+                            acc[r][m] = fmaf(bf16_lo(wv[r][u].w), x1.z, acc[r][m]);
+                            acc[r][m] = fmaf(bf16_hi(wv[r][u].w), x1.w, acc[r][m]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+}
+
 template <typename WT, int MB>
 __global__ void __launch_bounds__(kThreads)
 gemv_nk_kernel(const float *__restrict__ x, const WT *__restrict__ w, float *__restrict__ y, int M, size_t K, size_t N,
@@ -159,6 +214,34 @@ gemv_nk_kernel(const float *__restrict__ x, const WT *__restrict__ w, float *__r
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     constexpr int VEC = 16 / sizeof(WT);
     const bool vec_ok = (K % VEC == 0) && ((reinterpret_cast<uintptr_t>(w) & 15) == 0);
+    if constexpr (MB > 1) {
+        if (vec_ok) {  // several vectors: rows are taken RR at a time so that x is read once per RR rows
+            constexpr int RR = MB >= 8 ? 2 : 4;
+            for (size_t row0 = ((size_t)blockIdx.x * kWarps + warp) * RR; row0 < N; row0 += (size_t)gridDim.x * kWarps * RR) {
+                const WT *rows[RR];
+                float acc[RR][MB];
+#pragma unroll
+                for (int r = 0; r < RR; ++r) {
+                    rows[r] = w + (row0 + r < N ? row0 + r : N - 1) * K;  // rows past the end repeat the last one (not stored)
+#pragma unroll
+                    for (int m = 0; m < MB; ++m) acc[r][m] = 0.f;
+                }
+                rows_dot<WT, MB, RR>(rows, xs, K, lane, acc);
+#pragma unroll
+                for (int r = 0; r < RR; ++r) {
+#pragma unroll
+                    for (int m = 0; m < MB; ++m) {
+                        const float v = warp_sum(acc[r][m]);
+                        if (lane == 0 && m < M && row0 + r < N) {
+                            const size_t o = (size_t)m * ldy + row0 + r;
+                            y[o] = residual ? __fadd_rn(residual[o], v) : v;
+                        }
+                    }
+                }
+            }
+            return;
+        }
+    }
     for (size_t row = (size_t)blockIdx.x * kWarps + warp; row < N; row += (size_t)gridDim.x * kWarps) {
         float acc[MB];
 #pragma unroll
@@ -190,6 +273,27 @@ gemv_gate_up_kernel(const float *__restrict__ x, const WT *__restrict__ wg, cons
     constexpr int VEC = 16 / sizeof(WT);
     const bool vec_ok = (K % VEC == 0) && ((reinterpret_cast<uintptr_t>(wg) & 15) == 0) &&
                         ((reinterpret_cast<uintptr_t>(wu) & 15) == 0);
+    if constexpr (MB > 1) {
+        if (vec_ok) {  // the gate row and the up row of an output share every read of x
+            for (size_t row = (size_t)blockIdx.x * kWarps + warp; row < I; row += (size_t)gridDim.x * kWarps) {
+                const WT *rows[2] = {wg + row * K, wu + row * K};
+                float acc[2][MB];
+#pragma unroll
+                for (int m = 0; m < MB; ++m) acc[0][m] = acc[1][m] = 0.f;
+                rows_dot<WT, MB, 2>(rows, xs, K, lane, acc);
+#pragma unroll
+                for (int m = 0; m < MB; ++m) {
+                    const float g = warp_sum(acc[0][m]);
+                    const float u = warp_sum(acc[1][m]);
+                    if (lane == 0 && m < M) {
+                        const float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-g)));
+                        out[(size_t)m * I + row] = __fmul_rn(__fmul_rn(g, sig), u);
+                    }
+                }
+            }
+            return;
+        }
+    }
     for (size_t row = (size_t)blockIdx.x * kWarps + warp; row < I; row += (size_t)gridDim.x * kWarps) {
         float ag[MB], au[MB];
 #pragma unroll
