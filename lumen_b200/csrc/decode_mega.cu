@@ -1128,10 +1128,11 @@ int launch_decode_mega(lumen_ctx *ctx, MegaParams &p, cudaStream_t s) {
     const size_t smem = decode_mega_smem_bytes(stages, p.stage_bytes, p.D, kmax);
     if (smem > budget) return set_error(ctx, LUMEN_ERR_UNSUPPORTED, "shared memory: %zu bytes needed", smem);
     const void *kern = p.wbf16 ? (const void *)decode_mega_kernel<__nv_bfloat16> : (const void *)decode_mega_kernel<float>;
-    static bool attr_set[2] = {false, false};
-    if (!attr_set[p.wbf16 ? 1 : 0]) {  // once, for the largest ring any shape can ask for
+    static bool attr_set[64][2] = {};  // per device ordinal and weight type
+    const int dev = ctx->device >= 0 && ctx->device < 64 ? ctx->device : 0;
+    if (!attr_set[dev][p.wbf16 ? 1 : 0]) {  // once, for the largest ring any shape can ask for
         LUMEN_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget));
-        attr_set[p.wbf16 ? 1 : 0] = true;
+        attr_set[dev][p.wbf16 ? 1 : 0] = true;
     }
     void *args[] = {&p};
     LUMEN_CUDA(ctx, cudaLaunchCooperativeKernel(kern, dim3(grid), dim3(kThreads), args, smem, s));
