@@ -577,6 +577,11 @@ int launch_attn_prefill(lumen_ctx *ctx, const AttnPrefillArgs &a, cudaStream_t s
     p.q_rot = static_cast<float *>(qrot);
     attn_prefill_prep_kernel<<<dim3((unsigned)a.S, (unsigned)a.B), kThreads, kWarps * a.D * sizeof(float), s>>>(p);
     LUMEN_LAUNCHED(ctx);
+    if (attn_prefill_tc_usable(a)) {
+        const int rc = launch_attn_prefill_tc(ctx, a, p.q_rot, s);
+        const int rc2 = dev_free(ctx, qrot);
+        return rc != LUMEN_OK ? rc : rc2;
+    }
     dim3 grid((unsigned)((a.S + kWarps - 1) / kWarps), (unsigned)a.Hq, (unsigned)a.B);
     switch (pick_ni(a.D)) {
         case 1: attn_prefill_kernel<1><<<grid, kThreads, 0, s>>>(p); break;

@@ -228,6 +228,10 @@ struct AttnPrefillArgs {
     float *out = nullptr;
 };
 int launch_attn_prefill(lumen_ctx *ctx, const AttnPrefillArgs &a, cudaStream_t s);
+// Tensor-core prefill attention (attn_prefill_tc.cu): q_rot holds the rotated queries [B, S, Hq, D] and the
+// cache rows 0 .. past + S - 1 are already written.
+bool attn_prefill_tc_usable(const AttnPrefillArgs &a);
+int launch_attn_prefill_tc(lumen_ctx *ctx, const AttnPrefillArgs &a, const float *q_rot, cudaStream_t s);
 
 // Nucleus sampling of one logits vector on the device (sampler.cu); *token_dev is a device int.
 int launch_sample_top_p(lumen_ctx *ctx, const float *logits_dev, size_t vocab, float temperature, float top_p, float penalty,

@@ -16,16 +16,16 @@
 //
 // Every wait is bounded; a wait that gives up records LUMEN_ERR_TIMEOUT, the CTA stops issuing, lets the
 // copies in flight land, frees its tensor memory and returns.
-#include <cuda.h>
-
 #include <algorithm>
 
-#include "common.cuh"
+#include "tc_common.cuh"
 
 namespace lumen {
 namespace {
 
-constexpr int kBM = 128, kBK = 64;  // tile rows of A; kBK bf16 = one 128-byte swizzle row
+using namespace tc;
+
+constexpr int kBM = 128;  // tile rows of A
 constexpr int kTcThreads = 128;
 constexpr uint32_t kABytes = kBM * kBK * 2;
 // The tile is 128 x BN: BN = 128, or 64 / 32 for outputs narrower than that.
@@ -38,56 +38,8 @@ struct TcGeom {
     static constexpr int kStages = (200 * 1024 / kStageBytes) > 6 ? 6 : (200 * 1024 / kStageBytes);
     static constexpr int kTmemCols = BN < 32 ? 32 : BN;
     // Instruction descriptor: f32 accumulator, bf16 A and B, both K-major, N and M of the tile.
-    static constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+    static constexpr uint32_t kIdesc = idesc_bf16(kBM, BN);
 };
-constexpr long long kTcWaitCycles = 200000000LL;         // ~0.1 s
-
-__device__ __forceinline__ uint32_t saddr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void bar_init(uint64_t *bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(saddr(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void bar_expect(uint64_t *bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(saddr(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool bar_try(uint64_t *bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-                 : "=r"(ok) : "r"(saddr(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool bar_wait(uint64_t *bar, uint32_t parity, DeviceStatus *status, int site) {
-    if (bar_try(bar, parity)) return true;
-    const long long t0 = clock64();
-    while (!bar_try(bar, parity)) {
-        if (clock64() - t0 > kTcWaitCycles) {
-            if (status && atomicCAS(&status->code, 0, LUMEN_ERR_TIMEOUT) == 0) status->detail0 = site;
-            return false;
-        }
-    }
-    return true;
-}
-// 2-D tiled TMA load: box (kBK elements, rows) at element coordinates (x = k, y = row).  x is a multiple of
-// 64 bf16 elements = 128 bytes, so the 16-byte start rule of TMA holds.
-__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(saddr(dst)), "l"(map), "r"(x), "r"(y), "r"(saddr(bar)) : "memory");
-}
-// Shared-memory matrix descriptor of a K-major bf16 tile stored as rows of 128 bytes with the 128-byte
-// swizzle (what the TMA box above produces): start address, leading offset 1 (unused with swizzle), 1024
-// bytes between groups of 8 rows, descriptor version 1, layout type 2 = 128-byte swizzle.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
-    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
-           ((uint64_t)2 << 61);
-}
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-                 " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}"
-                 ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t *bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(saddr(bar)) : "memory");
-}
-
 struct TcParams {
     float *c;               // output, or the [splits][M][N] partial sums when the K range is split over blockIdx.z
     const float *residual;  // added in the epilogue (null with split K: the reduction kernel adds it)
@@ -185,16 +137,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constan
         for (int c0 = 0; c0 < kBN; c0 += 32) {
             uint32_t v[32];
             const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0;
-            asm volatile(
-                "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, "
-                "%19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
-                  "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
-                  "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
-                  "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-                : "r"(taddr)
-                : "memory");
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            tmem_ld32(taddr, v);
             if (row < p.M) {
                 float *crow = p.c + ((size_t)blockIdx.z * p.M + row) * p.N + n0 + c0;
                 const float *rrow = p.residual ? p.residual + (size_t)row * p.N + n0 + c0 : nullptr;
@@ -238,36 +181,6 @@ __global__ void split_bf16_kernel(const float *__restrict__ a, __nv_bfloat16 *__
     const __nv_bfloat16 h = __float2bfloat16_rn(x);
     hi[i] = h;
     lo[i] = __float2bfloat16_rn(x - __bfloat162float(h));
-}
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = [] {
-        void *p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
-            p = nullptr;
-        return reinterpret_cast<EncodeTiledFn>(p);
-    }();
-    return fn;
-}
-
-// Row-major bf16 matrix [rows, K] -> map with box (kBK, box_rows), 128-byte swizzle, zero fill out of bounds.
-int make_map(lumen_ctx *ctx, CUtensorMap *map, const void *base, size_t rows, size_t K, int box_rows) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return set_error(ctx, LUMEN_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
-    const cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return set_error(ctx, LUMEN_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
-    return LUMEN_OK;
 }
 
 }  // namespace

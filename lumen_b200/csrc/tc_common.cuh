@@ -1,0 +1,109 @@
+// Pieces shared by the tensor-core kernels (gemm_tc.cu, attn_prefill_tc.cu): mbarrier and TMA wrappers,
+// tcgen05 descriptors and instructions, bounded waits, and the tensor-map encoder looked up from the driver.
+#pragma once
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace lumen {
+namespace tc {
+
+constexpr int kBK = 64;                           // 64 bf16 = one 128-byte swizzle row
+constexpr long long kTcWaitCycles = 200000000LL;  // ~0.1 s
+
+__device__ __forceinline__ uint32_t saddr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void bar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(saddr(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void bar_expect(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(saddr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool bar_try(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(saddr(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded: gives up after kTcWaitCycles, records LUMEN_ERR_TIMEOUT with the site and returns false.
+__device__ __forceinline__ bool bar_wait(uint64_t *bar, uint32_t parity, DeviceStatus *status, int site) {
+    if (bar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!bar_try(bar, parity)) {
+        if (clock64() - t0 > kTcWaitCycles) {
+            if (status && atomicCAS(&status->code, 0, LUMEN_ERR_TIMEOUT) == 0) status->detail0 = site;
+            return false;
+        }
+    }
+    return true;
+}
+// 2-D tiled TMA load: box (kBK elements, rows) at element coordinates (x, y = row).  x is a multiple of
+// 64 bf16 elements = 128 bytes, so the 16-byte start rule of TMA holds.
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(saddr(dst)), "l"(map), "r"(x), "r"(y), "r"(saddr(bar)) : "memory");
+}
+// Shared-memory matrix descriptor of a K-major bf16 tile stored as rows of 128 bytes with the 128-byte
+// swizzle (what the TMA box above produces): start address, leading offset 1 (unused with swizzle), 1024
+// bytes between groups of 8 rows, descriptor version 1, layout type 2 = 128-byte swizzle.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+           ((uint64_t)2 << 61);
+}
+// Instruction descriptor of kind::f16: f32 accumulator, bf16 A and B, both K-major, an M x N tile.
+__host__ __device__ constexpr uint32_t idesc_bf16(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+                 " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}"
+                 ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(saddr(bar)) : "memory");
+}
+// 32 consecutive accumulator columns of this thread's lane (lane = 32 * warp + lane id), then the wait.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, "
+        "%19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+          "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
+          "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+          "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// Row-major bf16 matrix [rows, K] -> map with box (kBK, box_rows), 128-byte swizzle, zero fill out of bounds.
+inline int make_map(lumen_ctx *ctx, CUtensorMap *map, const void *base, size_t rows, size_t K, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return set_error(ctx, LUMEN_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return set_error(ctx, LUMEN_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
+    return LUMEN_OK;
+}
+
+}  // namespace tc
+}  // namespace lumen

@@ -139,6 +139,16 @@ def test_self_attention_tinyllama_geometry(L, oracle):
     assert err < 2e-5, err
 
 
+@pytest.mark.parametrize("e,hq,hkv", [(256, 4, 2), (512, 4, 1), (512, 4, 4)])
+@pytest.mark.parametrize("chunks", [[200, 1], [64, 130, 1, 70], [129], [300, 1, 1]])
+def test_self_attention_tensor_core_prefill(L, oracle, e, hq, hkv, chunks):
+    """Prompts of 64 positions and more with head dimensions 64 / 128 take the tensor-core prefill kernel
+    (tiles of 128 queries x 64 cached rows, hi/lo bf16 products): ragged tile edges, a second prompt into a
+    non-empty cache (mask j > past_len + i), grouped and ungrouped heads, two batch rows."""
+    err = _self_attention_case(L, oracle, e, hq, hkv, 512, 2, chunks, seed=e + sum(chunks))
+    assert err < 5e-5, err
+
+
 def test_self_attention_errors(L):
     attn = L.SelfAttention(32, 4, 2, 6, 10000.0, True)
     w = [np.zeros(s, np.float32) for s in ((32, 32), (16, 32), (16, 32), (32, 32))]
