@@ -27,7 +27,8 @@ using namespace tc;
 
 constexpr int kBQ = 128;   // query rows per CTA
 constexpr int kBKV = 64;   // cached rows per tile
-constexpr int kFaThreads = 128;
+constexpr int kFaWorkers = 256;             // 8 warps: two threads per query row
+constexpr int kFaThreads = kFaWorkers + 64;  // + a warp whose first lane issues the MMAs + a warp whose first lane issues the copies
 
 template <int D>
 struct FaGeom {
@@ -43,7 +44,8 @@ struct FaGeom {
     static constexpr uint32_t kPBytes = 2 * kPTile;          // hi, lo
     static constexpr int kStages = 2;
     static constexpr size_t kSmem = kQBytes + kStages * kStageBytes + kPBytes + 1024;  // + slack for the alignment
-    static constexpr int kTmemCols = D > 64 ? 256 : 128;     // S: columns 0..63, O: columns 64..64+D-1
+    // S of even tiles: columns 0..63, S of odd tiles: 64..127, O of even tiles: 128..128+D-1, O of odd tiles after it
+    static constexpr int kTmemCols = D > 64 ? 512 : 256;
     static constexpr uint32_t kIdescS = idesc_bf16(kBQ, kBKV);
     static constexpr uint32_t kIdescO = idesc_bf16(kBQ, D);
 };
@@ -56,27 +58,56 @@ struct FaParams {
     DeviceStatus *status;
 };
 
+__device__ __forceinline__ float ex2(float x) {  // 2^x, one MUFU operation (relative error 2^-22; -inf -> 0)
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<const uint32_t *>(&v);
 }
 
-// grid (s_pad / 128, Hq, B)
+// A wait that also ends when another thread of the CTA has given up (nobody leaves the tile loop early, so
+// every barrier keeps its full set of participants; after a failure the remaining iterations do not wait).
+__device__ __forceinline__ bool wait_or_failed(uint64_t *bar, uint32_t parity, volatile int *failed, DeviceStatus *status, int site) {
+    if (*failed) return false;
+    if (bar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!bar_try(bar, parity)) {
+        if (*failed) return false;
+        if (clock64() - t0 > kTcWaitCycles) {
+            if (status && atomicCAS(&status->code, 0, LUMEN_ERR_TIMEOUT) == 0) status->detail0 = site;
+            *failed = 1;
+            return false;
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ void bar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(saddr(bar)) : "memory");
+}
+
+// grid (s_pad / 128, Hq, B); 8 worker warps, warp 8 (first lane) issues the MMAs, warp 9 (first lane) the copies
 template <int D>
 __global__ void __launch_bounds__(kFaThreads, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constant__ CUtensorMap map_qlo,
                        const __grid_constant__ CUtensorMap map_khi, const __grid_constant__ CUtensorMap map_klo,
                        const __grid_constant__ CUtensorMap map_vhi, const __grid_constant__ CUtensorMap map_vlo, const FaParams p) {
     using G = FaGeom<D>;
-    constexpr int kKB = G::kKB;
+    constexpr int kKB = G::kKB, kDH = D / 2;  // a worker thread owns half a row of the context
     extern __shared__ unsigned char smem_raw[];
     // the 128-byte swizzle pattern repeats every 1024 bytes: tiles must start on that boundary
     unsigned char *q_s = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char *ring = q_s + G::kQBytes;
     unsigned char *p_s = ring + G::kStages * G::kStageBytes;
-    __shared__ uint64_t q_bar, full[G::kStages], s_bar, o_bar;
+    __shared__ uint64_t q_bar, k_full[G::kStages], v_full[G::kStages], k_free[G::kStages], v_free[G::kStages], s_bar[2], o_bar, p_bar;
     __shared__ uint32_t tmem_base_s;
-    __shared__ int failed;
+    __shared__ int failed_s;
+    // [column half][row]: row maxima, at the end the row sums.  One copy is enough: a thread writes its next value
+    // only after P.V of this tile, which is issued after its partner announced its weights (and so has read).
+    __shared__ float xch[2][kBQ];
+    volatile int *failed = &failed_s;
     const int tid = threadIdx.x, warp = tid >> 5;
     // the last tiles of a causal prompt walk the most rows: they go first
     const int qt = (int)(gridDim.x - 1 - blockIdx.x);
@@ -87,185 +118,267 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid
     const int i_hi = min(i0 + kBQ, p.S) - 1;
     const int visible = p.causal ? min(p.total, p.past + i_hi + 1) : p.total;
     const int nt = (visible + kBKV - 1) / kBKV;
-    const int q_row0 = (b * p.Hq + h) * p.s_pad + i0;
-    const int k_row0 = (b * p.Hkv + hk) * p.l_pad;
-    const int v_row0 = (b * p.Hkv + hk) * D;
 
     if (tid == 0) {
         bar_init(&q_bar, 1);
-        for (int s = 0; s < G::kStages; ++s) bar_init(&full[s], 1);
-        bar_init(&s_bar, 1);
+        for (int s = 0; s < G::kStages; ++s) {
+            bar_init(&k_full[s], 1);
+            bar_init(&v_full[s], 1);
+            bar_init(&k_free[s], 1);
+            bar_init(&v_free[s], 1);
+        }
+        bar_init(&s_bar[0], 1);
+        bar_init(&s_bar[1], 1);
         bar_init(&o_bar, 1);
-        failed = 0;
+        bar_init(&p_bar, kFaWorkers);
+        failed_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 0) {
+    if (warp == kFaWorkers / 32) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(saddr(&tmem_base_s)), "r"(G::kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem_s = tmem_base_s, tmem_o = tmem_base_s + kBKV;
-    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+    // tensor memory: scores of even tiles | scores of odd tiles | O of even tiles | O of odd tiles
+    const uint32_t tmem_s = tmem_base_s, tmem_o = tmem_base_s + 2 * kBKV;
 
-    auto load_tile = [&](int j) {  // thread 0: K and V^T of tile j into stage j % 2
-        const int s = j % G::kStages;
-        unsigned char *st = ring + (size_t)s * G::kStageBytes;
-        bar_expect(&full[s], G::kStageBytes);
-#pragma unroll
-        for (int kb = 0; kb < kKB; ++kb) {
-            tma_load_2d(st + kb * G::kKTile, &map_khi, kb * kBK, k_row0 + j * kBKV, &full[s]);
-            tma_load_2d(st + (kKB + kb) * G::kKTile, &map_klo, kb * kBK, k_row0 + j * kBKV, &full[s]);
-        }
-        tma_load_2d(st + G::kKBytes, &map_vhi, j * kBKV, v_row0, &full[s]);
-        tma_load_2d(st + G::kKBytes + G::kVTile, &map_vlo, j * kBKV, v_row0, &full[s]);
-    };
-
-    int in_flight = 0;  // thread 0: tiles whose copies were issued
-    if (tid == 0) {
-        bar_expect(&q_bar, G::kQBytes);
-#pragma unroll
-        for (int kb = 0; kb < kKB; ++kb) {
-            tma_load_2d(q_s + kb * G::kQTile, &map_qhi, kb * kBK, q_row0, &q_bar);
-            tma_load_2d(q_s + (kKB + kb) * G::kQTile, &map_qlo, kb * kBK, q_row0, &q_bar);
-        }
-        for (; in_flight < nt && in_flight < G::kStages; ++in_flight) load_tile(in_flight);
-    }
-    __syncwarp();
-
-    // this thread's query row: position, last visible cached row
-    const int i_row = min(i0 + tid, p.S - 1);
-    const int last = p.causal ? min(p.total - 1, p.past + i_row) : p.total - 1;
-    float ctx[D];
-#pragma unroll
-    for (int e = 0; e < D; ++e) ctx[e] = 0.f;
-    float m = -INFINITY, l = 0.f;
-
-#pragma unroll 1
-    for (int j = 0; j < nt; ++j) {
-        const int s = j % G::kStages;
-        const uint32_t st = saddr(ring + (size_t)s * G::kStageBytes);
-        if (tid == 0) {
-            bool ok = bar_wait(&full[s], (uint32_t)((j / G::kStages) & 1), p.status, 600);
-            if (ok && j == 0) ok = bar_wait(&q_bar, 0, p.status, 601);
-            if (!ok) failed = 1;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (ok) {
-                const uint32_t qa = saddr(q_s);
+    float ctx[kDH];
+    float l = 0.f;
+    if (warp == kFaWorkers / 32 + 1) {
+        if ((tid & 31) == 0) {
+            // ---- TMA producer: Q once, then K and V^T of tile j + 2 as soon as tile j has released its half stage ----
+            const int q_row0 = (b * p.Hq + h) * p.s_pad + i0;
+            const int k_row0 = (b * p.Hkv + hk) * p.l_pad;
+            const int v_row0 = (b * p.Hkv + hk) * D;
+            // A stage holds K (hi, lo) and V^T (hi, lo) of one tile; the two halves are refilled separately: K as
+            // soon as the tile's scores are done, V^T after its P.V.
+            auto load_k = [&](int j) {
+                const int s = j % G::kStages;
+                unsigned char *st = ring + (size_t)s * G::kStageBytes;
+                bar_expect(&k_full[s], G::kKBytes);
 #pragma unroll
                 for (int kb = 0; kb < kKB; ++kb) {
-                    const uint64_t qhi = smem_desc(qa + kb * G::kQTile), qlo = smem_desc(qa + (kKB + kb) * G::kQTile);
-                    const uint64_t khi = smem_desc(st + kb * G::kKTile), klo = smem_desc(st + (kKB + kb) * G::kKTile);
+                    tma_load_2d(st + kb * G::kKTile, &map_khi, kb * kBK, k_row0 + j * kBKV, &k_full[s]);
+                    tma_load_2d(st + (kKB + kb) * G::kKTile, &map_klo, kb * kBK, k_row0 + j * kBKV, &k_full[s]);
+                }
+            };
+            auto load_v = [&](int j) {
+                const int s = j % G::kStages;
+                unsigned char *st = ring + (size_t)s * G::kStageBytes;
+                bar_expect(&v_full[s], G::kVBytes);
+                tma_load_2d(st + G::kKBytes, &map_vhi, j * kBKV, v_row0, &v_full[s]);
+                tma_load_2d(st + G::kKBytes + G::kVTile, &map_vlo, j * kBKV, v_row0, &v_full[s]);
+            };
+            bar_expect(&q_bar, G::kQBytes);
 #pragma unroll
-                    for (int kk = 0; kk < kBK / 16; ++kk) {  // UMMA K = 16 bf16 = 32 bytes = 2 descriptor units
-                        umma_bf16(tmem_s, qhi + 2 * kk, khi + 2 * kk, G::kIdescS, (kb > 0 || kk > 0) ? 1u : 0u);
-                        umma_bf16(tmem_s, qlo + 2 * kk, khi + 2 * kk, G::kIdescS, 1u);
-                        umma_bf16(tmem_s, qhi + 2 * kk, klo + 2 * kk, G::kIdescS, 1u);
+            for (int kb = 0; kb < kKB; ++kb) {
+                tma_load_2d(q_s + kb * G::kQTile, &map_qhi, kb * kBK, q_row0, &q_bar);
+                tma_load_2d(q_s + (kKB + kb) * G::kQTile, &map_qlo, kb * kBK, q_row0, &q_bar);
+            }
+            for (int j = 0; j < nt && j < G::kStages; ++j) {
+                load_k(j);
+                load_v(j);
+            }
+#pragma unroll 1
+            for (int j = 0; j + G::kStages < nt; ++j) {
+                const int s = j % G::kStages;
+                const uint32_t par = (uint32_t)((j / G::kStages) & 1);
+                if (wait_or_failed(&k_free[s], par, failed, p.status, 640)) load_k(j + G::kStages);
+                if (wait_or_failed(&v_free[s], par, failed, p.status, 641)) load_v(j + G::kStages);
+            }
+        }
+        __syncwarp();
+    } else if (warp == kFaWorkers / 32) {
+        if ((tid & 31) == 0) {
+            // ---- MMA issuer: never waits for a result, only for operands ----------------------------------
+            // S = Q.K^T of tile j (three hi/lo products per 16-element K step) into the score buffer j % 2
+            auto issue_scores = [&](int j) {
+                const int s = j % G::kStages;
+                bool ok = wait_or_failed(&k_full[s], (uint32_t)((j / G::kStages) & 1), failed, p.status, 600);
+                if (ok && j == 0) ok = wait_or_failed(&q_bar, 0, failed, p.status, 601);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (ok) {
+                    const uint32_t qa = saddr(q_s), st = saddr(ring + (size_t)s * G::kStageBytes);
+                    const uint32_t acc = tmem_s + (uint32_t)((j & 1) * kBKV);
+#pragma unroll
+                    for (int kb = 0; kb < kKB; ++kb) {
+                        const uint64_t qhi = smem_desc(qa + kb * G::kQTile), qlo = smem_desc(qa + (kKB + kb) * G::kQTile);
+                        const uint64_t khi = smem_desc(st + kb * G::kKTile), klo = smem_desc(st + (kKB + kb) * G::kKTile);
+#pragma unroll
+                        for (int kk = 0; kk < kBK / 16; ++kk) {  // UMMA K = 16 bf16 = 32 bytes = 2 descriptor units
+                            umma_bf16(acc, qhi + 2 * kk, khi + 2 * kk, G::kIdescS, (kb > 0 || kk > 0) ? 1u : 0u);
+                            umma_bf16(acc, qlo + 2 * kk, khi + 2 * kk, G::kIdescS, 1u);
+                            umma_bf16(acc, qhi + 2 * kk, klo + 2 * kk, G::kIdescS, 1u);
+                        }
                     }
                 }
+                // both arrive when the MMAs above have completed (at once if none was issued): the workers may read
+                // the scores, the producer may refill the K half of the stage
+                umma_commit(&s_bar[j & 1]);
+                umma_commit(&k_free[s]);
+            };
+            issue_scores(0);
+#pragma unroll 1
+            for (int j = 0; j < nt; ++j) {
+                // The next tile's scores run while the workers turn this tile's scores into weights.  Its score
+                // buffer was last read for tile j - 1, whose weights were announced on p_bar before P.V of
+                // tile j - 1 was issued below.
+                if (j + 1 < nt) issue_scores(j + 1);
+                const int s = j % G::kStages;
+                bool ok = wait_or_failed(&p_bar, (uint32_t)(j & 1), failed, p.status, 630);
+                if (ok) ok = wait_or_failed(&v_full[s], (uint32_t)((j / G::kStages) & 1), failed, p.status, 635);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (ok) {
+                    const uint32_t st = saddr(ring + (size_t)s * G::kStageBytes), pa = saddr(p_s);
+                    const uint64_t phi = smem_desc(pa), plo = smem_desc(pa + G::kPTile);
+                    const uint64_t vhi = smem_desc(st + G::kKBytes), vlo = smem_desc(st + G::kKBytes + G::kVTile);
+                    const uint32_t acc = tmem_o + (uint32_t)((j & 1) * D);
+#pragma unroll
+                    for (int kk = 0; kk < kBKV / 16; ++kk) {
+                        umma_bf16(acc, phi + 2 * kk, vhi + 2 * kk, G::kIdescO, kk > 0 ? 1u : 0u);
+                        umma_bf16(acc, plo + 2 * kk, vhi + 2 * kk, G::kIdescO, 1u);
+                        umma_bf16(acc, phi + 2 * kk, vlo + 2 * kk, G::kIdescO, 1u);
+                    }
+                }
+                // P.V of this tile has completed when these flip: the workers may read O and rewrite the weights, the
+                // producer may refill the V^T half of the stage
+                umma_commit(&o_bar);
+                umma_commit(&v_free[s]);
             }
-            umma_commit(&s_bar);  // arrives when the MMAs above have completed (at once if none was issued)
         }
         __syncwarp();
-        if (!bar_wait(&s_bar, (uint32_t)(j & 1), p.status, 610)) failed = 1;
-        __syncwarp();  // the tensor-memory loads below are warp-wide
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    } else {
+        // ---- workers: thread (row, half) owns 32 of the 64 scores of its row and D/2 of its context values ----
+        const int row = tid & (kBQ - 1), half = tid >> 7, quad = warp & 3;
+        const uint32_t lane_off = (uint32_t)(quad * 32) << 16;  // warps w and w + 4 read the same 32 lanes of tensor memory
+        const int i_row = min(i0 + row, p.S - 1);
+        const int last = p.causal ? min(p.total - 1, p.past + i_row) : p.total - 1;
+        const int last_min = p.causal ? min(p.total - 1, p.past + i0) : p.total - 1;  // the smallest `last` of the CTA
+        // exp(s * scale - m) = 2^(s * scale * log2(e) - m'): the maximum is kept in the base-2 domain
+        const float scale2 = p.scale * 1.4426950408889634f;
+#pragma unroll
+        for (int e = 0; e < kDH; ++e) ctx[e] = 0.f;
+        float m = -INFINITY;
+        unsigned char *prow_hi = p_s + (size_t)row * 128, *prow_lo = prow_hi + G::kPTile;
 
-        // ---- scores of row `tid`: scale, mask, running maximum, weights -------------------------------
-        float sc[kBKV];
-        {
-            uint32_t v[32];
-            tmem_ld32(tmem_s + lane_off, v);
+        // ctx = ctx * factor + O of tile j (the accumulator of odd tiles sits D columns after that of even tiles)
+        auto fold = [&](int j, float factor) {
+            uint32_t v[kDH / 32][32];  // every load is issued before the one wait
 #pragma unroll
-            for (int c = 0; c < 32; ++c) sc[c] = __uint_as_float(v[c]);
-            tmem_ld32(tmem_s + lane_off + 32, v);
+            for (int q = 0; q < kDH / 32; ++q) tmem_ld32_issue(tmem_o + (uint32_t)((j & 1) * D) + lane_off + half * kDH + 32 * q, v[q]);
+            tmem_ld_wait();
 #pragma unroll
-            for (int c = 0; c < 32; ++c) sc[32 + c] = __uint_as_float(v[c]);
-        }
-        const int key0 = j * kBKV;
-        float mt = m;
+            for (int q = 0; q < kDH / 32; ++q)
 #pragma unroll
-        for (int c = 0; c < kBKV; ++c) {
-            sc[c] = key0 + c <= last ? __fmul_rn(sc[c], p.scale) : -INFINITY;
-            mt = fmaxf(mt, sc[c]);
-        }
-        const float r = expf(m - mt);  // 0 for the first tile (m = -inf; row 0 of the cache is visible to every query)
-        m = mt;
-        float lsum = 0.f;
-        unsigned char *prow_hi = p_s + (size_t)tid * 128, *prow_lo = prow_hi + G::kPTile;
-#pragma unroll
-        for (int c8 = 0; c8 < kBKV / 8; ++c8) {
-            uint32_t hi[4], lo[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const float w0 = expf(sc[c8 * 8 + 2 * u] - mt), w1 = expf(sc[c8 * 8 + 2 * u + 1] - mt);
-                lsum += w0 + w1;
-                const __nv_bfloat16 h0 = __float2bfloat16_rn(w0), h1 = __float2bfloat16_rn(w1);
-                hi[u] = pack_bf16(__bfloat162float(h0), __bfloat162float(h1));
-                lo[u] = pack_bf16(w0 - __bfloat162float(h0), w1 - __bfloat162float(h1));
-            }
-            // 128-byte swizzle: 16-byte chunk c8 of row r sits at chunk position c8 ^ (r & 7)
-            const int off = ((c8 ^ (tid & 7)) << 4);
-            *reinterpret_cast<uint4 *>(prow_hi + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-            *reinterpret_cast<uint4 *>(prow_lo + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-        }
-        l = fmaf(l, r, lsum);
-        // the weights were written through the generic proxy; the tensor core reads through the async proxy
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        if (__syncthreads_or(failed)) break;  // the same answer in every thread
-
-        if (tid == 0) {
+                for (int c = 0; c < 32; ++c) ctx[32 * q + c] = fmaf(ctx[32 * q + c], factor, __uint_as_float(v[q][c]));
+        };
+        float r_prev = 0.f;  // the factor that goes with the O tile not folded in yet
+#pragma unroll 1
+        for (int j = 0; j < nt; ++j) {
+            wait_or_failed(&s_bar[j & 1], (uint32_t)((j >> 1) & 1), failed, p.status, 610);
+            __syncwarp();  // the tensor-memory loads below are warp-wide
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t pa = saddr(p_s);
-            const uint64_t phi = smem_desc(pa), plo = smem_desc(pa + G::kPTile);
-            const uint64_t vhi = smem_desc(st + G::kKBytes), vlo = smem_desc(st + G::kKBytes + G::kVTile);
+            float sc[32];
+            {
+                uint32_t v[32];
+                tmem_ld32(tmem_s + (uint32_t)((j & 1) * kBKV) + lane_off + 32 * half, v);
 #pragma unroll
-            for (int kk = 0; kk < kBKV / 16; ++kk) {
-                umma_bf16(tmem_o, phi + 2 * kk, vhi + 2 * kk, G::kIdescO, kk > 0 ? 1u : 0u);
-                umma_bf16(tmem_o, plo + 2 * kk, vhi + 2 * kk, G::kIdescO, 1u);
-                umma_bf16(tmem_o, phi + 2 * kk, vlo + 2 * kk, G::kIdescO, 1u);
+                for (int c = 0; c < 32; ++c) sc[c] = __uint_as_float(v[c]);
             }
-            umma_commit(&o_bar);
+            const int key0 = j * kBKV + 32 * half;
+            float mx = -INFINITY;
+            if (j * kBKV + kBKV - 1 > last_min) {  // the tile crosses the diagonal or the end of the context (same for the CTA)
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    sc[c] = key0 + c <= last ? sc[c] * scale2 : -INFINITY;
+                    mx = fmaxf(mx, sc[c]);
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    sc[c] *= scale2;
+                    mx = fmaxf(mx, sc[c]);
+                }
+            }
+            // the row maximum needs the other half's: exchanged between warps w and w + 4 (64-thread named barriers:
+            // one after the writes, one after the reads so that the next tile's write cannot overtake a read)
+            xch[half][row] = mx;
+            asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory");
+            const float mt = fmaxf(m, fmaxf(mx, xch[half ^ 1][row]));
+            asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory");
+            const float r = ex2(m - mt);  // 0 for the first tile (m = -inf; row 0 of the cache is visible to every query)
+            m = mt;
+            float lsum = 0.f;
+            uint32_t hi[16], lo[16];
+#pragma unroll
+            for (int u = 0; u < 16; ++u) {
+                const float w0 = ex2(sc[2 * u] - mt), w1 = ex2(sc[2 * u + 1] - mt);
+                lsum += w0 + w1;
+                hi[u] = pack_bf16(w0, w1);  // low half: w0
+                lo[u] = pack_bf16(w0 - __uint_as_float(hi[u] << 16), w1 - __uint_as_float(hi[u] & 0xffff0000u));
+            }
+            l = fmaf(l, r, lsum);  // this half's share of the row sum: both halves scale by the same factors
+            // Everything above overlapped P.V of the previous tile; the weights buffer is free once that has completed.
+            if (j > 0) {
+                wait_or_failed(&o_bar, (uint32_t)((j - 1) & 1), failed, p.status, 620);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            }
+#pragma unroll
+            for (int c8 = 0; c8 < 4; ++c8) {
+                // 128-byte swizzle: 16-byte chunk c of row r sits at chunk position c ^ (r & 7)
+                const int off = (((4 * half + c8) ^ (row & 7)) << 4);
+                *reinterpret_cast<uint4 *>(prow_hi + off) = make_uint4(hi[4 * c8], hi[4 * c8 + 1], hi[4 * c8 + 2], hi[4 * c8 + 3]);
+                *reinterpret_cast<uint4 *>(prow_lo + off) = make_uint4(lo[4 * c8], lo[4 * c8 + 1], lo[4 * c8 + 2], lo[4 * c8 + 3]);
+            }
+            // the weights were written through the generic proxy; the tensor core reads through the async proxy
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            bar_arrive(&p_bar);
+            // while P.V of this tile runs: fold in the previous tile's O (its accumulator is rewritten by the tile after
+            // this one, whose P.V is not issued before this thread has announced that tile's weights)
+            if (j > 0) {
+                __syncwarp();  // the tensor-memory loads are warp-wide
+                fold(j - 1, r_prev);
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            }
+            r_prev = r;
         }
+        wait_or_failed(&o_bar, (uint32_t)((nt - 1) & 1), failed, p.status, 621);
         __syncwarp();
-        if (!bar_wait(&o_bar, (uint32_t)(j & 1), p.status, 620)) failed = 1;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        // every MMA that read stage s has completed: refill it with the tile after next
-        if (tid == 0 && in_flight < nt && !failed) load_tile(in_flight++);
-        __syncwarp();  // the tensor-memory loads below are warp-wide
-#pragma unroll
-        for (int c0 = 0; c0 < D; c0 += 32) {
-            uint32_t v[32];
-            tmem_ld32(tmem_o + lane_off + c0, v);
-#pragma unroll
-            for (int c = 0; c < 32; ++c) ctx[c0 + c] = fmaf(ctx[c0 + c], r, __uint_as_float(v[c]));
-        }
+        fold(nt - 1, r_prev);
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        xch[half][row] = l;
     }
     __syncthreads();
-    if (!failed) {
-        if (i0 + tid < p.S) {
-            const float inv = __fdiv_rn(1.0f, __fadd_rn(l, 1e-9f));
-            float *o = p.out + (((size_t)b * p.S + (i0 + tid)) * p.Hq + h) * D;
+    if (!*failed) {
+        if (warp < kFaWorkers / 32) {
+            const int row = tid & (kBQ - 1), half = tid >> 7;
+            if (i0 + row < p.S) {
+                const float inv = __fdiv_rn(1.0f, __fadd_rn(xch[0][row] + xch[1][row], 1e-9f));
+                float *o = p.out + (((size_t)b * p.S + (i0 + row)) * p.Hq + h) * D + half * kDH;
 #pragma unroll
-            for (int e = 0; e < D; e += 4)
-                *reinterpret_cast<float4 *>(o + e) = make_float4(__fmul_rn(ctx[e], inv), __fmul_rn(ctx[e + 1], inv),
-                                                                 __fmul_rn(ctx[e + 2], inv), __fmul_rn(ctx[e + 3], inv));
+                for (int e = 0; e < kDH; e += 4)
+                    *reinterpret_cast<float4 *>(o + e) = make_float4(__fmul_rn(ctx[e], inv), __fmul_rn(ctx[e + 1], inv),
+                                                                     __fmul_rn(ctx[e + 2], inv), __fmul_rn(ctx[e + 3], inv));
+            }
         }
-    } else if (tid == 0) {
+    } else if (tid == kFaWorkers + 32) {
         // A wait gave up: let the copies that are still in flight land before the CTA exits (bounded).
         const long long t0 = clock64();
         while (!bar_try(&q_bar, 0) && clock64() - t0 < kTcWaitCycles) {}
         for (int s = 0; s < G::kStages; ++s) {
             const long long t1 = clock64();
-            while (!bar_try(&full[s], 0) && !bar_try(&full[s], 1) && clock64() - t1 < kTcWaitCycles) {}
+            while (!bar_try(&k_full[s], 0) && !bar_try(&k_full[s], 1) && clock64() - t1 < kTcWaitCycles) {}
+            while (!bar_try(&v_full[s], 0) && !bar_try(&v_full[s], 1) && clock64() - t1 < kTcWaitCycles) {}
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base_s), "r"(G::kTmemCols) : "memory");
+    if (warp == kFaWorkers / 32)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base_s), "r"(G::kTmemCols) : "memory");
 }
 
 __device__ __forceinline__ void split_store(float x, __nv_bfloat16 *hi, __nv_bfloat16 *lo, size_t i) {

@@ -79,6 +79,37 @@ def test_small_models_vs_oracle(L, oracle, over, batch, prompt, wdt):
         assert rel_err(k, oc[l].k) < kv_tol and rel_err(v, oc[l].v) < kv_tol, (l, rel_err(k, oc[l].k), rel_err(v, oc[l].v))
 
 
+@pytest.mark.parametrize("over", [
+    dict(hidden_size=256, intermediate_size=320, num_attention_heads=4, num_key_value_heads=2),                # head_dim 64
+    dict(hidden_size=256, intermediate_size=320, num_attention_heads=2, num_key_value_heads=1, head_dim=128,
+         qk_norm=True, rope_theta=1e6),                                                                        # Qwen3-style
+])
+@pytest.mark.parametrize("wdt", ["f32", "bf16"])
+def test_long_prompt_slices_tensor_core_prefill(L, oracle, over, wdt):
+    """Prompts of 64 positions and more run their attention on the tensor cores.  Two prompt slices (the second
+    one into a partly filled cache), then decode steps over the cache both slices wrote."""
+    cfg = small_cfg(max_seq_len=256, **over)
+    params = make_params(L, cfg, 71, std=0.05, round_bf16=(wdt == "bf16"), random_norms=True)
+    ids = np.random.default_rng(72).integers(0, cfg["vocab_size"], size=(2, 176)).astype(np.float32)
+    model = L.LlamaModel(cfg_obj(L, cfg, wdt))
+    model.load_state(params)
+    caches = model.init_kv_caches(2)
+    m = oracle.Llama(cfg, params, "f64")
+    ocaches = m.init_kv_caches(2)
+    tol = TOL_BF16 if wdt == "bf16" else TOL_F32
+    with L.no_grad():
+        for lo, hi in [(0, 100), (100, 170)] + [(t, t + 1) for t in range(170, 176)]:
+            got = model.forward(ids[:, lo:hi], caches, 0)
+            want = m.forward(ids[:, lo:hi], ocaches)
+            for t in range(hi - lo):
+                assert rel_err(got[:, t], want[:, t]) < tol, (lo, t, rel_err(got[:, t], want[:, t]))
+            assert rel_err(got, want) < TOL_F32
+            assert np.array_equal(got.argmax(-1), want.argmax(-1))
+    for l in range(cfg["num_hidden_layers"]):
+        k, v = caches[l].read()
+        assert rel_err(k, ocaches[l].k) < 5e-5 and rel_err(v, ocaches[l].v) < 5e-5
+
+
 def test_forward_last_and_device_entry_points(L, oracle):
     cfg = small_cfg()
     params = make_params(L, cfg, 31, std=0.08)
