@@ -261,6 +261,35 @@ def run_micro(args):
                               "note": "algorithmic flops 2*M*K*N; the kernel issues twice that (activations as hi+lo bf16)"}),
                   flush=True)
             del keep
+    elif args.micro == "prefill":
+        # SelfAttention::forward over a whole prompt at the Qwen3-8B / Llama-7B attention geometry (32 query heads of
+        # 128, 8 KV heads, f32 weights): four projections on the tensor-core GEMM + the tensor-core prefill attention.
+        # The time is the whole forward; per-kernel times are in the profiler launch list of this command.
+        e, hq, hkv = 4096, 32, 8
+        d = e // hq
+        ws = [L.Tensor.from_array_no_grad(rng.standard_normal(sh, dtype=np.float32) * np.float32(e ** -0.5), ctx)
+              for sh in ((e, e), (hkv * d, e), (hkv * d, e), (e, e))]
+        for b, s_len in ((1, 512), (1, 2048), (2, 4096)):
+            attn = L.SelfAttention(e, hq, hkv, s_len + 8, 1e6, True, ctx)
+            attn.set_weights(*ws)
+            x = L.Tensor.from_array_no_grad(rng.standard_normal((b, s_len, e), dtype=np.float32), ctx)
+            with L.no_grad():
+                _, cache = attn.forward(x, None)
+                state = {}
+
+                def step():
+                    cache.reset()
+                    state["out"] = attn.forward(x, cache)[0]
+
+                ms = _event_time_ms(ctx, stream, step, iters=5)
+            attn_flops = b * hq * s_len * (s_len + 1) / 2 * 4 * d
+            proj_flops = 2.0 * b * s_len * e * (2 * e + 2 * hkv * d)
+            print(json.dumps({"micro": "self_attention_prefill", "batch": b, "positions": s_len, "heads": hq, "kv_heads": hkv,
+                              "head_dim": d, "ms": ms, "attention_gflop": attn_flops / 1e9, "projection_gflop": proj_flops / 1e9,
+                              "tflops_whole_forward": (attn_flops + proj_flops) / (ms * 1e-3) / 1e12,
+                              "note": "algorithmic flops (causal half for the attention); f32 operands go through the tensor "
+                                      "cores as hi/lo bf16 pairs, three products per term"}), flush=True)
+            del attn, x, cache
     else:
         hq, hkv, d = 32, 4, 64
         for b, ctx_len in ATTN_SWEEP:
@@ -313,7 +342,7 @@ def main():
     ap.add_argument("--profile-layers", type=int, default=0,
                     help="profiling aid: truncate the model to this many layers so that a profiler capture stays "
                          "small; the printed line is then marked and is not a benchmark value")
-    ap.add_argument("--micro", choices=["gemv", "attn", "gemm"], default=None,
+    ap.add_argument("--micro", choices=["gemv", "attn", "gemm", "prefill"], default=None,
                     help="secondary measurements instead of the decode benchmark: the vector-matrix sweep or "
                          "decode attention over a static cache (one JSON line per case)")
     ap.add_argument("--batch", type=int, default=1,
