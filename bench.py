@@ -291,8 +291,10 @@ def run_micro(args):
                                       "cores as hi/lo bf16 pairs, three products per term"}), flush=True)
             del attn, x, cache
     else:
-        hq, hkv, d = 32, 4, 64
-        for b, ctx_len in ATTN_SWEEP:
+        # configuration 3's geometry over its sweep, then the Qwen3-8B geometry (32 query heads of 128, 8 KV heads) at the
+        # context of configuration 5
+        cases = [(32, 4, 64, b, n) for b, n in ATTN_SWEEP] + [(32, 8, 128, 16, 4096), (32, 8, 128, 64, 4096)]
+        for hq, hkv, d, b, ctx_len in cases:
             iters = 20
             kv_bytes = b * hkv * ctx_len * d * 4 * 2
             copies = int(min(16, max(1, -(-300e6 // kv_bytes))))
@@ -321,7 +323,7 @@ def run_micro(args):
             ms = _event_time_ms(ctx, stream, step, iters=iters)
             nbytes = kv_bytes + b * hq * d * 8 + b * hkv * d * 8
             gbs = nbytes / (ms * 1e-3) / 1e9
-            print(json.dumps({"micro": "attention_decode", "batch": b, "context": ctx_len, "us": ms * 1e3,
+            print(json.dumps({"micro": "attention_decode", "heads": hq, "kv_heads": hkv, "head_dim": d, "batch": b, "context": ctx_len, "us": ms * 1e3,
                               "algorithmic_bytes": nbytes, "gbs": gbs, "frac_of_measured_peak": gbs / peak,
                               "peak_kind": peak_kind, "working_set_mb": copies * kv_bytes / 1e6}), flush=True)
             del caches
