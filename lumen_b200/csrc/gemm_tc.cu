@@ -1,7 +1,8 @@
 // C[M,N] = A[M,K] . W[N,K]^T (+ residual) on the 5th-generation tensor cores, for the M > 8 branch of
 // ops::matmul (src/ops/matmul.rs:70-92: prefill and batched decode), for bf16 and for f32 weights.
 //
-// sm_100a structure: one CTA per 128 x 128 output tile; thread 0 is the TMA producer (2-D tiled copies
+// sm_100a structure: one CTA per 128 x 128 output tile (for at most 64 output rows: 128 weight rows x 64 output rows, the
+// operands swapped so that the weights fill the 128-row side of the MMA); thread 0 is the TMA producer (2-D tiled copies
 // with 128-byte swizzle into a 4-stage shared-memory ring, mbarrier transaction counts), thread 32 issues
 // tcgen05.mma (kind::f16, bf16 operands, f32 accumulation) with the accumulator in tensor memory (128
 // lanes x 128 columns) and releases each stage with tcgen05.commit; afterwards the four warps read the
@@ -28,18 +29,22 @@ using namespace tc;
 constexpr int kBM = 128;  // tile rows of A
 constexpr int kTcThreads = 128;
 constexpr uint32_t kABytes = kBM * kBK * 2;
-// The tile is 128 x BN: BN = 128, or 64 / 32 for outputs narrower than that.
-// WSPLIT = false: bf16 weights, a stage holds A hi, A lo, B.
-// WSPLIT = true : f32 weights split like the activations, a stage holds A hi, A lo, B hi, B lo.
-template <bool WSPLIT, int BN>
+// The tile is 128 x BN: BN = 128, or 64 / 32 for outputs narrower than that.  The 128-row side ("A") and the BN-row
+// side ("B") each arrive as one or two bf16 matrices (a bf16 matrix, or the hi and lo parts of an f32 one):
+//   plain:   A = activations (hi, lo), B = weights (bf16: one part; f32: hi, lo)   -> tile rows are output rows
+//   swapped: A = weights (bf16: one part; f32: hi, lo), B = activations (hi, lo)   -> tile rows are output columns
+// The swapped form serves few output rows (M <= 64, batched decode): the 128-row side of the MMA is filled with
+// weight rows instead of mostly empty activation rows, so an MMA does useful work on all of its rows.
+template <int NA, int NB, int BN>
 struct TcGeom {
     static constexpr uint32_t kBBytes = BN * kBK * 2;
-    static constexpr uint32_t kStageBytes = 2 * kABytes + (WSPLIT ? 2 : 1) * kBBytes;
+    static constexpr uint32_t kStageBytes = NA * kABytes + NB * kBBytes;
     static constexpr int kStages = (200 * 1024 / kStageBytes) > 6 ? 6 : (200 * 1024 / kStageBytes);
     static constexpr int kTmemCols = BN < 32 ? 32 : BN;
     // Instruction descriptor: f32 accumulator, bf16 A and B, both K-major, N and M of the tile.
     static constexpr uint32_t kIdesc = idesc_bf16(kBM, BN);
 };
+
 struct TcParams {
     float *c;               // output, or the [splits][M][N] partial sums when the K range is split over blockIdx.z
     const float *residual;  // added in the epilogue (null with split K: the reduction kernel adds it)
@@ -48,11 +53,11 @@ struct TcParams {
     DeviceStatus *status;
 };
 
-template <bool WSPLIT, int BN>
+template <int NA, int NB, int BN, bool SWAP>
 __global__ void __launch_bounds__(kTcThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constant__ CUtensorMap map_alo,
                const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_blo, const TcParams p) {
-    using Geom = TcGeom<WSPLIT, BN>;
+    using Geom = TcGeom<NA, NB, BN>;
     constexpr int kStages = Geom::kStages, kBN = BN, kTmemCols = Geom::kTmemCols;
     constexpr uint32_t kStageBytes = Geom::kStageBytes, kBBytes = Geom::kBBytes, kIdesc = Geom::kIdesc;
     extern __shared__ unsigned char smem_raw[];
@@ -62,7 +67,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constan
     __shared__ uint32_t tmem_base_s;
     __shared__ int failed;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int m0 = blockIdx.y * kBM, n0 = blockIdx.x * kBN;
+    // first row of this CTA's tile on the 128-row side and on the BN-row side (blockIdx.x walks the weight rows)
+    const int a0 = (SWAP ? blockIdx.x : blockIdx.y) * kBM, b0 = (SWAP ? blockIdx.y : blockIdx.x) * kBN;
     // This CTA's range of 64-element K blocks: all of them, or slice blockIdx.z when K is split over the grid
     // (few output tiles and a long K: more CTAs stream the weights).  kb below counts from the slice's start.
     const int kb_all = (p.K + kBK - 1) / kBK;
@@ -98,10 +104,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constan
             unsigned char *st = tiles + (size_t)s * kStageBytes;
             bar_expect(&full[s], kStageBytes);
             const int kx = (kb0 + kb) * kBK;
-            tma_load_2d(st, &map_ahi, kx, m0, &full[s]);
-            tma_load_2d(st + kABytes, &map_alo, kx, m0, &full[s]);
-            tma_load_2d(st + 2 * kABytes, &map_b, kx, n0, &full[s]);
-            if (WSPLIT) tma_load_2d(st + 2 * kABytes + kBBytes, &map_blo, kx, n0, &full[s]);
+            tma_load_2d(st, &map_ahi, kx, a0, &full[s]);
+            if (NA == 2) tma_load_2d(st + kABytes, &map_alo, kx, a0, &full[s]);
+            tma_load_2d(st + NA * kABytes, &map_b, kx, b0, &full[s]);
+            if (NB == 2) tma_load_2d(st + NA * kABytes + kBBytes, &map_blo, kx, b0, &full[s]);
         }
     } else if (tid == 32) {
         // ---- MMA issuer ----
@@ -112,13 +118,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constan
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t st = saddr(tiles + (size_t)s * kStageBytes);
-            const uint64_t dhi = smem_desc(st), dlo = smem_desc(st + kABytes), db = smem_desc(st + 2 * kABytes);
-            const uint64_t dblo = smem_desc(st + 2 * kABytes + kBBytes);
+            const uint64_t dhi = smem_desc(st), dlo = smem_desc(st + kABytes), db = smem_desc(st + NA * kABytes);
+            const uint64_t dblo = smem_desc(st + NA * kABytes + kBBytes);
 #pragma unroll
             for (int kk = 0; kk < kBK / 16; ++kk) {  // UMMA K = 16 bf16 = 32 bytes = 2 descriptor units
                 umma_bf16(tmem_base, dhi + 2 * kk, db + 2 * kk, kIdesc, (kb > 0 || kk > 0) ? 1u : 0u);
-                umma_bf16(tmem_base, dlo + 2 * kk, db + 2 * kk, kIdesc, 1u);
-                if (WSPLIT) umma_bf16(tmem_base, dhi + 2 * kk, dblo + 2 * kk, kIdesc, 1u);  // (a_lo . w_lo ~ 2^-18: dropped)
+                if (NA == 2) umma_bf16(tmem_base, dlo + 2 * kk, db + 2 * kk, kIdesc, 1u);
+                if (NB == 2) umma_bf16(tmem_base, dhi + 2 * kk, dblo + 2 * kk, kIdesc, 1u);  // (lo . lo ~ 2^-18: dropped)
             }
             umma_commit(&empty[s]);  // arrives when the MMAs above have finished reading the stage
         }
@@ -131,22 +137,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constan
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     __syncthreads();
     if (have && !failed) {
-        const int row = m0 + warp * 32 + lane;
-        const bool empty_slice = nkb == 0;  // nothing was accumulated: the tile's contribution is zero
+        const int arow = a0 + warp * 32 + lane;  // this thread's row of the tile's 128-row side
+        const bool empty_slice = nkb == 0;       // nothing was accumulated: the tile's contribution is zero
+        float *cbase = p.c + (size_t)blockIdx.z * p.M * p.N;
 #pragma unroll 1
         for (int c0 = 0; c0 < kBN; c0 += 32) {
             uint32_t v[32];
             const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0;
             tmem_ld32(taddr, v);
-            if (row < p.M) {
-                float *crow = p.c + ((size_t)blockIdx.z * p.M + row) * p.N + n0 + c0;
-                const float *rrow = p.residual ? p.residual + (size_t)row * p.N + n0 + c0 : nullptr;
+            if (!SWAP) {
+                if (arow < p.M) {  // output row arow, columns b0 + c0 ..
+                    float *crow = cbase + (size_t)arow * p.N + b0 + c0;
+                    const float *rrow = p.residual ? p.residual + (size_t)arow * p.N + b0 + c0 : nullptr;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        if (b0 + c0 + j < p.N) {
+                            float x = empty_slice ? 0.f : __uint_as_float(v[j]);
+                            if (rrow) x = __fadd_rn(rrow[j], x);  // x + residual as `Tensor + Tensor` (arithmetic.rs:48-52)
+                            crow[j] = x;
+                        }
+                    }
+                }
+            } else if (arow < p.N) {  // output column arow, rows b0 + c0 ..: a warp writes 32 adjacent columns of one row
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
-                    if (n0 + c0 + j < p.N) {
+                    const int m = b0 + c0 + j;
+                    if (m < p.M) {
                         float x = empty_slice ? 0.f : __uint_as_float(v[j]);
-                        if (rrow) x = __fadd_rn(rrow[j], x);  // x + residual as `Tensor + Tensor` (arithmetic.rs:48-52)
-                        crow[j] = x;
+                        if (p.residual) x = __fadd_rn(p.residual[(size_t)m * p.N + arow], x);
+                        cbase[(size_t)m * p.N + arow] = x;
                     }
                 }
             }
@@ -197,20 +216,22 @@ bool gemm_tc_usable(lumen_dtype wdt, size_t M, size_t K, size_t N, const void *w
 
 namespace {
 
-template <bool WSPLIT, int BN>
+template <int NA, int NB, int BN, bool SWAP>
 int launch_tc_kernel(lumen_ctx *ctx, const CUtensorMap &mhi, const CUtensorMap &mlo, const CUtensorMap &mb, const CUtensorMap &mblo,
                      const TcParams &p, size_t M, size_t N, cudaStream_t s) {
-    constexpr size_t smem = (size_t)TcGeom<WSPLIT, BN>::kStages * TcGeom<WSPLIT, BN>::kStageBytes + 1024;  // + slack for the alignment
+    using Geom = TcGeom<NA, NB, BN>;
+    constexpr size_t smem = (size_t)Geom::kStages * Geom::kStageBytes + 1024;  // + slack for the alignment
     static bool attr_set[64] = {false};
     const int dev = ctx->device >= 0 && ctx->device < 64 ? ctx->device : 0;
     if (!attr_set[dev]) {
-        LUMEN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<WSPLIT, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        LUMEN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<NA, NB, BN, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attr_set[dev] = true;
     }
     const int kb_all = (p.K + kBK - 1) / kBK;
     const int splits = (kb_all + p.kb_per_split - 1) / p.kb_per_split;
-    dim3 grid((unsigned)((N + BN - 1) / BN), (unsigned)((M + kBM - 1) / kBM), (unsigned)splits);
-    gemm_tc_kernel<WSPLIT, BN><<<grid, kTcThreads, smem, s>>>(mhi, mlo, mb, mblo, p);
+    const dim3 grid = SWAP ? dim3((unsigned)((N + kBM - 1) / kBM), (unsigned)((M + BN - 1) / BN), (unsigned)splits)
+                           : dim3((unsigned)((N + BN - 1) / BN), (unsigned)((M + kBM - 1) / kBM), (unsigned)splits);
+    gemm_tc_kernel<NA, NB, BN, SWAP><<<grid, kTcThreads, smem, s>>>(mhi, mlo, mb, mblo, p);
     LUMEN_LAUNCHED(ctx);
     return LUMEN_OK;
 }
@@ -249,18 +270,31 @@ int launch_gemm_tc(lumen_ctx *ctx, const float *a, const void *w, lumen_dtype wd
         if (e != cudaSuccess) rc = cuda_fail(ctx, e, "split_bf16_kernel launch");
         else ctx->launches += 1;
     }
-    CUtensorMap map_hi, map_lo, map_b, map_blo;
-    if (rc == LUMEN_OK) rc = make_map(ctx, &map_hi, hi, M, K, kBM);
-    if (rc == LUMEN_OK) rc = make_map(ctx, &map_lo, lo, M, K, kBM);
-    const int bn = pick_bn(M, N, ctx->num_sms);
-    if (rc == LUMEN_OK) rc = make_map(ctx, &map_b, wsplit ? (const void *)whi : w, N, K, bn);
-    if (rc == LUMEN_OK) rc = make_map(ctx, &map_blo, wsplit ? (const void *)wlo : w, N, K, bn);
+    // Few output rows: the weights take the 128-row side of the tile and the activations the 64-row side.
+    static const bool no_swap = [] {
+        const char *e = getenv("LUMEN_NO_TC_SWAP");
+        return e && e[0] == '1';
+    }();
+    const bool swap = M <= 64 && !no_swap;
+    CUtensorMap map_hi, map_lo, map_b, map_blo;  // 128-row side (hi, lo), BN-row side (hi, lo)
+    const int bn = swap ? 64 : pick_bn(M, N, ctx->num_sms);
+    if (!swap) {
+        if (rc == LUMEN_OK) rc = make_map(ctx, &map_hi, hi, M, K, kBM);
+        if (rc == LUMEN_OK) rc = make_map(ctx, &map_lo, lo, M, K, kBM);
+        if (rc == LUMEN_OK) rc = make_map(ctx, &map_b, wsplit ? (const void *)whi : w, N, K, bn);
+        if (rc == LUMEN_OK) rc = make_map(ctx, &map_blo, wsplit ? (const void *)wlo : w, N, K, bn);
+    } else {
+        if (rc == LUMEN_OK) rc = make_map(ctx, &map_hi, wsplit ? (const void *)whi : w, N, K, kBM);
+        if (rc == LUMEN_OK) rc = make_map(ctx, &map_lo, wsplit ? (const void *)wlo : w, N, K, kBM);
+        if (rc == LUMEN_OK) rc = make_map(ctx, &map_b, hi, M, K, bn);
+        if (rc == LUMEN_OK) rc = make_map(ctx, &map_blo, lo, M, K, bn);
+    }
     // Few output tiles (one row of tiles: M <= 128) and many K blocks: split K over blockIdx.z so that about
     // every SM streams a share of W; the slices' partial tiles are summed in slice order by a second kernel.
     const int kb_all = (int)((K + kBK - 1) / kBK);
     int splits = 1;
     if (M <= (size_t)kBM) {
-        const int tiles = (int)((N + bn - 1) / bn);
+        const int tiles = (int)((N + (swap ? kBM : bn) - 1) / (swap ? kBM : bn));
         splits = std::max(1, std::min(std::min(ctx->num_sms / std::max(tiles, 1), kb_all / 4), 16));
     }
     const int kb_per_split = (kb_all + splits - 1) / splits;
@@ -270,9 +304,10 @@ int launch_gemm_tc(lumen_ctx *ctx, const float *a, const void *w, lumen_dtype wd
     if (rc == LUMEN_OK) {
         TcParams p{splits > 1 ? static_cast<float *>(partial) : c, splits > 1 ? nullptr : residual, (int)M, (int)N, (int)K,
                    kb_per_split, ctx->d_status};
-#define LUMEN_TC(WS, BN_) launch_tc_kernel<WS, BN_>(ctx, map_hi, map_lo, map_b, map_blo, p, M, N, s)
-        if (wsplit) rc = bn == 128 ? LUMEN_TC(true, 128) : bn == 64 ? LUMEN_TC(true, 64) : LUMEN_TC(true, 32);
-        else rc = bn == 128 ? LUMEN_TC(false, 128) : bn == 64 ? LUMEN_TC(false, 64) : LUMEN_TC(false, 32);
+#define LUMEN_TC(NA_, NB_, BN_, SW_) launch_tc_kernel<NA_, NB_, BN_, SW_>(ctx, map_hi, map_lo, map_b, map_blo, p, M, N, s)
+        if (swap) rc = wsplit ? LUMEN_TC(2, 2, 64, true) : LUMEN_TC(1, 2, 64, true);
+        else if (wsplit) rc = bn == 128 ? LUMEN_TC(2, 2, 128, false) : bn == 64 ? LUMEN_TC(2, 2, 64, false) : LUMEN_TC(2, 2, 32, false);
+        else rc = bn == 128 ? LUMEN_TC(2, 1, 128, false) : bn == 64 ? LUMEN_TC(2, 1, 64, false) : LUMEN_TC(2, 1, 32, false);
 #undef LUMEN_TC
         if (rc == LUMEN_OK && splits > 1) {
             const size_t mn = M * N;
