@@ -20,14 +20,14 @@ def _gpu_count() -> int:
     return torch.cuda.device_count()
 
 
-def _run(cfg: dict, world: int, dtype: str):
+def _run(cfg: dict, world: int, dtype: str, prompt: int = 7):
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     procs = []
     for r in range(world):
         env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
-                   TP_TEST_CFG=json.dumps(cfg), TP_TEST_DTYPE=dtype, NCCL_NVLS_ENABLE="0")
+                   TP_TEST_CFG=json.dumps(cfg), TP_TEST_DTYPE=dtype, TP_TEST_PROMPT=str(prompt), NCCL_NVLS_ENABLE="0")
         procs.append(subprocess.Popen([sys.executable, str(ROOT / "tests" / "tp_gpu_worker.py")], env=env,
                                       stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True))
     outs = []
@@ -50,6 +50,18 @@ def test_tp2_matches_oracle(dtype):
     cfg = small_cfg(vocab_size=96, hidden_size=128, num_attention_heads=8, num_key_value_heads=2, intermediate_size=320,
                     num_hidden_layers=3, max_seq_len=32)
     res = _run(cfg, 2, dtype)
+    assert res["max_rel_err"] < (TOL_F32 if dtype == "f32" else TOL_BF16), res
+    assert res["argmax_equal"]
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_tp2_long_prompt(dtype):
+    """A 100-token prompt: per-rank heads through the tensor-core GEMM and prefill attention, all-reduce per block."""
+    if _gpu_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    cfg = small_cfg(vocab_size=96, hidden_size=256, num_attention_heads=4, num_key_value_heads=2, intermediate_size=320,
+                    num_hidden_layers=2, max_seq_len=128)
+    res = _run(cfg, 2, dtype, prompt=100)
     assert res["max_rel_err"] < (TOL_F32 if dtype == "f32" else TOL_BF16), res
     assert res["argmax_equal"]
 

@@ -29,7 +29,7 @@ def main():
     params = {n: w for n, w in synth.iter_params(lcfg, 3, std=0.05, round_bf16=(wdt == "bf16"))}
     for n, w in params.items():
         model.set_param(n, w)  # every rank passes the full tensor; the library keeps its slice
-    prompt, steps = 7, 6
+    prompt, steps = int(os.environ.get("TP_TEST_PROMPT", "7")), 6
     ids = synth.token_ids(5, prompt + steps, cfg["vocab_size"])
     caches = model.init_kv_caches(1)
     got = []
