@@ -112,8 +112,18 @@ WORKLOADS = {  # name -> (synth config, label, default weight dtype)
 }
 
 
+def load_synth():
+    """The seeded generators (lumen_b200/synth.py, numpy only) loaded by file path: the CPU arm must not import
+    the package, whose import loads the CUDA library."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("_lumen_synth", ROOT / "lumen_b200" / "synth.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
 def tinyllama_cfg(dtype: str, max_seq: int, layers: int = 0, workload: str = "tinyllama"):
-    from lumen_b200 import synth
+    synth = load_synth()
     cfg = dict(getattr(synth, WORKLOADS[workload][0]))
     cfg["max_seq_len"] = max_seq
     if layers:
@@ -122,10 +132,27 @@ def tinyllama_cfg(dtype: str, max_seq: int, layers: int = 0, workload: str = "ti
 
 
 def gen_params(cfg: dict, dtype: str, workload: str = "tinyllama"):
-    from lumen_b200 import synth
-    from lumen_b200.llama import LlamaConfig
+    synth = load_synth()
     gen = synth.iter_params if workload == "tinyllama" else synth.iter_params_tiled
-    return gen(LlamaConfig(**cfg), 0, std=0.02, round_bf16=(dtype == "bf16"))
+    return gen(cfg, 0, std=0.02, round_bf16=(dtype == "bf16"))
+
+
+def stream_bytes(cfg: dict, dtype: str, tp: int = 1) -> int:
+    """Weight bytes one decode step reads on one rank (the embedding contributes one row per token, not counted)."""
+    e = 2 if dtype == "bf16" else 4
+    h, i, v, l = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"], cfg["num_hidden_layers"]
+    d = cfg.get("head_dim") or h // cfg["num_attention_heads"]
+    hq, hkv = cfg["num_attention_heads"] // tp, max(1, cfg["num_key_value_heads"] // tp)
+    qkv_rows = (hq + 2 * hkv) * d
+    per_layer = (qkv_rows * h + h * hq * d + 3 * (i // tp) * h) * e + 2 * h * 4 + (2 * d * 4 if cfg.get("qk_norm") else 0)
+    return l * per_layer + h * 4 + (v // tp) * h * e
+
+
+def make_config(args, workload: str, dtype: str, batch: int, max_seq: int, world: int, cfg: dict) -> dict:
+    """The `config` object of the JSON line: the same for the GPU arm and the CPU arm."""
+    return {"workload": f"{WORKLOADS[workload][1]}_{dtype}_batch{batch}_decode", "weights": dtype, "batch": batch,
+            "prompt_len": PROMPT_LEN, "max_seq_len": max_seq, "parallelism": f"tp{world}",
+            "l2": "inputs larger than L2: every step streams %.2f GB of weights per GPU" % (stream_bytes(cfg, dtype, world) / 1e9)}
 
 
 def algorithmic_bytes_per_step(cfg: dict, weight_bytes: int, ctx_len_mean: float, tp: int, batch: int = 1) -> float:
@@ -136,44 +163,54 @@ def algorithmic_bytes_per_step(cfg: dict, weight_bytes: int, ctx_len_mean: float
     return weight_bytes + batch * (kv + cfg["hidden_size"] * 4 + cfg["vocab_size"] * 4 / tp)
 
 
-def cpu_decode(cfg: dict, params: dict, ids: np.ndarray, budget_s: float, max_steps: int):
-    """Times the CPU restatement on a bounded sample: full 32-token prefill, then decode steps until the
-    budget is spent.  Returns (tokens/s over the decode steps, steps, threads, logits of those steps)."""
+def cpu_decode(cfg: dict, params: dict, ids: np.ndarray, budget_s: float, max_steps: int, warmup: int = 0):
+    """Times the CPU restatement on a bounded sample: full prompt prefill and `warmup` untimed decode steps, then
+    decode steps until `max_steps` or the budget is reached.  Every host core is used whatever OMP_NUM_THREADS says
+    (launchers such as torchrun set it to 1).  Returns (tokens/s over the timed steps, timed steps, threads,
+    logits of the warm-up and timed steps)."""
     from oracle import binding as O
+    threads = O.set_num_threads()
     model = O.Llama(cfg, params, "f32")
     caches = model.init_kv_caches(1)
     model.forward(ids[None, :PROMPT_LEN], caches)
     logits = []
+    pos = PROMPT_LEN
+    for _ in range(warmup):
+        logits.append(model.forward(ids[None, pos:pos + 1], caches)[0, 0])
+        pos += 1
     t0 = time.perf_counter()
     steps = 0
     while steps < max_steps:
-        logits.append(model.forward(ids[None, PROMPT_LEN + steps:PROMPT_LEN + steps + 1], caches)[0, 0])
+        logits.append(model.forward(ids[None, pos:pos + 1], caches)[0, 0])
+        pos += 1
         steps += 1
         if time.perf_counter() - t0 > budget_s:
             break
     dt = time.perf_counter() - t0
-    return steps / dt, steps, O.num_threads(), np.stack(logits)
+    return steps / dt, steps, threads, np.stack(logits)
 
 
 def run_reference(args):
-    """--impl reference: the reference's CPU path (restated in C; the Rust crate cannot be built here)."""
+    """--impl reference: the reference's CPU path (restated in C; the Rust crate cannot be built here) on all host
+    cores: the same prompt, `--warmup` untimed and `--steps` timed teacher-forced decode steps (bounded by a time
+    budget).  Loads neither the package nor the CUDA library."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
     cfg = tinyllama_cfg(args.dtype, 2048)
     params = dict(gen_params(cfg, args.dtype))
-    from lumen_b200 import synth
-    ids = synth.token_ids(1, PROMPT_LEN + args.warmup + args.steps + 1, cfg["vocab_size"])
-    budget = 90.0
-    tps, steps, threads, _ = cpu_decode(cfg, params, ids, budget, max(1, args.steps))
+    ids = load_synth().token_ids(1, PROMPT_LEN + args.warmup + args.steps + 1, cfg["vocab_size"])
+    budget = 120.0
+    tps, steps, threads, _ = cpu_decode(cfg, params, ids, budget, max(1, args.steps), args.warmup)
     line = {
         "impl": "reference", "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
-        "warmup": 0, "ms_per_step": 1000.0 / tps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "warmup": args.warmup, "ms_per_step": 1000.0 / tps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"tinyllama_1.1b_{args.dtype}_batch1_decode", "prompt_len": PROMPT_LEN, "max_seq_len": 2048,
-                   "note": "Rust reference cannot be built here (no rustc); this times its C/OpenMP restatement"},
+        "config": make_config(args, "tinyllama", args.dtype, 1, 2048, args.gpus, cfg),
+        "note": "the Rust reference cannot be built here (no rustc): this times its C/OpenMP restatement on the host cores",
         "cpu_baseline": {"value": tps, "unit": UNIT, "cores": threads, "kind": "port",
-                         "sample": f"{PROMPT_LEN}-token prefill (untimed) + {steps} decode steps, <= {budget:.0f} s"},
+                         "sample": f"{PROMPT_LEN}-token prefill and {args.warmup} warm-up steps (untimed) + {steps} decode steps, "
+                                   f"<= {budget:.0f} s"},
         "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -352,6 +389,9 @@ def main():
                          "per-operator kernels: tensor-core GEMMs and the tiled attention kernel)")
     ap.add_argument("--prompt-len", type=int, default=32,
                     help="tokens of the (untimed) prefill; 32 is the metric's configuration, 512 configuration 4's")
+    ap.add_argument("--repeats", type=int, default=0,
+                    help="repetitions of the timed K-step region (0: as many as make the timed regions add up to ~0.5 s, 3..25)")
+    ap.add_argument("--no-extra", action="store_true", help="N > 1: skip the short Llama-2-7B run reported beside the headline")
     ap.add_argument("--prefill-chunk", type=int, default=0,
                     help="prefill the prompt in slices of this many positions (0: one forward)")
     args = ap.parse_args()
@@ -398,7 +438,7 @@ def main():
     ctx = L.Context(local_rank, rank, world, nccl_id)
     model = L.LlamaModel(L.LlamaConfig(**cfg, weight_dtype=args.dtype), ctx)
     B = max(1, args.batch)
-    keep_params = (rank == 0 and world == 1 and not args.no_cpu_baseline and not big and B == 1)
+    keep_params = (rank == 0 and not args.no_cpu_baseline and not big and B == 1 and not args.profile_layers)
     params = {}
     for name, w in gen_params(cfg, args.dtype, args.workload):
         model.set_param(name, w)
@@ -444,8 +484,20 @@ def main():
         ctx.synchronize()
         prefill_ms.append((time.perf_counter() - t0) * 1000.0)
 
-    # ---- device-resident throughput --------------------------------------------------------------------
-    with L.no_grad():
+    # The timed region is exactly K steps; it is repeated R times (fresh prompt prefill and W untimed warm-up steps
+    # before each repetition, so every repetition covers the same context lengths) and the median repetition is the
+    # value.  R is chosen from the first repetition so that the timed regions add up to about half a second.
+    def repeat_count(first_ms: float) -> int:
+        if args.repeats > 0:
+            return args.repeats
+        r = int(np.ceil(500.0 / max(first_ms, 1e-3)))
+        return max(3, min(25, r))
+
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches = 0
+
+    def timed_device_steps() -> float:
+        nonlocal launches
         prefill()
         pos = PROMPT_LEN
         for _ in range(args.warmup):
@@ -453,7 +505,6 @@ def main():
             pos += 1
         barrier()
         launches0 = ctx.launch_count
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         sampler.active = True
         e0.record(stream)
         for _ in range(args.steps):
@@ -462,28 +513,41 @@ def main():
         e1.record(stream)
         barrier()
         sampler.active = False
-        dev_ms = max_over_ranks(e0.elapsed_time(e1))
         launches = ctx.launch_count - launches0
+        return max_over_ranks(e0.elapsed_time(e1))
 
-        # ---- end to end through the host API: id in (pinned staging inside the library), logits out -------
+    host_logits = []
+
+    def timed_host_steps() -> float:
+        # end to end through the host API: id in (pinned staging inside the library), logits out, every step
         prefill()
         pos = PROMPT_LEN
-        host_logits = []
         for _ in range(args.warmup):
             model.forward(ids_all[pos][:, None], caches)
             pos += 1
         barrier()
+        keep = not host_logits
         t0 = time.perf_counter()
         e0.record(stream)
         for _ in range(args.steps):
             lg = model.forward(ids_all[pos][:, None], caches)
-            if len(host_logits) < 4:
+            if keep and len(host_logits) < 4:
                 host_logits.append(lg[0, 0].copy())
             pos += 1
         e1.record(stream)
         barrier()
-        e2e_wall_ms = (time.perf_counter() - t0) * 1000.0
-        e2e_ms = max_over_ranks(max(e0.elapsed_time(e1), e2e_wall_ms))
+        wall_ms = (time.perf_counter() - t0) * 1000.0
+        return max_over_ranks(max(e0.elapsed_time(e1), wall_ms))
+
+    with L.no_grad():
+        dev_runs = [timed_device_steps()]
+        for _ in range(repeat_count(dev_runs[0]) - 1):
+            dev_runs.append(timed_device_steps())
+        dev_ms = float(np.median(dev_runs))
+        e2e_runs = [timed_host_steps()]
+        for _ in range(min(len(dev_runs), repeat_count(e2e_runs[0])) - 1):
+            e2e_runs.append(timed_host_steps())
+        e2e_ms = float(np.median(e2e_runs))
 
         # ---- the same steps with the sampler on the device: only a token id comes back (single GPU) --------
         sampled_ms = None
@@ -510,57 +574,117 @@ def main():
     bytes_step = algorithmic_bytes_per_step(cfg, weight_bytes, ctx_mean, world, B)
     peak, peak_kind = measured_hbm_peak()
     achieved = bytes_step / (dev_ms / args.steps / 1000.0) / 1e9
+    mega = launches == args.steps
+    # measured DRAM traffic exists for one case only: the persistent kernel, f32 weights, one GPU, the TinyLlama shape
+    traffic = bytes_step * MEGA_TRAFFIC_RATIO if (mega and world == 1 and args.dtype == "f32" and args.workload == "tinyllama") else None
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
+                "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
+                "kernel": ("decode_mega_kernel: one persistent launch runs the whole token" if mega else
+                           "whole decode step (CUDA graph of %d kernels)" % (launches // max(args.steps, 1))),
+                "algorithmic_bytes_per_step": bytes_step, "per": "GPU"}
+    if traffic is not None:
+        roofline["traffic_note"] = ("ncu dram bytes of a capture of the same kernel on a 4-layer truncation of the model, scaled by "
+                                    "algorithmic bytes")
     line = {
         "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"{WORKLOADS[args.workload][1]}_{args.dtype}_batch{B}_decode", "weights": args.dtype, "batch": B,
-                   "prompt_len": PROMPT_LEN, "max_seq_len": max_seq, "parallelism": f"tp{world}",
-                   "l2": "inputs larger than L2: every step streams %.2f GB of weights" % (weight_bytes / 1e9)},
+        "config": make_config(args, args.workload, args.dtype, B, max_seq, world, cfg),
+        "repeats": {"n": len(dev_runs), "value": "median", "ms_per_step_min": min(dev_runs) / args.steps,
+                    "ms_per_step_max": max(dev_runs) / args.steps, "timed_s": sum(dev_runs) / 1000.0,
+                    "e2e_n": len(e2e_runs), "e2e_ms_per_step_min": min(e2e_runs) / args.steps,
+                    "e2e_ms_per_step_max": max(e2e_runs) / args.steps},
         "e2e": {"value": e2e_tps, "unit": UNIT, "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B * cfg["vocab_size"],
                 "ms_per_step": e2e_ms / args.steps},
         "e2e_sampled": (None if sampled_ms is None else
                         {"value": args.steps / (sampled_ms / 1000.0), "unit": UNIT, "h2d_bytes_per_step": 4 + 4 * 96,
                          "d2h_bytes_per_step": 4, "ms_per_step": sampled_ms / args.steps,
                          "note": "forward + top-p sampling on the device (temperature 0.8, top_p 0.9, repetition penalty 1.1 "
-                                 "over 96 tokens): the reference samples on the host from the full logits.  Random weights give a flat "
-                                 "distribution whose nucleus holds ~90 % of the vocabulary, the worst case for the sequential "
-                                 "cumulative sum the sampler keeps for parity"}),
+                                 "over 96 tokens): the reference samples on the host from the full logits"}),
         "gpu_launches": int(launches),
-        # untimed part, for information: host wall clock of the second prefill (the first one pays the one-time set-up)
+        # untimed part, for information: host wall clock of the last prefill (the first one pays the one-time set-up)
         "prefill": {"tokens": B * PROMPT_LEN, "ms": prefill_ms[-1], "tokens_per_s": B * PROMPT_LEN / (prefill_ms[-1] / 1000.0),
                     "slice": args.prefill_chunk if args.prefill_chunk > 0 else PROMPT_LEN},
         "clocks": sampler.summary(),
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": (bytes_step * MEGA_TRAFFIC_RATIO if launches == args.steps else None),
-                     "traffic_note": "ncu dram bytes of a capture of the same kernel on a 4-layer truncation of the model, "
-                                     "scaled by algorithmic bytes", "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
-                     "kernel": ("decode_mega_kernel: one persistent launch runs the whole token"
-                                if launches == args.steps else
-                                "whole decode step (CUDA graph of %d kernels)" % (launches // max(args.steps, 1))),
-                     "algorithmic_bytes_per_step": bytes_step},
+        "roofline": roofline,
     }
     if args.profile_layers:
         line["profile_only"] = f"model truncated to {args.profile_layers} layers: not a benchmark value"
         line["config"]["workload"] += f"_truncated_{args.profile_layers}_layers"
     if keep_params:
-        tps_cpu, n, threads, cpu_logits = cpu_decode(cfg, params, ids[:PROMPT_LEN + args.warmup + 4 + 64], args.cpu_budget_s,
-                                                     args.warmup + 4)
-        line["cpu_baseline"] = {"value": tps_cpu, "unit": UNIT, "cores": threads, "kind": "port",
-                                "sample": f"{PROMPT_LEN}-token prefill (untimed) + {n} decode steps of the same workload"}
-        # the CPU steps cover the warm-up positions and then the first timed ones: compare where they overlap
-        k = min(len(host_logits), n - args.warmup)
+        # The CPU restatement on this box's host cores (rank 0).  N = 1: timed on a bounded sample, the reported baseline.
+        # Every N: its logits at the first timed positions are compared with what the GPU arm returned there.
+        n_cpu = max(4, min(args.steps, 256)) if world == 1 else 4
+        tps_cpu, n, threads, cpu_logits = cpu_decode(cfg, params, ids, args.cpu_budget_s, n_cpu, args.warmup)
+        if world == 1:
+            line["cpu_baseline"] = {"value": tps_cpu, "unit": UNIT, "cores": threads, "kind": "port",
+                                    "sample": f"{PROMPT_LEN}-token prefill and {args.warmup} warm-up steps (untimed) + {n} decode steps of "
+                                              f"the same workload, <= {args.cpu_budget_s:.0f} s"}
+        k = min(len(host_logits), n)
         if k > 0:
             errs = [float(np.abs(host_logits[i] - cpu_logits[args.warmup + i]).max() / np.abs(cpu_logits[args.warmup + i]).max())
                     for i in range(k)]
-            line["parity_vs_cpu"] = {"steps_compared": k, "max_rel_err": max(errs),
+            line["parity_vs_cpu"] = {"steps_compared": k, "max_rel_err": max(errs), "tolerance": 1e-4 if args.dtype == "f32" else 1e-2,
+                                     "cores": threads,
                                      "argmax_equal": all(int(host_logits[i].argmax()) == int(cpu_logits[args.warmup + i].argmax())
                                                          for i in range(k))}
+    if world > 1 and not args.no_extra and args.workload == "tinyllama" and not args.profile_layers and B == 1:
+        # the tensor-parallel shape the scaling claim is about, measured in the same process: Llama-2-7B, bf16 weights
+        del model, caches
+        extra = run_extra_7b(L, ctx, torch, dist, rank, world, local_rank)
+        if extra:
+            line["extra"] = extra
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
     return 0
+
+
+def run_extra_7b(L, ctx, torch, dist, rank, world, local_rank, prompt: int = 32, steps: int = 32, warmup: int = 4):
+    """A short decode run at the Llama-2-7B shape (bf16 weights, tiled synthetic values), tensor-parallel over the
+    same ranks: tokens/s, ms per step and the per-GPU fraction of the HBM peak (device-resident ids and logits)."""
+    synth = load_synth()
+    cfg = dict(synth.LLAMA2_7B)
+    cfg["max_seq_len"] = 256
+    model = L.LlamaModel(L.LlamaConfig(**cfg, weight_dtype="bf16"), ctx)
+    for name, w in synth.iter_params_tiled(cfg, 0, std=0.02, round_bf16=True):
+        model.set_param(name, w)
+    ids = synth.token_ids(4, prompt + warmup + steps + 1, cfg["vocab_size"])
+    caches = model.init_kv_caches(1)
+    d_ids = L.Tensor.from_array_no_grad(ids, ctx)
+    d_logits = L.Tensor.from_array_no_grad(np.zeros(cfg["vocab_size"], np.float32), ctx)
+    stream = torch.cuda.ExternalStream(ctx.stream, device=torch.device("cuda", local_rank))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    runs = []
+    with L.no_grad():
+        for _ in range(3):
+            model.reset_kv_caches(caches)
+            model.forward(ids[None, :prompt], caches, 0, last_only=True)
+            pos = prompt
+            for _ in range(warmup):
+                model.forward_device(d_ids.data_ptr + 4 * pos, 1, 1, caches, d_logits.data_ptr)
+                pos += 1
+            ctx.synchronize()
+            dist.barrier()
+            e0.record(stream)
+            for _ in range(steps):
+                model.forward_device(d_ids.data_ptr + 4 * pos, 1, 1, caches, d_logits.data_ptr)
+                pos += 1
+            e1.record(stream)
+            ctx.synchronize()
+            dist.barrier()
+            t = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            runs.append(float(t.item()))
+    ms = float(np.median(runs))
+    ctx_mean = prompt + warmup + (steps - 1) / 2.0
+    bytes_step = algorithmic_bytes_per_step(cfg, model.weight_bytes_per_step, ctx_mean, world, 1)
+    peak, peak_kind = measured_hbm_peak()
+    gbs = bytes_step / (ms / steps / 1000.0) / 1e9
+    return {"workload": f"llama2_7b_bf16_batch1_decode_tp{world}", "prompt_len": prompt, "steps": steps, "warmup": warmup,
+            "value": steps / (ms / 1000.0), "unit": UNIT, "ms_per_step": ms / steps, "repeats": len(runs),
+            "per_gpu_hbm_gbs": gbs, "per_gpu_frac": gbs / peak, "peak_kind": f"of {peak_kind}"}
 
 
 if __name__ == "__main__":

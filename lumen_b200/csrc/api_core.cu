@@ -61,6 +61,7 @@ int check_device_status(lumen_ctx *ctx) {
     LUMEN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     if (ctx->h_status->code != 0) {
         int code = ctx->h_status->code, d0 = ctx->h_status->detail0, d1 = ctx->h_status->detail1;
+        ctx->abort_gen += 1;  // host mirrors of the cache lengths may be ahead of the device: see kv_resync_len
         LUMEN_CUDA(ctx, cudaMemsetAsync(ctx->d_status, 0, sizeof(DeviceStatus), ctx->stream));
         // A persistent decode kernel that gave up leaves its abort flag raised: clear it.
         LUMEN_CUDA(ctx, cudaMemsetAsync(ctx->d_mega_sync, 0, 16, ctx->stream));
@@ -68,6 +69,17 @@ int check_device_status(lumen_ctx *ctx) {
         if (code == LUMEN_ERR_TIMEOUT) return set_error(ctx, code, "device-side wait gave up (site %d, value %d)", d0, d1);
         return set_error(ctx, code, "device status %d (%d, %d)", code, d0, d1);
     }
+    return LUMEN_OK;
+}
+
+int kv_resync_len(lumen_kv_cache *c) {
+    if (!c || !c->ctx || c->seen_abort == c->ctx->abort_gen) return LUMEN_OK;
+    lumen_ctx *ctx = c->ctx;
+    int dev_len = 0;
+    LUMEN_CUDA(ctx, cudaMemcpyAsync(&dev_len, c->d_len, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    LUMEN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    c->len = dev_len < 0 ? 0 : (size_t)dev_len;
+    c->seen_abort = ctx->abort_gen;
     return LUMEN_OK;
 }
 
@@ -114,7 +126,7 @@ int lumen_ctx_create(int device, int tp_rank, int tp_size, const void *nccl_uniq
     ctx->tp_size = tp_size;
     auto fail = [&](cudaError_t err, const char *what) {
         fprintf(stderr, "lumen_ctx_create: %s: %s\n", what, cudaGetErrorString(err));
-        delete ctx;
+        lumen_ctx_destroy(ctx);  // frees whatever was created so far
         return LUMEN_ERR_CUDA;
     };
     if ((e = cudaSetDevice(device)) != cudaSuccess) return fail(e, "cudaSetDevice");
@@ -123,7 +135,7 @@ int lumen_ctx_create(int device, int tp_rank, int tp_size, const void *nccl_uniq
     if (prop.major != 10) {
         fprintf(stderr, "lumen_ctx_create: device %d is sm_%d%d; this library is built for sm_100a only\n", device,
                 prop.major, prop.minor);
-        delete ctx;
+        lumen_ctx_destroy(ctx);
         return LUMEN_ERR_UNSUPPORTED;
     }
     ctx->num_sms = prop.multiProcessorCount;

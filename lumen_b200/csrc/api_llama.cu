@@ -85,6 +85,8 @@ struct lumen_llama {
     int *d_sched_count = nullptr;
     size_t sched_capacity = 0;
     int sched_stride = 0;
+    CUtensorMap *d_tmaps = nullptr;   // tensor maps of the segmented matrices (see MegaParams::tmaps); null when there are none
+    size_t tmaps_capacity = 0;
     const void *mega_key = nullptr;  // first cache's k pointer the layer table was built for
     unsigned long long *d_trace = nullptr;  // phase timestamps of the last persistent step (LUMEN_DECODE_TRACE=1)
     uint2 *d_exchange = nullptr;            // tagged activation exchange buffers of the persistent kernel
@@ -286,6 +288,7 @@ int check_caches(lumen_llama *m, size_t b, size_t s, lumen_kv_cache **caches, si
     for (size_t l = 0; l < m->L; ++l) {
         lumen_kv_cache *c = caches[l];
         if (!c) return set_error(ctx, LUMEN_ERR_INVALID, "null KV cache for layer %zu", l);
+        LUMEN_TRY(kv_resync_len(c));
         if (c->b != b || c->h_kv != m->hkv_l || c->d != m->D)
             return set_error(ctx, LUMEN_ERR_SHAPE, "KV cache %zu geometry [%zu,%zu,%zu,%zu] does not match batch %zu / model", l, c->b, c->h_kv, c->max_seq, c->d, b);
         if (c->len != caches[0]->len) return set_error(ctx, LUMEN_ERR_INVALID, "KV caches have different lengths");
@@ -321,7 +324,8 @@ int run_mega(lumen_llama *m, lumen_kv_cache **caches) {
         std::vector<uint4> entries;
         std::vector<int> counts;
         int stride = 0;
-        decode_mega_build_schedule(p, host.data(), ctx->num_sms, entries, counts, stride);
+        std::vector<CUtensorMap> tmaps;
+        decode_mega_build_schedule(p, host.data(), ctx->num_sms, entries, counts, stride, tmaps);
         LUMEN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // earlier launches may still read the tables
         if (!m->d_mega_layers) LUMEN_CUDA(ctx, cudaMalloc(&m->d_mega_layers, std::max<size_t>(m->L, 1) * sizeof(MegaLayer)));
         if (m->d_sched && m->sched_capacity < entries.size()) {
@@ -333,6 +337,21 @@ int run_mega(lumen_llama *m, lumen_kv_cache **caches) {
             m->sched_capacity = entries.size();
         }
         if (!m->d_sched_count) LUMEN_CUDA(ctx, cudaMalloc(&m->d_sched_count, counts.size() * sizeof(int)));
+        if (m->d_tmaps && m->tmaps_capacity < tmaps.size()) {
+            cudaFree(m->d_tmaps);
+            m->d_tmaps = nullptr;
+        }
+        if (!tmaps.empty()) {
+            if (!m->d_tmaps) {
+                LUMEN_CUDA(ctx, cudaMalloc(&m->d_tmaps, tmaps.size() * sizeof(CUtensorMap)));
+                m->tmaps_capacity = tmaps.size();
+            }
+            LUMEN_CUDA(ctx, cudaMemcpy(m->d_tmaps, tmaps.data(), tmaps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice));
+        } else if (m->d_tmaps) {
+            cudaFree(m->d_tmaps);
+            m->d_tmaps = nullptr;
+            m->tmaps_capacity = 0;
+        }
         LUMEN_CUDA(ctx, cudaMemcpy(m->d_mega_layers, host.data(), m->L * sizeof(MegaLayer), cudaMemcpyHostToDevice));
         LUMEN_CUDA(ctx, cudaMemcpy(m->d_sched, entries.data(), entries.size() * sizeof(uint4), cudaMemcpyHostToDevice));
         LUMEN_CUDA(ctx, cudaMemcpy(m->d_sched_count, counts.data(), counts.size() * sizeof(int), cudaMemcpyHostToDevice));
@@ -341,6 +360,7 @@ int run_mega(lumen_llama *m, lumen_kv_cache **caches) {
     }
     p.layers = m->d_mega_layers;
     p.sched = m->d_sched; p.sched_count = m->d_sched_count; p.sched_stride = m->sched_stride;
+    p.tmaps = m->d_tmaps;
     p.cos_t = m->cos_t; p.sin_t = m->sin_t;
     p.eps = m->cfg.rms_norm_eps;
     p.scale = 1.0f / sqrtf((float)m->D);
@@ -391,7 +411,10 @@ int run_mega(lumen_llama *m, lumen_kv_cache **caches) {
 }
 
 bool mega_usable(lumen_llama *m, size_t b, size_t s) {
-    if (!m->use_mega || b != 1 || s != 1 || m->ctx->tp_size > 8 || m->L == 0) return false;
+    if (!m->use_mega || b != 1 || s != 1 || m->L == 0) return false;
+    // the kernel's fused all-reduce has forms for 2, 4 and 8 ranks; other rank counts take the per-operator path + NCCL
+    const int T = m->ctx->tp_size;
+    if (T != 1 && T != 2 && T != 4 && T != 8) return false;
     MegaParams p{};
     p.H = (int)m->H; p.I = (int)m->inter_l; p.qd = (int)m->qd_l; p.D = (int)m->D;
     p.qkv_rows = (int)m->qkv_rows; p.kvd = (int)m->kvd_l;
@@ -642,6 +665,7 @@ int lumen_llama_init_kv_caches(lumen_llama *m, size_t batch, lumen_kv_cache **ca
         c->k = base + (2 * l) * per;
         c->v = base + (2 * l + 1) * per;
         c->d_len = lens + l;
+        c->seen_abort = ctx->abort_gen;
         c->owns_slab = false;
         c->slab = slab;
         slab->refs += 1;
@@ -730,6 +754,7 @@ int lumen_llama_free(lumen_llama *m) {
     if (m->d_mega_layers) cudaFree(m->d_mega_layers);
     if (m->d_sched) cudaFree(m->d_sched);
     if (m->d_sched_count) cudaFree(m->d_sched_count);
+    if (m->d_tmaps) cudaFree(m->d_tmaps);
     if (m->d_trace) cudaFree(m->d_trace);
     if (m->d_exchange) cudaFree(m->d_exchange);
     if (m->ws.base) cudaFree(m->ws.base);

@@ -264,6 +264,7 @@ int lumen_kv_new(lumen_ctx *ctx, size_t b, size_t h_kv, size_t max_seq, size_t d
     }
     c->v = c->k + n;
     c->d_len = reinterpret_cast<int *>(c->v + n);
+    c->seen_abort = ctx->abort_gen;
     LUMEN_CUDA(ctx, cudaMemsetAsync(c->k, 0, 2 * n * sizeof(float) + 16, ctx->stream));
     *out = c;
     return LUMEN_OK;
@@ -272,11 +273,16 @@ int lumen_kv_new(lumen_ctx *ctx, size_t b, size_t h_kv, size_t max_seq, size_t d
 int lumen_kv_reset(lumen_kv_cache *c) {
     if (!c) return LUMEN_ERR_INVALID;
     c->len = 0;  // contents are kept, like KVCacheInner::reset
+    c->seen_abort = c->ctx->abort_gen;
     LUMEN_CUDA(c->ctx, cudaMemsetAsync(c->d_len, 0, sizeof(int), c->ctx->stream));
     return LUMEN_OK;
 }
 
-size_t lumen_kv_len(const lumen_kv_cache *c) { return c ? c->len : 0; }
+size_t lumen_kv_len(const lumen_kv_cache *c) {
+    if (!c) return 0;
+    kv_resync_len(const_cast<lumen_kv_cache *>(c));  // after a device-side abort the device copy is the truth
+    return c->len;
+}
 
 int lumen_kv_free(lumen_kv_cache *c) {
     if (!c) return LUMEN_ERR_INVALID;
@@ -311,6 +317,7 @@ int lumen_kv_write(lumen_kv_cache *c, const float *k_in, const float *v_in, size
     LUMEN_CUDA(c->ctx, cudaMemcpyAsync(c->d_len, &ilen, sizeof(int), cudaMemcpyHostToDevice, c->ctx->stream));
     LUMEN_CUDA(c->ctx, cudaStreamSynchronize(c->ctx->stream));
     c->len = len;
+    c->seen_abort = c->ctx->abort_gen;
     return LUMEN_OK;
 }
 
@@ -373,6 +380,7 @@ int lumen_attention_decode(lumen_ctx *ctx, const float *q_dev, const float *k_ne
                            lumen_kv_cache *cache, lumen_rope *rope, int causal, float *out_dev) {
     if (!ctx || !q_dev || !k_new_dev || !v_new_dev || !cache || !out_dev) return set_error(ctx, LUMEN_ERR_INVALID, "attention_decode: null argument");
     (void)causal;  // with S == 1 the causal test `j > past_len` never fires (self_attention.rs:255-258)
+    LUMEN_TRY(kv_resync_len(cache));
     if (cache->len + 1 > cache->max_seq)
         return set_error(ctx, LUMEN_ERR_KV_OVERFLOW, "KV cache overflow: new_len=%zu > max_seq=%zu", cache->len + 1, cache->max_seq);
     if (rope) {
@@ -454,6 +462,7 @@ int lumen_self_attention_forward(lumen_self_attention *attn, const lumen_tensor 
     if (cache->b != B || cache->h_kv != Hkv || cache->d != D) return bail(set_error(ctx, LUMEN_ERR_SHAPE, "KV cache geometry does not match the layer"));
     // Order of the reference's checks: prefill runs rope.forward (range panic) before the overflow assert;
     // decode asserts overflow first (self_attention.rs:144-149 vs :334-346).
+    if (int rs = kv_resync_len(cache)) return bail(rs);
     const size_t past = cache->len;
     if (S == 1) {
         if (past + 1 > cache->max_seq) return bail(set_error(ctx, LUMEN_ERR_KV_OVERFLOW, "KV cache overflow: new_len=%zu > max_seq=%zu", past + 1, cache->max_seq));

@@ -43,6 +43,10 @@ struct lumen_ctx {
     // epoch from which the next launch derives the tags of its exchanged activations.
     unsigned long long *d_mega_sync = nullptr;
     unsigned int mega_epoch = 1;
+    // Counts the device-side aborts the host has read (check_device_status).  A kernel that gave up did not
+    // advance the device copy of the cache lengths although the host mirror was bumped at enqueue time, so
+    // every cache re-reads its device length the first time it is used after an abort (kv_resync_len).
+    unsigned int abort_gen = 0;
 };
 
 struct lumen_storage {
@@ -82,6 +86,7 @@ struct lumen_kv_cache {
     int *d_len = nullptr;  // device copy read by replayable kernels
     float *k = nullptr;    // [B,Hkv,max_seq,D]
     float *v = nullptr;
+    unsigned int seen_abort = 0;  // ctx->abort_gen at the last time `len` was known to equal *d_len
     bool owns_slab = true;  // false when carved out of a model-wide slab
     lumen_storage *slab = nullptr;  // shared slab (reference counted) when !owns_slab
 };
@@ -112,6 +117,9 @@ int cuda_fail(lumen_ctx *ctx, cudaError_t e, const char *what);
     } while (0)
 
 int check_device_status(lumen_ctx *ctx);
+// Brings the host mirror of a cache's length back in line with the device copy after a device-side abort
+// (one 4-byte synchronising read, only on the first use after the abort).
+int kv_resync_len(lumen_kv_cache *c);
 
 // y[M,N] = a[M,K] . w[N,K]^T (+ residual): vector-matrix kernel for M <= 8, tiled GEMM otherwise.
 int matmul_dispatch(lumen_ctx *ctx, const float *a, const void *w, lumen_dtype wdt, float *y, size_t M, size_t K,

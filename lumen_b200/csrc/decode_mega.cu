@@ -3,20 +3,27 @@
 // attention self_attention.rs:141-297, vector-matrix products src/ops/matmul.rs:42-69).
 //
 // Design for B200: one CTA per SM (launched cooperatively so that all CTAs are co-resident).  The
-// last warp of each CTA is a producer: it walks a schedule of bulk copies that the host built once (the
-// CTA's rows of every matrix of every layer, in execution order) and streams the weight tiles from HBM
-// into a shared-memory ring with 1-D bulk TMA copies (cp.async.bulk + mbarrier transaction counts, L2
-// evict-first, a short cp.async.bulk.prefetch.L2 look-ahead).  The schedule does not depend on the
-// activations, so the producer keeps HBM busy across phase boundaries while the consumer warps wait for
-// activations or run the (weight-free) attention.
+// last warp of each CTA is a producer: it walks a schedule of copies that the host built once (the CTA's
+// rows of every matrix of every layer, in execution order) and streams the weight tiles from HBM into a
+// shared-memory ring of 16 KB stages with TMA copies (mbarrier transaction counts, L2 evict-first).  A tile
+// is four rows x 4 KB: rows of up to 4 KB travel whole (1-D bulk copy of the contiguous rows), longer rows
+// are cut into segments and a tile is ONE 3-D tiled copy (cp.async.bulk.tensor: a box of four rows x one
+// segment out of the row-major matrix).  Each producer lane issues one copy of a batch of 32, so the fixed
+// cost of a copy is paid once per batch.  The schedule does not depend on the activations, so the producer
+// keeps HBM busy across phase boundaries while the consumer warps wait for activations or run the
+// (weight-free) attention.
 //
-// Consumers: a phase's input vector is staged in shared memory (RMSNorm applied in place), tiles go
-// round-robin to the 4 consumer warps, and a warp works through its own tiles alone: per 16-byte step
-// a lane reads one vector of x and the matching vector of up to 4 weight rows with conflict-free 128-bit
-// shared loads, the row sums are folded across lanes by one butterfly, and the only CTA-wide barrier is
-// at the end of a row block, where the fused epilogue runs (residual add, SiLU*mul) and the results are
-// published.  Phases of a layer: qkv | attention | o_proj(+residual) | gate/up(+SiLU*mul) |
-// down(+residual).
+// Consumers: a phase's input vector is staged in shared memory (multiplied by the RMSNorm gains on the
+// way in; the 1/rms factor is a scalar and is applied to the row sums).  Tiles go round-robin to the six
+// consumer warps and a warp works through a tile alone: per 16-byte step a lane reads one vector of x and the
+// matching vector of four weight rows with conflict-free 128-bit shared loads, the four row sums are folded
+// across lanes by one butterfly and land in the row's column (one per segment) of a table of partial sums.
+// The only CTA-wide barrier is at the end of a row block, where the partial sums of a row are added, the
+// fused epilogue runs (1/rms, residual add, SiLU*mul) and the results are published.  Phases of a layer:
+// qkv | attention | o_proj(+residual) | gate/up(+SiLU*mul) | down(+residual).
+// The arithmetic on tiles that already sit in shared memory is what the token's time is made of (measured
+// with the copies switched off), so the kernel is kept free of register spills: with the L1 squeezed by
+// ~220 KB of shared memory a spill reload inside the tile loop is a round trip through L2.
 //
 // Activations cross CTAs through global memory (L2) as tagged words {f32 bits, tag}: a consumer polls
 // the words it needs until their tag equals the one of the producing phase of this launch, so there is
@@ -36,14 +43,16 @@
 namespace lumen {
 namespace {
 
-// 4 consumer warps + 1 producer warp: at most two warps per SM sub-partition, so every thread may use up
-// to 255 registers (a ninth warp would cap the kernel at 168 and the spills, with the L1 squeezed by
-// ~200 KB of shared memory, turn into L2 round trips on the critical path).
-constexpr int kConsumers = 128;
+// 6 consumer warps + 1 producer warp: at most two warps per SM sub-partition, so every thread may use up to 255
+// registers (with three warps on a sub-partition the limit is 168).  The kernel must not spill: the L1 is squeezed by
+// ~220 KB of shared memory, and a spill reload inside the tile loop is a round trip through L2.
+constexpr int kConsumers = 192;
 constexpr int kConsumerWarps = kConsumers / 32;
-constexpr int kThreads = kConsumers + 32;  // + producer warp
+constexpr int kThreads = kConsumers + 32;   // + producer warp
 constexpr int kMaxRowsPerTile = 8;
-constexpr int kRowBlock = 128;             // rows reduced together (one per consumer thread)
+constexpr int kRowBlock = 64;              // rows reduced together (one per consumer thread, half of them idle)
+constexpr int kMaxSeg = 8;                 // segments a row is cut into at most
+constexpr int kPartCols = kMaxSeg;         // columns of the table of partial row sums: one per segment
 constexpr int kMaxSplit = 4;               // attention splits merged in the o_proj prologue
 constexpr long long kWaitCycles = 400000000LL;  // ~0.2 s at 1.9 GHz
 
@@ -51,7 +60,7 @@ constexpr long long kWaitCycles = 400000000LL;  // ~0.2 s at 1.9 GHz
 // warp through a row: 4 x 32 lanes x 8 elements) and of the table of row sums of a row block ([2][kRowBlock][4]).
 __host__ __device__ inline size_t mega_xs_floats(int kmax) { return (((size_t)kmax + 1023) / 1024) * 1024; }
 __host__ __device__ inline size_t mega_table_floats(int kmax) {
-    return mega_xs_floats(kmax) + 2 * (size_t)kRowBlock * kConsumerWarps;
+    return mega_xs_floats(kmax) + 2 * (size_t)kRowBlock * kPartCols;
 }
 
 // ---- PTX helpers -------------------------------------------------------------------------------------
@@ -75,6 +84,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// Non-blocking test of a barrier phase (try_wait may suspend the thread for an implementation-defined time).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ uint64_t make_evict_first_policy() {
     uint64_t pol;
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
@@ -85,6 +104,14 @@ __device__ __forceinline__ void bulk_load(void *dst_smem, const void *src, uint3
     asm volatile(
         "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
         ::"r"(smem_u32(dst_smem)), "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(pol)
+        : "memory");
+}
+// 3-D tiled TMA copy: box of the map at (0, unit, row) -> this CTA's shared memory.  The innermost coordinate is
+// always 0, so the 16-byte start rule of TMA holds.
+__device__ __forceinline__ void tensor_load(void *dst_smem, const CUtensorMap *map, int unit, int row, uint64_t *bar, uint64_t pol) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3, %4}], [%5], %6;"
+        ::"r"(smem_u32(dst_smem)), "l"(map), "r"(0), "r"(unit), "r"(row), "r"(smem_u32(bar)), "l"(pol)
         : "memory");
 }
 __device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory"); }
@@ -109,6 +136,13 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
 __device__ __forceinline__ void trace_stamp(const MegaParams &p, int cta, int tid, int slot) {
     if (p.trace && cta == 0 && tid == 0) p.trace[slot] = globaltimer_ns();
 }
+// Per-CTA stamps: which = 0 (input arrived) or 1 (results published).
+__device__ __forceinline__ void trace_cta(const MegaParams &p, int cta, int tid, int which, int ph) {
+    if (p.trace && tid == 0 && cta < kMegaTraceCtas) {
+        const size_t nph = 5 * (size_t)p.L + 1;
+        p.trace[decode_mega_trace_base_words(p.L) + ((size_t)which * nph + ph) * kMegaTraceCtas + cta] = globaltimer_ns();
+    }
+}
 __device__ __forceinline__ int ld_volatile_int(const int *p) { return *reinterpret_cast<const volatile int *>(p); }
 
 __device__ __forceinline__ float warp_sum(float v) {
@@ -123,13 +157,15 @@ __device__ __forceinline__ float bf16_hi(uint32_t u) { return __uint_as_float(u 
 struct Shared {
     unsigned char *stages;
     float *xs;         // the phase's input vector (zero-padded)
-    float *part;       // [2][kRowBlock][kConsumerWarps]: row sums of one block (first slot of each row)
-    float *red;        // [kConsumerWarps]
+    float *part;       // [2][kRowBlock][kPartCols]: partial row sums of one block, one column per (segment, half) of the row
+    float *red;        // [kConsumerWarps] partial sums of squares of the staged vector
+    float *xraw;       // [kRowBlock] the residual-stream values of this CTA's rows, before the gains
     float *attn;       // scratch of the attention item
     uint64_t *full;    // [S]
     uint64_t *empty;   // [S]
     volatile int *abort;
     volatile int *decision;  // [2] abort flag sampled by thread 0 before a barrier, read by all after it
+    volatile int *issued;    // [S] producer: the last use of each stage whose copies have been issued (-1: none yet)
     volatile int *seen;      // [S] number of uses of each stage whose data a consumer has seen land
     int S, stage_bytes;
 };
@@ -143,12 +179,17 @@ __device__ __forceinline__ void raise_abort(const MegaParams &p, volatile int *a
     }
 }
 
+#ifdef LUMEN_MEGA_TRYWAIT
+#define MEGA_WAIT mbar_try_wait
+#else
+#define MEGA_WAIT mbar_test_wait
+#endif
 // Bounded mbarrier wait; false = gave up (abort raised) or somebody else aborted.
 __device__ __forceinline__ bool mbar_wait(const MegaParams &p, Shared &sh, uint64_t *bar, uint32_t parity, int site) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_test_wait(bar, parity)) return true;
     const long long t0 = clock64();
     int spins = 0;
-    while (!mbar_try_wait(bar, parity)) {
+    while (!(MEGA_WAIT(bar, parity))) {
         if ((++spins & 63) == 0) {
             if (*sh.abort) return false;
             if (clock64() - t0 > kWaitCycles) {
@@ -160,8 +201,8 @@ __device__ __forceinline__ bool mbar_wait(const MegaParams &p, Shared &sh, uint6
     return true;
 }
 
-// Bounded wait until `uses` fills of stage s are known to have landed (written by the groups that
-// consumed them).  In steady state this is already true and costs one shared-memory read.
+// Bounded wait until `uses` fills of stage s are known to have landed (written by the
+// warps that consumed them).  In steady state this is already true and costs one shared-memory read.
 __device__ __forceinline__ bool stage_use_seen(const MegaParams &p, Shared &sh, int s, int uses, int site) {
     if (sh.seen[s] >= uses) return true;
     const long long t0 = clock64();
@@ -207,29 +248,39 @@ __host__ __device__ __forceinline__ Phase get_phase(const MegaParams &p, const M
     return g;
 }
 
-// The CTA's tiles of one phase, in the order both the producer and the consumers walk them: chunks of up
-// to R whole rows; per chunk one tile per matrix (gate rows, then the same rows of up).
-struct TileIter {
-    long r, r0, r1;
-    int nmat, R, rowbytes, mat;
-    __host__ __device__ TileIter(const Phase &g, int esz, int stage_bytes, int cta, int nctas, bool skip_tiles = false) {
+// The CTA's tiles of one phase, in the order both the producer and the consumers walk them.
+// A tile is up to R rows (4, or 8 for very short rows) x one segment of the row length.  Rows longer than a
+// quarter of a ring stage are cut into nseg = 2 or 4 segments of whole steps (a step = 32 consecutive 16-byte
+// vectors, one per lane), so that every tile holds four rows and each 16-byte vector of x read from shared
+// memory feeds four weight rows; a segmented tile arrives as one bulk copy per row, packed back to back in the
+// stage.  Tile t of the phase = (chunk of R rows, matrix, segment): t = (chunk * nmat + mat) * nseg + seg.
+// The partial row sums of the segments of a row land in different columns of the row-sum table.
+struct PhaseTiles {
+    long r0, r1;  // the CTA's rows of the matrix (or matrices)
+    int nmat, R, nseg, per, njl, rowbytes, nrows, chunks;
+    __host__ __device__ PhaseTiles(const Phase &g, int esz, int stage_bytes, int cta, int nctas) {
         rowbytes = g.K * esz;
         nmat = g.nmat;
-        r0 = r = (long)g.N * cta / nctas;
+        r0 = (long)g.N * cta / nctas;
         r1 = (long)g.N * (cta + 1) / nctas;
-        R = stage_bytes / (rowbytes > 0 ? rowbytes : 1);
-        R = R < 1 ? 1 : (R > kMaxRowsPerTile ? kMaxRowsPerTile : R);
-        if (R > 4 && R < 8) R = 4;  // the consumers take rows four at a time
-        mat = 0;
-        if (skip_tiles) r = r1;  // debug: keep the row range, stream nothing
-    }
-    __host__ __device__ bool valid() const { return r < r1; }
-    __host__ __device__ int rows() const { return (int)((long)R < r1 - r ? (long)R : r1 - r); }
-    __host__ __device__ void advance() {
-        if (++mat == nmat) {
-            mat = 0;
-            r += R;
+        nrows = (int)(r1 - r0);
+        njl = (rowbytes / 16 + 31) / 32;  // steps of a lane through a whole row
+        // Four whole rows per stage where they fit; otherwise four rows x segments of stage_bytes / 4 bytes each (a
+        // whole number of blocks of four steps, the unit of the consumers' inner loop).
+        nseg = 1;
+        per = njl;
+        if (4 * rowbytes > stage_bytes) {
+            per = (stage_bytes / 4 / 512) & ~3;
+            nseg = (njl + per - 1) / per;
         }
+        R = (nseg == 1 && 8 * rowbytes <= stage_bytes) ? 8 : 4;
+        chunks = (nrows + R - 1) / R;
+    }
+    __host__ __device__ int tiles() const { return chunks * nmat * nseg; }
+    __host__ __device__ int seg_steps(int seg) const { return (njl < (seg + 1) * per ? njl : (seg + 1) * per) - seg * per; }
+    __host__ __device__ int seg_bytes(int seg) const {
+        const int b1 = (seg + 1) * per * 512;
+        return (b1 < rowbytes ? b1 : rowbytes) - seg * per * 512;
     }
 };
 
@@ -243,104 +294,116 @@ __device__ __forceinline__ void prefetch_l2(const void *src, uint32_t bytes) {
 // is issued, so its latency is hidden); lane 0 then issues the copies: on the first copy of a tile it waits
 // for the stage to be free and arms the stage's mbarrier with the tile's byte count.  A tile made of row
 // segments is one copy per row, packed back to back in the stage.
+__device__ __forceinline__ void prefetch_tensor_l2(const CUtensorMap *map, int unit, int row) {
+    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global [%0, {%1, %2, %3}];" ::"l"(map), "r"(0), "r"(unit), "r"(row) : "memory");
+}
+__device__ __forceinline__ void prefetch_entry(const MegaParams &p, const uint4 &f) {
+    if (f.w & 0x80000000u) prefetch_tensor_l2(p.tmaps + (f.x & 0xffffu), (int)(f.x >> 16), (int)f.y);
+    else prefetch_l2(reinterpret_cast<const char *>(((unsigned long long)f.y << 32) | f.x), f.z & 0xffffu);
+}
+
+// The producer warp.  Each lane owns one entry of a batch of 32 schedule entries (one coalesced load; the next
+// batch is requested before the current one is issued) and issues that copy by itself: it waits until the ring
+// stage of its tile is free, arms the stage's barrier with the tile's byte count if the copy is the first of
+// its tile, and issues the copy.  The lanes run in lockstep, so the fixed cost of a copy (barrier test, address
+// set-up, the TMA instruction) is paid once per pass for all the copies whose stages are free, instead of once
+// per copy by a single thread, which capped the stream at one tile per ~0.33 us.  A batch is issued in passes of
+// at most S tiles: within a pass no two tiles share a stage, so a stage's barrier is never tested for a use
+// before the use before it has been issued (a parity test tells two uses apart, not three).
 __device__ __forceinline__ void producer_loop(const MegaParams &p, Shared &sh, int cta, int lane) {
     const uint64_t pol = make_evict_first_policy();
     const int nphases = 5 * p.L + 1;
     const uint4 *sched = p.sched + (size_t)cta * p.sched_stride;
     const int n = p.sched_count[cta];
-    int s = -1;          // stage of the current tile
-    uint32_t use = 0;    // how many times the ring has wrapped
-    uint32_t off = 0;    // bytes of the current tile already requested
-    long tiles = 0;
-    int last_ph = -1;
+    const uint32_t S = (uint32_t)sh.S;
+    uint32_t tiles = 0;  // tiles before the current batch (the same in every lane)
+    int last_ph = -1;    // trace: phase of the last entry of the previous batch
     bool ok = true;
     uint4 nxt = lane < n ? sched[lane] : make_uint4(0u, 0u, 0u, 0u);
-    for (int base = 0; base < n; base += 32) {
-        const uint4 cur = nxt;
+    for (int base = 0; base < n && ok; base += 32) {
+        const uint4 e = nxt;
         if (base + 32 + lane < n) nxt = sched[base + 32 + lane];
-        const int cnt = min(32, n - base);
-        for (int i = 0; i < cnt; ++i) {
-            // L2 look-ahead: the lane that holds the entry `ahead` copies further on (in this batch or the
-            // next) asks the L2 to fetch it.  While the consumers wait for activations the ring fills up
-            // within a few microseconds, but HBM keeps streaming into the 126 MB L2, and the ring later
-            // refills from there faster than HBM could deliver.
-            if (p.l2_ahead > 0) {
-                const int j = i + p.l2_ahead;
-                if (lane == (j & 31) && j < 64 && base + j < n) {
-                    const uint4 f = j < 32 ? cur : nxt;
-                    prefetch_l2(reinterpret_cast<const char *>(((unsigned long long)f.y << 32) | f.x), f.z & 0xffffu);
-                }
-            }
-            uint4 e;
-            e.x = __shfl_sync(0xffffffffu, cur.x, i);
-            e.y = __shfl_sync(0xffffffffu, cur.y, i);
-            e.z = __shfl_sync(0xffffffffu, cur.z, i);
-            e.w = __shfl_sync(0xffffffffu, cur.w, i);
-            if (lane != 0 || !ok) continue;
-            if (e.w) {  // first copy of a tile: next stage
-                if (++s == sh.S) {
-                    s = 0;
-                    ++use;
-                }
-                const int ph = (int)(e.z >> 16);
-                if (p.trace && cta == 0 && ph != last_ph) {
-                    p.trace[3 * nphases + 1 + ph] = globaltimer_ns();
-                    last_ph = ph;
-                }
-                if (use > 0 && !mbar_wait(p, sh, &sh.empty[s], (use - 1) & 1, 100)) {
-                    ok = false;
-                    --s;  // this tile was not issued (s == -1 cannot occur here: use > 0)
-                    continue;
-                }
-                mbar_expect_tx(&sh.full[s], e.w);
-                off = 0;
-                if (p.trace && cta == 0 && tiles < kMegaTileTrace) p.trace[7 * nphases + 1 + tiles] = globaltimer_ns();
-                ++tiles;
-            }
-            const uint32_t bytes = e.z & 0xffffu;
-            const char *src = reinterpret_cast<const char *>(((unsigned long long)e.y << 32) | e.x);
-            bulk_load(sh.stages + (size_t)s * sh.stage_bytes + off, src, bytes, &sh.full[s], pol);
-            off += bytes;
+        const bool valid = base + lane < n;
+        const bool first = valid && (e.w & 0xffffu) != 0;  // first copy of a tile
+        const uint32_t firsts = __ballot_sync(0xffffffffu, first);
+        // tile of this lane's copy: a continuation copy belongs to the tile of the nearest first copy before it
+        const uint32_t tile = tiles + (uint32_t)__popc(firsts & (0xffffffffu >> (31 - lane))) - 1u;
+        const uint32_t slot = tile % S, use = tile / S;
+        unsigned char *dst = sh.stages + (size_t)slot * sh.stage_bytes + (size_t)((e.w >> 16) & 0xfffu) * 16;
+        if (p.trace && cta == 0) {  // (uniform: every lane takes part in the shuffles)
+            const int ph = valid ? (int)(e.z >> 16) : -1;
+            int ph_prev = __shfl_up_sync(0xffffffffu, ph, 1);
+            if (lane == 0) ph_prev = last_ph;
+            last_ph = __shfl_sync(0xffffffffu, ph, min(31, n - base - 1));
+            if (first && tile < (uint32_t)kMegaTileTrace) p.trace[7 * nphases + 1 + tile] = globaltimer_ns();
+            if (valid && ph_prev != ph) p.trace[3 * nphases + 1 + ph] = globaltimer_ns();  // first copy of a phase
         }
+        bool pending = valid;
+        const uint32_t ntiles_batch = (uint32_t)__popc(firsts);
+        for (uint32_t t0 = tiles; __any_sync(0xffffffffu, pending) && ok; t0 += S) {
+            const bool mine = pending && tile < t0 + S;  // this pass: tiles [t0, t0 + S)
+            const long long c0 = clock64();
+            int spins = 0;
+            bool waiting = mine;
+            while (__any_sync(0xffffffffu, waiting)) {
+                if (waiting && (use == 0 || mbar_try_wait(&sh.empty[slot], (use - 1) & 1))) {
+                    if (first) mbar_expect_tx(&sh.full[slot], e.w & 0xffffu);
+                    if (e.w & 0x80000000u) {  // box of rows x one segment of the row length (3-D tiled copy)
+                        tensor_load(dst, p.tmaps + (e.x & 0xffffu), (int)(e.x >> 16), (int)e.y, &sh.full[slot], pol);
+                    } else {
+                        bulk_load(dst, reinterpret_cast<const char *>(((unsigned long long)e.y << 32) | e.x), e.z & 0xffffu, &sh.full[slot], pol);
+                    }
+                    if (first) sh.issued[slot] = (int)use;
+                    waiting = false;
+                    pending = false;
+                }
+                if ((++spins & 63) == 0) {
+                    bool give_up = *sh.abort != 0;
+                    if (!give_up && clock64() - c0 > kWaitCycles) {
+                        if (waiting) raise_abort(p, sh.abort, 100, (int)slot);
+                        give_up = true;
+                    }
+                    if (__any_sync(0xffffffffu, give_up)) {
+                        ok = false;
+                        break;
+                    }
+                }
+            }
+        }
+        tiles += ntiles_batch;
     }
-    if (lane == 0 && !ok) {
-        // Wait (bounded) for the copies still in flight before the CTA may exit: the last min(tiles, S) tiles.
-        const long m = tiles < sh.S ? tiles : sh.S;
-        for (long i = 0; i < m; ++i) {
-            const long idx = tiles - 1 - i;
-            uint64_t *bar = &sh.full[idx % sh.S];
-            const uint32_t parity = (uint32_t)((idx / sh.S) & 1);
+    if (!ok && lane < (int)S) {
+        // Wait (bounded) for this stage's last copies still in flight before the CTA may exit.
+        const int u = sh.issued[lane];
+        if (u >= 0) {
             const long long t0 = clock64();
-            while (!mbar_try_wait(bar, parity) && clock64() - t0 < kWaitCycles) {}
+            while (!mbar_try_wait(&sh.full[lane], (uint32_t)u & 1) && clock64() - t0 < kWaitCycles) {}
         }
     }
 }
 
 // ---- consumers ---------------------------------------------------------------------------------------
-// Tagged exchange words.  An aligned 8-byte store is single-copy atomic, so a reader that sees the tag
-// also sees the value; 16-byte loads fetch two such words (each half is checked on its own).
+// Tagged exchange words {f32 bits, tag}.  A word is written and read as ONE 64-bit access (b64 stores, v2.b64
+// loads: each 64-bit element is single-copy atomic in the PTX memory model), so a reader that sees the tag
+// also sees the value that was stored with it.  A 16-byte load fetches two such words; each is checked on its own.
 __device__ __forceinline__ void st_tagged(uint2 *dst, float v, uint32_t tag) {
-    asm volatile("st.relaxed.gpu.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(v)), "r"(tag) : "memory");
+    const unsigned long long w = ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(v);
+    asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(dst), "l"(w) : "memory");
 }
 __device__ __forceinline__ uint4 ld_tagged2(const uint4 *src) {
-    uint4 v;
-    asm volatile("ld.relaxed.gpu.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(src)
-                 : "memory");
-    return v;
+    unsigned long long a, b;
+    asm volatile("ld.relaxed.gpu.global.v2.b64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(src) : "memory");
+    return make_uint4((uint32_t)a, (uint32_t)(a >> 32), (uint32_t)b, (uint32_t)(b >> 32));
 }
 // The same at system scope, for words that another GPU writes or reads over NVLink.
 __device__ __forceinline__ void st_tagged_sys(uint2 *dst, float v, uint32_t tag) {
-    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(v)), "r"(tag) : "memory");
+    const unsigned long long w = ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(v);
+    asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(dst), "l"(w) : "memory");
 }
 __device__ __forceinline__ uint4 ld_tagged2_sys(const uint4 *src) {
-    uint4 v;
-    asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(src)
-                 : "memory");
-    return v;
+    unsigned long long a, b;
+    asm volatile("ld.relaxed.sys.global.v2.b64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(src) : "memory");
+    return make_uint4((uint32_t)a, (uint32_t)(a >> 32), (uint32_t)b, (uint32_t)(b >> 32));
 }
 __device__ __forceinline__ uint32_t phase_tag(const MegaParams &p, int ph) { return p.epoch_base + (uint32_t)ph + 1u; }
 
@@ -360,12 +423,44 @@ __device__ __forceinline__ bool poll_continue(const MegaParams &p, volatile int 
     return true;
 }
 
+// What the staging of a phase's input vector does besides copying it (all optional):
+//   gains   RMSNorm gains: xs[k] = x[k] * gains[k].  RMSNorm::forward (rms_norm.rs:49-56) is (x * inv) * w with
+//           the scalar inv = 1 / sqrt(mean(x^2) + eps); inv multiplies the finished row sums instead.
+//   ss      this thread's share of sum(x^2), accumulated over the raw values
+//   xraw    the raw values of elements [r0, r1) are kept aside (the residual stream of this CTA's rows)
+struct StageOpts {
+    const float *gains = nullptr;
+    float *xraw = nullptr;
+    int r0 = 0, r1 = 0;
+};
+__device__ __forceinline__ void stage_pair(const StageOpts o, float *xs, int idx, float a, float b, float2 g, float &ss) {
+    ss = fmaf(a, a, ss);
+    ss = fmaf(b, b, ss);
+    if (o.xraw) {
+        const int e = 2 * idx;
+        if (e >= o.r0 && e < o.r1) o.xraw[e - o.r0] = a;
+        if (e + 1 >= o.r0 && e + 1 < o.r1) o.xraw[e + 1 - o.r0] = b;
+    }
+    *reinterpret_cast<float2 *>(xs + 2 * idx) = make_float2(__fmul_rn(a, g.x), __fmul_rn(b, g.y));
+}
+
 // All consumer threads: wait until the `n` tagged words at `src` (n even) carry `tag`, and leave their
-// values as floats in shared memory `xs[n]`.  Returns false (uniformly) when the CTA is aborting.
+// values as floats in shared memory `xs[n]`.  The gains are requested before the first poll so that their trip
+// to L2 is not added to the critical path.
 template <int kBatch>  // 16-byte loads in flight per thread and pass
 __device__ __forceinline__ void poll_vector_pass(const MegaParams &p, Shared &sh, const uint4 *s4, int npairs, int base, uint32_t tag,
-                                                 float *xs, int tid, int site) {
+                                                 float *xs, int tid, int site, const StageOpts o, float &ss) {
     uint4 v[kBatch];
+    // up to 8 loads per thread the gains wait in registers; longer vectors fetch them after the wait instead
+    constexpr bool kEarlyGains = kBatch <= 8;
+    float2 g[kEarlyGains ? kBatch : 1];
+    if (kEarlyGains) {
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+            const int idx = base + tid + kConsumers * u;
+            g[u] = (o.gains && idx < npairs) ? __ldg(reinterpret_cast<const float2 *>(o.gains) + idx) : make_float2(1.f, 1.f);
+        }
+    }
     const long long t0 = clock64();
     int spins = 0;
     bool done = false, alive = true;
@@ -384,23 +479,34 @@ __device__ __forceinline__ void poll_vector_pass(const MegaParams &p, Shared &sh
 #pragma unroll
         for (int u = 0; u < kBatch; ++u) {
             const int idx = base + tid + kConsumers * u;
-            if (idx < npairs) *reinterpret_cast<float2 *>(xs + 2 * idx) = make_float2(__uint_as_float(v[u].x), __uint_as_float(v[u].z));
+            if (idx >= npairs) continue;
+            const float2 gu = kEarlyGains ? g[kEarlyGains ? u : 0]
+                                          : (o.gains ? __ldg(reinterpret_cast<const float2 *>(o.gains) + idx) : make_float2(1.f, 1.f));
+            stage_pair(o, xs, idx, __uint_as_float(v[u].x), __uint_as_float(v[u].z), gu, ss);
         }
     }
 }
 
-// The whole vector is requested in one pass whenever it fits 24 loads per thread (6144 words): every pass
+// Leaves this warp's share of sum(x^2) in red[warp] (read by everybody after the next consumer barrier).
+__device__ __forceinline__ void publish_ss(Shared &sh, float ss, int tid) {
+    ss = warp_sum(ss);
+    if ((tid & 31) == 0) sh.red[tid >> 5] = ss;
+}
+
+// The whole vector is requested in one pass whenever it fits 16 loads per thread (4096 words): every pass
 // costs a round trip through L2, which is what this wait is made of.
 __device__ __forceinline__ bool poll_vector(const MegaParams &p, Shared &sh, const uint2 *src, int n, uint32_t tag, float *xs,
-                                            int tid, int &bk, int site) {
+                                            int tid, int &bk, int site, const StageOpts o = StageOpts()) {
     const uint4 *s4 = reinterpret_cast<const uint4 *>(src);
     const int npairs = n / 2;
     const int per_thread = (npairs + kConsumers - 1) / kConsumers;
-    if (per_thread <= 4) poll_vector_pass<4>(p, sh, s4, npairs, 0, tag, xs, tid, site);
-    else if (per_thread <= 8) poll_vector_pass<8>(p, sh, s4, npairs, 0, tag, xs, tid, site);
-    else if (per_thread <= 16) poll_vector_pass<16>(p, sh, s4, npairs, 0, tag, xs, tid, site);
+    float ss = 0.f;
+    // At most 8 loads per thread and pass: more words in flight would push the kernel's hot loops into spilling,
+    // and with the L1 squeezed by the shared-memory ring a spill costs a round trip through L2.
+    if (per_thread <= 4) poll_vector_pass<4>(p, sh, s4, npairs, 0, tag, xs, tid, site, o, ss);
     else
-        for (int base = 0; base < npairs; base += kConsumers * 16) poll_vector_pass<16>(p, sh, s4, npairs, base, tag, xs, tid, site);
+        for (int base = 0; base < npairs; base += kConsumers * 8) poll_vector_pass<8>(p, sh, s4, npairs, base, tag, xs, tid, site, o, ss);
+    publish_ss(sh, ss, tid);
     return consumer_bar_ok(sh.abort, sh.decision, tid, bk);
 }
 
@@ -408,7 +514,7 @@ __device__ __forceinline__ bool poll_vector(const MegaParams &p, Shared &sh, con
 // (slots of `n` words, `slot_words` apart) and stages their sum, added in rank order.
 template <int T, int KB>
 __device__ __forceinline__ void poll_x_sum_pass(const MegaParams &p, Shared &sh, const uint2 *src, int slot_words, int npairs, int base,
-                                                uint32_t tag, float *xs, int tid) {
+                                                uint32_t tag, float *xs, int tid, const StageOpts o, float &ss) {
     uint4 v[T][KB];
     const long long t0 = clock64();
     int spins = 0;
@@ -441,19 +547,23 @@ __device__ __forceinline__ void poll_x_sum_pass(const MegaParams &p, Shared &sh,
             a = __fadd_rn(a, __uint_as_float(v[r][u].x));
             b = __fadd_rn(b, __uint_as_float(v[r][u].z));
         }
-        *reinterpret_cast<float2 *>(xs + 2 * idx) = make_float2(a, b);
+        // (the T * KB words in flight leave no registers to hold the gains through the wait)
+        const float2 gu = o.gains ? __ldg(reinterpret_cast<const float2 *>(o.gains) + idx) : make_float2(1.f, 1.f);
+        stage_pair(o, xs, idx, a, b, gu, ss);
     }
 }
 
 __device__ __forceinline__ bool poll_x_sum(const MegaParams &p, Shared &sh, const uint2 *src, int n, uint32_t tag, float *xs, int tid,
-                                           int &bk) {
+                                           int &bk, const StageOpts o) {
     const int npairs = n / 2, sw = p.x_slot_words;
+    float ss = 0.f;
     if (p.tp_size == 2)
-        for (int base = 0; base < npairs; base += kConsumers * 8) poll_x_sum_pass<2, 8>(p, sh, src, sw, npairs, base, tag, xs, tid);
+        for (int base = 0; base < npairs; base += kConsumers * 4) poll_x_sum_pass<2, 4>(p, sh, src, sw, npairs, base, tag, xs, tid, o, ss);
     else if (p.tp_size == 4)
-        for (int base = 0; base < npairs; base += kConsumers * 4) poll_x_sum_pass<4, 4>(p, sh, src, sw, npairs, base, tag, xs, tid);
-    else
-        for (int base = 0; base < npairs; base += kConsumers * 2) poll_x_sum_pass<8, 2>(p, sh, src, sw, npairs, base, tag, xs, tid);
+        for (int base = 0; base < npairs; base += kConsumers * 2) poll_x_sum_pass<4, 2>(p, sh, src, sw, npairs, base, tag, xs, tid, o, ss);
+    else  // 8 ranks (the launcher admits 1, 2, 4 and 8)
+        for (int base = 0; base < npairs; base += kConsumers) poll_x_sum_pass<8, 1>(p, sh, src, sw, npairs, base, tag, xs, tid, o, ss);
+    publish_ss(sh, ss, tid);
     return consumer_bar_ok(sh.abort, sh.decision, tid, bk);
 }
 
@@ -585,12 +695,12 @@ __device__ __forceinline__ bool poll_attention(const MegaParams &p, Shared &sh, 
 
 // One vector-matrix phase for the consumer threads.
 //
-// The input vector lives in shared memory for the whole phase (normalised in place when the phase starts
-// with an RMSNorm), so a warp needs no registers for it and any warp can take any tile: tiles go
-// round-robin to the four consumer warps, each warp works through its own tiles without ever meeting the
-// others, and the only CTA-wide synchronisation is at the end of a row block.  Per 16-byte step a lane
-// reads one vector of x and the matching vector of RB weight rows (all conflict-free 128-bit shared loads)
-// and feeds RB accumulators; the RB cross-lane sums are folded into one butterfly (reduce_rows).
+// The input vector lives in shared memory for the whole phase (already multiplied by the RMSNorm gains when
+// the phase starts with an RMSNorm).  All four consumer warps walk the CTA's tiles in order and each takes
+// its own quarter of the row length of every tile: per 16-byte step a lane reads one vector of x and the
+// matching vector of RB weight rows (all conflict-free 128-bit shared loads) and feeds RB accumulators; the
+// RB cross-lane sums are folded into one butterfly (reduce_rows) and land in the warp's column of the
+// table of partial row sums.  A warp hands its share of the stage back as soon as its loads are done.
 //   xres = the residual-stream value of the row this thread finishes in the o_proj / down phases (the row
 //   split of those two phases is the same, so the value never leaves the thread).
 
@@ -627,26 +737,29 @@ __device__ __forceinline__ int reduce_row_of(int lane) {
     return row;
 }
 
-// Rows [rb, rb + RB) of one tile (row indices clamped to the tile's last row; x is zero-padded so that the
-// clamped vector index of the last lanes contributes nothing).
+// Steps [s0, s1) of a lane through rows [rb, rb + RB) of one tile: a step is 32 consecutive 16-byte vectors of
+// the row, one per lane.  Row indices are clamped to the tile's last row, vector indices to the row's last
+// vector (x is zero-padded to whole steps, so a clamped vector contributes nothing).
 template <typename WT, int RB>
-__device__ __forceinline__ void tile_rows(const uint4 *st, const float4 *xs4, int nvec, int njl, int lane, int nr, int rb,
-                                          float (&acc)[RB]) {
+__device__ __forceinline__ void tile_rows(const uint4 *st, const float4 *xs4, int stride, int nvec, int s0, int s1, int lane, int nr,
+                                          int rb, float (&acc)[RB]) {
     constexpr int XQ = VecTraits<WT>::XQ;
-    constexpr int NA = RB >= 4 ? 1 : 4 / RB;  // accumulators per row: four independent FMA chains in all
+    // accumulators per row: two FMA chains per row measured 24 % faster than one on tiles resident in shared memory
+    // (904 against 1194 cycles per 16 KB tile and warp), the dependent chain of one being 32 FMAs long
+    constexpr int NA = RB >= 4 ? 2 : 4 / RB;
     const uint4 *row[RB];
     float a[RB][NA];
 #pragma unroll
     for (int i = 0; i < RB; ++i) {
-        row[i] = st + (size_t)min(rb + i, nr - 1) * nvec;
+        row[i] = st + (size_t)min(rb + i, nr - 1) * stride;
 #pragma unroll
         for (int c = 0; c < NA; ++c) a[i][c] = 0.f;
     }
     const int vlast = nvec - 1;
-    for (int j0 = 0; j0 < njl; j0 += 4) {  // four steps at a time (x is zero-padded to a whole four steps)
+    for (int j = s0; j < s1; j += 4) {  // four steps at a time (x is zero-padded to a whole four steps past the row end)
 #pragma unroll
         for (int jj = 0; jj < 4; ++jj) {
-            const int vx = lane + 32 * (j0 + jj);
+            const int vx = lane + 32 * (j + jj);
             const int v = min(vx, vlast);
             float4 x[XQ];
 #pragma unroll
@@ -664,24 +777,26 @@ __device__ __forceinline__ void tile_rows(const uint4 *st, const float4 *xs4, in
     }
 }
 
+// One tile, worked through by one warp: nr rows of seg_nvec vectors each (row groups of RB), against the
+// matching part of x; part points at the tile's first row in the table of partial sums (column = segment).
 template <typename WT, int RB>
-__device__ __forceinline__ void consume_tile(const MegaParams &p, Shared &sh, const uint4 *st, const float4 *xs4, int nvec, int njl,
-                                             int lane, int nr, bool have, float *part, int rs, uint32_t slot, int cta) {
+__device__ __forceinline__ void consume_tile(const MegaParams &p, Shared &sh, const uint4 *st, const float4 *xs4, int stride, int seg_nvec,
+                                             int s0, int s1, int lane, int nr, bool have, float *part, int rs, uint32_t slot, int cta) {
     for (int rb = 0; rb < nr; rb += RB) {
         float acc[RB];
         if (have) {
-            tile_rows<WT, RB>(st, xs4, nvec, njl, lane, nr, rb, acc);
+            tile_rows<WT, RB>(st, xs4, stride, seg_nvec, s0, s1, lane, nr, rb, acc);
         } else {
 #pragma unroll
             for (int i = 0; i < RB; ++i) acc[i] = 0.f;
         }
         if (rb + RB >= nr) {  // the tile's last loads are done: the stage can go back to the producer
             __syncwarp();
-            if (lane == 0) release_stage(p, sh, rs, kConsumerWarps, slot, cta, 0);  // all 4 arrivals of the stage
+            if (lane == 0 && !(p.debug_flags & 16)) release_stage(p, sh, rs, 1, slot, cta, 0);
         }
         const float s = reduce_rows<RB>(acc, lane);
         const int r = reduce_row_of<RB>(lane);
-        if (r >= 0 && rb + r < nr) part[(rb + r) * kConsumerWarps] = s;
+        if (r >= 0 && rb + r < nr) part[(rb + r) * kPartCols] = s;
     }
 }
 
@@ -689,43 +804,39 @@ template <typename WT>
 __device__ __forceinline__ bool gemv_phase(const MegaParams &p, Shared &sh, const Phase &g, long id, RingPos &rp, int cta, int nctas,
                                            int tid, int &bk, int ph, float &xres) {
     constexpr int XPV = VecTraits<WT>::XPV;
-    constexpr int XQ = VecTraits<WT>::XQ;
     const int lane = tid & 31, warp = tid >> 5;
     const MegaLayer *lw = g.layer < p.L ? &p.layers[g.layer] : nullptr;
-    const TileIter ti(g, (int)sizeof(WT), sh.stage_bytes, cta, nctas, (p.debug_flags & 1) != 0);
+    const PhaseTiles ti(g, (int)sizeof(WT), sh.stage_bytes, cta, nctas);
     // No rows of this matrix here: nothing to read, nothing to publish - except that the phases which stage
     // the residual stream also refresh the residual value this thread carries for the o_proj / down epilogues.
     const bool has_rows = ti.r0 != ti.r1;
     const bool stages_x = g.kind == PH_QKV || g.kind == PH_GATEUP;
     if (!has_rows && !stages_x) return true;
-    const int nvec = g.K / XPV;          // 16-byte weight vectors per row
-    const int njl = (nvec + 31) / 32;    // steps of a lane through a row
+    const int njl = ti.njl;  // steps of a lane through a whole row
 
     // ---- prologue: the input vector, in shared memory ---------------------------------------------------
     float *xs = sh.xs;
     float4 *xs4 = reinterpret_cast<float4 *>(xs);
-    // RMSNorm gains of the phase are requested before the wait for x, so that their trip to L2 is not added
-    // to the critical path (up to 4 vectors per thread: K <= 2048; longer rows fetch them afterwards).
-    const float *norm_w = nullptr;
-    if (g.kind == PH_QKV) norm_w = lw->norm1;
-    else if (g.kind == PH_GATEUP) norm_w = lw->norm2;
-    else if (g.kind == PH_LMHEAD) norm_w = p.final_norm;
-    constexpr int kEarlyGains = 4;
-    const int n4s = g.K / 4;
-    const bool early = norm_w != nullptr && n4s <= kEarlyGains * kConsumers;
-    float4 gains[kEarlyGains];
-    if (early) {
-#pragma unroll
-        for (int u = 0; u < kEarlyGains; ++u) {
-            const int i = tid + kConsumers * u;
-            gains[u] = i < n4s ? __ldg(reinterpret_cast<const float4 *>(norm_w) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
+    StageOpts so;
+    if (g.kind == PH_QKV) so.gains = lw->norm1;
+    else if (g.kind == PH_GATEUP) so.gains = lw->norm2;
+    else if (g.kind == PH_LMHEAD) so.gains = p.final_norm;
+    const bool normed = so.gains != nullptr;
+    const long r0h = (long)p.H * cta / nctas, r1h = (long)p.H * (cta + 1) / nctas;
+    if (stages_x) {
+        so.xraw = sh.xraw;
+        so.r0 = (int)r0h;
+        so.r1 = (int)r1h;
     }
-    const int njl4 = (njl + 3) & ~3;     // the inner loop takes four steps at a time
-    for (int k = g.K + tid; k < njl4 * 32 * XPV; k += kConsumers) xs[k] = 0.f;  // zero padding up to whole steps
+    const int njl4 = (njl + 3) & ~3;  // the inner loop takes four steps at a time
+    for (int k = g.K + tid; k < njl4 * 32 * XPV; k += kConsumers) xs[k] = 0.f;  // zero padding up to whole blocks of steps
     if (g.kind == PH_QKV && g.layer == 0) {
         // Embedding::forward (embedding.rs:47-57): the token's row is the first layer's input
-        for (int k = tid; k < g.K; k += kConsumers) xs[k] = embed_elem(p, id, k);
+        float ss = 0.f;
+        for (int k = tid; k < g.K / 2; k += kConsumers)
+            stage_pair(so, xs, k, embed_elem(p, id, 2 * k), embed_elem(p, id, 2 * k + 1),
+                       __ldg(reinterpret_cast<const float2 *>(so.gains) + k), ss);
+        publish_ss(sh, ss, tid);
         consumer_bar();
     } else {
         const uint32_t tag = phase_tag(p, ph - 1);  // every phase consumes what the phase before it published
@@ -734,96 +845,96 @@ __device__ __forceinline__ bool gemv_phase(const MegaParams &p, Shared &sh, cons
         const uint2 *xsrc = p.xT + (size_t)(g.kind == PH_GATEUP ? 0 : 1) * p.tp_size * p.x_slot_words;
         if (g.kind == PH_O) ok = poll_attention(p, sh, tag, xs, tid, bk);
         else if (g.kind == PH_DOWN) ok = poll_vector(p, sh, p.actT, g.K, tag, xs, tid, bk, 330 + g.kind);
-        else if (p.tp_size == 1) ok = poll_vector(p, sh, xsrc, g.K, tag, xs, tid, bk, 330 + g.kind);
-        else ok = poll_x_sum(p, sh, xsrc, g.K, tag, xs, tid, bk);
+        else if (p.tp_size == 1) ok = poll_vector(p, sh, xsrc, g.K, tag, xs, tid, bk, 330 + g.kind, so);
+        else ok = poll_x_sum(p, sh, xsrc, g.K, tag, xs, tid, bk, so);
         if (!ok) return false;
         if (p.trace && cta == 0 && tid == 0) p.trace[4 * (5 * p.L + 1) + 1 + ph] = globaltimer_ns();
     }
+    // RMSNorm::forward (rms_norm.rs:49-56): rms = sqrt(ss/dim + eps), inv = 1/rms.  The vector in shared memory
+    // carries the gains; inv multiplies the row sums in the epilogue.
+    float inv = 1.f;
+    if (normed) {
+        float tot = 0.f;
+#pragma unroll
+        for (int w = 0; w < kConsumerWarps; ++w) tot += sh.red[w];
+        inv = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(tot, (float)g.K), p.eps)));
+    }
     if (stages_x) {
-        // xs holds the whole residual stream (all ranks' partial sums added): keep this thread's row of it
-        const long r0h = (long)p.H * cta / nctas, r1h = (long)p.H * (cta + 1) / nctas;
-        if (tid < r1h - r0h) xres = xs[r0h + tid];
+        // keep this thread's row of the residual stream (all ranks' partial sums added, before the gains)
+        if (tid < r1h - r0h) xres = sh.xraw[tid];
         if (!has_rows) {
             trace_stamp(p, cta, tid, 3 * ph + 1);
             trace_stamp(p, cta, tid, 3 * ph + 2);
             return true;
         }
     }
-    if (norm_w) {
-        // RMSNorm::forward (rms_norm.rs:49-56): rms = sqrt(ss/dim + eps); x = (x * (1/rms)) * w, in place
-        const float4 *n4 = reinterpret_cast<const float4 *>(norm_w);
-        float ss = 0.f;
-        for (int i = tid; i < n4s; i += kConsumers) {
-            const float4 v = xs4[i];
-            ss = fmaf(v.x, v.x, ss);
-            ss = fmaf(v.y, v.y, ss);
-            ss = fmaf(v.z, v.z, ss);
-            ss = fmaf(v.w, v.w, ss);
-        }
-        ss = warp_sum(ss);
-        if (lane == 0) sh.red[warp] = ss;
-        consumer_bar();
-        const float tot = (sh.red[0] + sh.red[1]) + (sh.red[2] + sh.red[3]);
-        const float inv = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(tot, (float)g.K), p.eps)));
-        auto rescale = [&](int i, const float4 w) {
-            float4 v = xs4[i];
-            v.x = __fmul_rn(__fmul_rn(v.x, inv), w.x);
-            v.y = __fmul_rn(__fmul_rn(v.y, inv), w.y);
-            v.z = __fmul_rn(__fmul_rn(v.z, inv), w.z);
-            v.w = __fmul_rn(__fmul_rn(v.w, inv), w.w);
-            xs4[i] = v;
-        };
-        if (early) {
-#pragma unroll
-            for (int u = 0; u < kEarlyGains; ++u) {
-                const int i = tid + kConsumers * u;
-                if (i < n4s) rescale(i, gains[u]);
-            }
-        } else {
-            for (int i = tid; i < n4s; i += kConsumers) rescale(i, __ldg(n4 + i));
-        }
-        consumer_bar();
-    }
     trace_stamp(p, cta, tid, 3 * ph + 1);
+    trace_cta(p, cta, tid, 0, ph);
 
     // ---- tiles ------------------------------------------------------------------------------------------
-    // Tiles are addressed in closed form: tile t of the phase covers rows [R * (t / nmat), +R) of the CTA's
-    // range in matrix t % nmat (gate rows, then the same rows of up) and sits in ring slot (tiles consumed
-    // so far + t).  Warp w owns tiles w, w + 4, ...  Rows are reduced and published in blocks of at most
-    // kRowBlock (a block never splits a tile).
-    const int R = ti.R, nmat = ti.nmat;
-    const int nrows_cta = (int)(ti.r1 - ti.r0);
-    const int chunks = (p.debug_flags & 1) ? 0 : (nrows_cta + R - 1) / R;
+    // Tiles are addressed in closed form (see PhaseTiles) and sit in ring slot (tiles consumed so far + t).
+    // Warp w owns tiles w, w + 4, ...  Rows are reduced and published in blocks of at most kRowBlock (a block
+    // never splits a chunk of rows).
+    constexpr int XQ = VecTraits<WT>::XQ;
+    const int R = ti.R, nmat = ti.nmat, nseg = ti.nseg;
+    const int nrows_cta = ti.nrows;
+    const int chunks = ((p.debug_flags & 1) && !(p.debug_flags & 16)) ? 0 : ti.chunks;
+    const bool dry = (p.debug_flags & 16) != 0;  // debug: no copies are issued (bit 0); run the arithmetic on whatever the ring holds
     const int chunks_per_block = kRowBlock / R;
+    const int tpc = nmat * nseg;  // tiles per chunk of rows
+    // rows of a segment tile that came as a box sit a whole segment slot apart (the box is zero-filled past the row end)
+    const bool boxed = nseg > 1 && p.tmaps != nullptr;
     for (int cb = 0; cb < chunks; cb += chunks_per_block) {
         const int cend = min(chunks, cb + chunks_per_block);
-        const int t0 = cb * nmat, t1 = cend * nmat;
+        const int t0 = cb * tpc, t1 = cend * tpc;
         const int row0_blk = cb * R;  // first row of the block, relative to the CTA's first row
-        for (int t = t0 + ((warp - t0) & (kConsumerWarps - 1)); t < t1; t += kConsumerWarps) {
-            const int chunk = t / nmat, mat = t - chunk * nmat;
+        // Warp w owns tiles w, w + W, ... of the phase.  The tile's coordinates and its ring position are carried
+        // along incrementally (no divisions in the loop).
+        int t = t0 + (warp + kConsumerWarps - t0 % kConsumerWarps) % kConsumerWarps;
+        int chunk = t / tpc, mat = (t - chunk * tpc) / nseg, seg = t - chunk * tpc - mat * nseg;
+        uint32_t slot = rp.n + (uint32_t)t;
+        int rs = (int)(slot % (uint32_t)sh.S);
+        uint32_t use = slot / (uint32_t)sh.S;
+        for (; t < t1; t += kConsumerWarps) {
             const int rrel = chunk * R;
             const int nr = min(R, nrows_cta - rrel);
-            const uint32_t slot = rp.n + (uint32_t)t;
-            const int rs = (int)(slot % (uint32_t)sh.S);
-            const uint32_t use = slot / (uint32_t)sh.S;
             // A parity test tells two phases apart, not three: before testing for use `u` of this stage,
             // use `u-1` (owned by another warp) must be known to have landed.  Its owner publishes that.
             // A failed wait must not leave early (see consumer_bar_ok): skip the math, keep the sequence.
-            bool have = stage_use_seen(p, sh, rs, (int)use, 310 + g.kind);
-            have = have && mbar_wait(p, sh, &sh.full[rs], use & 1, 300 + g.kind);
-            if (have && lane == 0) sh.seen[rs] = (int)use + 1;
+            bool have = dry || stage_use_seen(p, sh, rs, (int)use, 310 + g.kind);
+            have = have && (dry || mbar_wait(p, sh, &sh.full[rs], use & 1, 300 + g.kind));
+            if (have && lane == 0 && !dry) sh.seen[rs] = (int)use + 1;
             if (p.debug_flags & 4) have = false;  // debug: wait for the tiles but skip the arithmetic
             const uint4 *st = reinterpret_cast<const uint4 *>(sh.stages + (size_t)rs * sh.stage_bytes);
-            float *part = sh.part + ((size_t)mat * kRowBlock + (size_t)(rrel - row0_blk)) * kConsumerWarps;
-            if (R >= 4) consume_tile<WT, 4>(p, sh, st, xs4, nvec, njl, lane, nr, have, part, rs, slot, cta);
-            else if (R >= 2) consume_tile<WT, 2>(p, sh, st, xs4, nvec, njl, lane, nr, have, part, rs, slot, cta);
-            else consume_tile<WT, 1>(p, sh, st, xs4, nvec, njl, lane, nr, have, part, rs, slot, cta);
+            float *part = sh.part + ((size_t)mat * kRowBlock + (size_t)(rrel - row0_blk)) * kPartCols + seg;
+            const int seg_nvec = ti.seg_bytes(seg) / 16;  // valid 16-byte vectors of a row of this tile
+            consume_tile<WT, 4>(p, sh, st, xs4 + (size_t)seg * ti.per * 32 * XQ, boxed ? ti.per * 32 : seg_nvec, seg_nvec, 0, ti.seg_steps(seg),
+                                lane, nr, have, part, rs, slot, cta);
+            // the next tile of this warp
+            slot += kConsumerWarps;
+            rs += kConsumerWarps;
+            while (rs >= sh.S) {
+                rs -= sh.S;
+                ++use;
+            }
+            seg += kConsumerWarps;
+            while (seg >= nseg) {
+                seg -= nseg;
+                if (++mat == nmat) {
+                    mat = 0;
+                    ++chunk;
+                }
+            }
         }
-        // End of a row block: run the epilogue on the row sums and publish.
+        // End of a row block: add the warps' partial sums, run the epilogue and publish.
         const int nrows = min(cend * R, nrows_cta) - row0_blk;
         if (!consumer_bar_ok(sh.abort, sh.decision, tid, bk)) return false;
         if (tid < nrows) {
-            const float tot = sh.part[(size_t)tid * kConsumerWarps];
+            // the segments of the row, added in order
+            const float *pr = sh.part + (size_t)tid * kPartCols;
+            float acc = pr[0];
+            for (int c = 1; c < nseg; ++c) acc += pr[c];
+            const float tot = __fmul_rn(acc, inv);
             const long row = ti.r0 + row0_blk + tid;
             const uint32_t tag = phase_tag(p, ph);
             switch (g.kind) {
@@ -846,7 +957,10 @@ __device__ __forceinline__ bool gemv_phase(const MegaParams &p, Shared &sh, cons
                     break;
                 }
                 case PH_GATEUP: {  // SiLU (activation.rs:143-146) then gate_act * up (llama.rs:61-63)
-                    const float up = sh.part[((size_t)kRowBlock + tid) * kConsumerWarps];
+                    const float *pu = sh.part + ((size_t)kRowBlock + tid) * kPartCols;
+                    float accu = pu[0];
+                    for (int c = 1; c < nseg; ++c) accu += pu[c];
+                    const float up = __fmul_rn(accu, inv);
                     const float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-tot)));
                     st_tagged(p.actT + row, __fmul_rn(__fmul_rn(tot, sig), up), tag);
                     break;
@@ -856,13 +970,14 @@ __device__ __forceinline__ bool gemv_phase(const MegaParams &p, Shared &sh, cons
         }
         if (cend < chunks) consumer_bar();  // the table is rewritten by the next block
     }
-    rp.n += (uint32_t)(chunks * nmat);
-    if ((p.debug_flags & 1) && ti.r0 + tid < ti.r1) {  // debug (no tiles streamed): publish zeros so that the chain runs
+    rp.n += (uint32_t)(chunks * tpc);
+    if ((p.debug_flags & 1) && !dry && ti.r0 + tid < ti.r1) {  // debug (no tiles streamed): publish zeros so that the chain runs
         const uint32_t tag = phase_tag(p, ph);
         uint2 *dst = g.kind == PH_QKV ? p.qkvT : g.kind == PH_GATEUP ? p.actT : p.xT + (size_t)(g.kind == PH_O ? 0 : 1) * p.x_slot_words;
         if (g.kind != PH_LMHEAD) st_tagged(dst + ti.r0 + tid, 0.f, tag);
     }
     trace_stamp(p, cta, tid, 3 * ph + 2);
+    trace_cta(p, cta, tid, 1, ph);
     return true;
 }
 
@@ -973,6 +1088,7 @@ __device__ __forceinline__ void consumer_loop(const MegaParams &p, Shared &sh, i
             if (!attention_phase(p, sh, g.layer, ph, past, cta, nctas, tid, bk)) return;
             trace_stamp(p, cta, tid, 3 * ph + 1);
             trace_stamp(p, cta, tid, 3 * ph + 2);
+            if (cta < p.Hq * p.nsplit) trace_cta(p, cta, tid, 1, ph);
         } else {
             if (!gemv_phase<WT>(p, sh, g, id, rp, cta, nctas, tid, bk, ph, xres)) return;
         }
@@ -995,6 +1111,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const __grid_c
     __shared__ int abort_flag;
     __shared__ int decision[2];
     __shared__ int seen[kMegaMaxStages];
+    __shared__ int issued[kMegaMaxStages];
     Shared sh;
     sh.S = p.stages;
     sh.stage_bytes = p.stage_bytes;
@@ -1003,20 +1120,25 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const __grid_c
     sh.xs = fl;
     sh.part = fl + mega_xs_floats(max(p.H, max(p.qd, p.I)));
     sh.red = fl + mega_table_floats(max(p.H, max(p.qd, p.I)));
-    sh.attn = sh.red + kConsumerWarps;
+    sh.xraw = sh.red + kConsumerWarps;
+    sh.attn = sh.xraw + kRowBlock;
     sh.full = bars;
     sh.empty = bars + kMegaMaxStages;
     sh.abort = &abort_flag;
     sh.decision = decision;
     sh.seen = seen;
+    sh.issued = issued;
     const int tid = threadIdx.x;
     if (tid == 0) {
         abort_flag = 0;
         decision[0] = decision[1] = 0;
-        for (int s = 0; s < kMegaMaxStages; ++s) seen[s] = 0;
+        for (int s = 0; s < kMegaMaxStages; ++s) {
+            seen[s] = 0;
+            issued[s] = -1;
+        }
         for (int s = 0; s < sh.S; ++s) {
             mbar_init(&sh.full[s], 1);                 // the producer's arrive.expect_tx
-            mbar_init(&sh.empty[s], kConsumerWarps);   // 4 arrivals: the owning group's warps, G each
+            mbar_init(&sh.empty[s], 1);                // the warp that worked on the tile
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -1033,7 +1155,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const __grid_c
 
 size_t decode_mega_smem_bytes(int stages, int stage_bytes, int head_dim, int kmax) {
     return (size_t)stages * stage_bytes +
-           (mega_table_floats(kmax) + kConsumerWarps + attn_decode_smem_floats(1, head_dim, kConsumerWarps) + 3 * (size_t)head_dim) * sizeof(float);
+           (mega_table_floats(kmax) + kConsumerWarps + kRowBlock + attn_decode_smem_floats(1, head_dim, kConsumerWarps) + 3 * (size_t)head_dim) *
+               sizeof(float);
 }
 
 int decode_mega_max_splits() { return kMaxSplit; }
@@ -1046,23 +1169,109 @@ int decode_mega_debug_flags() {
     return flags;
 }
 
+namespace {
+// Tensor map over a row-major matrix [rows, rowbytes] seen as 32-bit words [rows][rowbytes / 256][64]: a box of
+// box_rows rows x `units` 256-byte units (one segment of the row length), no swizzle, zero fill past the edges.
+bool make_segment_map(CUtensorMap *map, const void *base, size_t rows, size_t rowbytes, int units, int box_rows) {
+    typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                 const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn fn = [] {
+        void *f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+            f = nullptr;
+        return reinterpret_cast<EncodeFn>(f);
+    }();
+    if (!fn || rowbytes % 256 || units < 1 || units > 256) return false;
+    const cuuint64_t dims[3] = {64, (cuuint64_t)(rowbytes / 256), (cuuint64_t)rows};
+    const cuuint64_t strides[2] = {256, (cuuint64_t)rowbytes};
+    const cuuint32_t box[3] = {64, (cuuint32_t)units, (cuuint32_t)box_rows};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+}  // namespace
+
 void decode_mega_build_schedule(const MegaParams &p_in, const MegaLayer *host_layers, int grid, std::vector<uint4> &entries,
-                                std::vector<int> &counts, int &stride) {
+                                std::vector<int> &counts, int &stride, std::vector<CUtensorMap> &tmaps) {
     MegaParams p = p_in;
     p.debug_flags = decode_mega_debug_flags();
     const int esz = p.wbf16 ? 2 : 4, nphases = 5 * p.L + 1;
-    std::vector<std::vector<uint4>> per(grid);
-    for (int cta = 0; cta < grid; ++cta) {
-        for (int ph = 0; ph < nphases; ++ph) {
-            const Phase g = get_phase(p, host_layers, ph);
-            if (g.kind == PH_ATT) continue;
-            for (TileIter ti(g, esz, kMegaStageBytes, cta, grid, (p.debug_flags & 1) != 0); ti.valid(); ti.advance()) {
-                // whole rows are one contiguous block: one copy per tile
-                const unsigned long long a = (unsigned long long)(uintptr_t)((ti.mat == 0 ? g.w0 : g.w1) + (size_t)ti.r * ti.rowbytes);
-                const uint32_t tile_bytes = (uint32_t)ti.rows() * (uint32_t)ti.rowbytes;
-                per[cta].push_back(make_uint4((uint32_t)a, (uint32_t)(a >> 32), tile_bytes | ((uint32_t)ph << 16), tile_bytes));
+    // Tensor maps are all or nothing (the consumers derive the layout of a segment tile from `tmaps != nullptr`):
+    // if one cannot be made, the schedule is built again without any.
+    bool no_tensor = getenv("LUMEN_MEGA_NO_TENSOR_COPY") != nullptr;
+    bool retry = false;
+    std::vector<std::vector<uint4>> per;
+build:
+    tmaps.clear();
+    per.assign(grid, std::vector<uint4>());
+    for (int ph = 0; ph < nphases; ++ph) {
+        const Phase g = get_phase(p, host_layers, ph);
+        if (g.kind == PH_ATT) continue;
+        // Matrices whose rows are cut into segments get two tensor maps each (boxes of 4 rows and of 1 row).
+        int map0[2] = {-1, -1};
+        {
+            const PhaseTiles pt(g, esz, kMegaStageBytes, 0, grid);
+            if (pt.nseg > 1 && !no_tensor) {
+                for (int mat = 0; mat < pt.nmat; ++mat) {
+                    CUtensorMap m4, m1;
+                    const char *w = mat == 0 ? g.w0 : g.w1;
+                    if (make_segment_map(&m4, w, (size_t)g.N, (size_t)pt.rowbytes, pt.per * 2, 4) &&
+                        make_segment_map(&m1, w, (size_t)g.N, (size_t)pt.rowbytes, pt.per * 2, 1)) {
+                        map0[mat] = (int)tmaps.size();
+                        tmaps.push_back(m4);
+                        tmaps.push_back(m1);
+                    } else {
+                        retry = true;
+                    }
+                }
+                if (retry) break;
             }
         }
+        for (int cta = 0; cta < grid; ++cta) {
+            const PhaseTiles pt(g, esz, kMegaStageBytes, cta, grid);
+            const int ntiles = (p.debug_flags & 1) ? 0 : pt.tiles();  // debug: stream nothing
+            for (int t = 0; t < ntiles; ++t) {
+                const int seg = t % pt.nseg, mat = (t / pt.nseg) % pt.nmat, chunk = t / (pt.nseg * pt.nmat);
+                const int nr = std::min(pt.R, pt.nrows - chunk * pt.R);
+                const long row = pt.r0 + (long)chunk * pt.R;
+                const uint32_t phz = (uint32_t)ph << 16;
+                if (pt.nseg == 1) {  // whole rows are one contiguous block: one plain copy per tile
+                    const unsigned long long a = (unsigned long long)(uintptr_t)((mat == 0 ? g.w0 : g.w1) + (size_t)row * pt.rowbytes);
+                    const uint32_t tile_bytes = (uint32_t)nr * (uint32_t)pt.rowbytes;
+                    per[cta].push_back(make_uint4((uint32_t)a, (uint32_t)(a >> 32), tile_bytes | phz, tile_bytes));
+                    continue;
+                }
+                // Segments: the rows of a tile sit pt.per * 512 bytes apart in the stage, whatever the segment's length.
+                const uint32_t slot_bytes = (uint32_t)pt.per * 512u;
+                if (map0[mat] >= 0) {  // one box of four rows, or one box per row for a shorter last chunk
+                    const uint32_t unit0 = (uint32_t)(seg * pt.per * 2);
+                    if (nr == 4) {
+                        per[cta].push_back(make_uint4((uint32_t)map0[mat] | (unit0 << 16), (uint32_t)row, 4u * slot_bytes | phz,
+                                                      4u * slot_bytes | 0x80000000u));
+                    } else {
+                        for (int c = 0; c < nr; ++c)
+                            per[cta].push_back(make_uint4((uint32_t)(map0[mat] + 1) | (unit0 << 16), (uint32_t)(row + c), slot_bytes | phz,
+                                                          (c == 0 ? (uint32_t)nr * slot_bytes : 0u) | (((uint32_t)c * slot_bytes / 16u) << 16) |
+                                                              0x80000000u));
+                    }
+                } else {  // no tensor maps: one plain copy per row
+                    const uint32_t sb = (uint32_t)pt.seg_bytes(seg);
+                    const char *w = (mat == 0 ? g.w0 : g.w1) + (size_t)row * pt.rowbytes + (size_t)seg * pt.per * 512;
+                    for (int c = 0; c < nr; ++c) {
+                        const unsigned long long a = (unsigned long long)(uintptr_t)(w + (size_t)c * pt.rowbytes);
+                        per[cta].push_back(make_uint4((uint32_t)a, (uint32_t)(a >> 32), sb | phz,
+                                                      (c == 0 ? (uint32_t)nr * sb : 0u) | (((uint32_t)c * sb / 16u) << 16)));
+                    }
+                }
+            }
+        }
+    }
+    if (retry && !no_tensor) {
+        no_tensor = true;
+        retry = false;
+        goto build;
     }
     size_t mx = 1;
     for (auto &v : per) mx = std::max(mx, v.size());
@@ -1090,8 +1299,8 @@ int decode_mega_supported(const MegaParams &p, char *why, size_t why_len) {
             snprintf(why, why_len, "row of %d elements is not a multiple of 16 bytes", k);
             return 0;
         }
-        if (k * esz > kMegaStageBytes) {
-            snprintf(why, why_len, "a row of %d elements does not fit one %d-byte ring stage", k, kMegaStageBytes);
+        if (k * esz > kMaxSeg * (kMegaStageBytes / 4)) {
+            snprintf(why, why_len, "a row of %d elements is longer than %d segments of %d bytes", k, kMaxSeg, kMegaStageBytes / 4);
             return 0;
         }
     }
@@ -1122,7 +1331,8 @@ int launch_decode_mega(lumen_ctx *ctx, MegaParams &p, cudaStream_t s) {
     p.debug_flags = decode_mega_debug_flags();
     // L2 look-ahead of the producer in copies per CTA, counted from the copy being issued (the ring itself
     // holds `stages` of them): 0 = off, at most 56.
-    p.l2_ahead = 8;  // measured: +2 % at 8, no gain at 12, a loss from 20 on (the look-ahead competes with the exchanges)
+    // (copies handed to the L2 each time the ring is full; the producer holds at most 64 entries of its schedule)
+    p.l2_ahead = 12;
     if (const char *e = getenv("LUMEN_MEGA_L2_AHEAD")) p.l2_ahead = std::max(0, std::min(56, atoi(e)));
     if (!p.sched || !p.sched_count) return set_error(ctx, LUMEN_ERR_INVALID, "persistent decode kernel: no producer schedule");
     const size_t smem = decode_mega_smem_bytes(stages, p.stage_bytes, p.D, kmax);

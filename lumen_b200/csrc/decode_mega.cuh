@@ -1,12 +1,17 @@
 // Parameters of the whole-token persistent decode kernel (decode_mega.cu).
 #pragma once
 
+#include <cuda.h>
+
 #include "common.cuh"
 
 namespace lumen {
 
-constexpr int kMegaMaxStages = 7;
-constexpr int kMegaStageBytes = 32 * 1024;  // one ring stage: a row (or row segment) of every supported matrix fits
+// The ring: many small stages rather than few large ones.  A consumer warp holds the stage it works on, and a held
+// stage is not in flight: with four warps at work, what bounds the streaming rate of an SM is (stages - 4) x stage
+// bytes / memory latency.  One stage = four rows x 4 KB (rows longer than 4 KB are cut into segments).
+constexpr int kMegaMaxStages = 13;
+constexpr int kMegaStageBytes = 16 * 1024;
 
 struct MegaLayer {
     const char *wqkv, *wo, *wgate, *wup, *wdown;  // [rows, K] row-major, f32 or bf16
@@ -56,15 +61,23 @@ struct MegaParams {
     //   [6nph+1, +nph)   warp 0: clock cycles spent on the tiles of the phase (loads, FMAs, reductions)
     //   [7nph+1, +512)   producer: ns timestamp of the issue of each of the first 512 tiles
     //   [7nph+513, +512) consumers: ns timestamp of the release of each of those tiles
+    //   then, written by every CTA c < kMegaTraceCtas: [nph][kMegaTraceCtas] ns timestamp when the phase's input
+    //   had arrived, and [nph][kMegaTraceCtas] ns timestamp when the CTA had published the phase's results
     unsigned long long *trace;
     // Producer schedule: for CTA c the bulk copies of one token in issue order, sched[c * sched_stride + i],
     // i < sched_count[c].  Entry = {src address lo, hi, copy bytes | phase << 16, tile bytes}; tile bytes is
     // non-zero on the first copy of a tile (= the transaction count of its stage) and 0 on the following ones.
     // The schedule depends only on the model's shapes and addresses, so it is built once on the host
     // (decode_mega_build_schedule) and the producer does no address arithmetic at all.
+    // A copy is either a plain 1-D bulk copy, entry = {src address lo, hi, copy bytes | phase << 16, w},
+    // or (bit 31 of w set) a 3-D tiled TMA copy of a box of rows x one segment of the row length out of a
+    // row-major matrix, entry = {tensor map index | first 256-byte unit of the segment << 16, first row,
+    // copy bytes | phase << 16, w}.  w = tile bytes (bits 0-15, non-zero on the first copy of a tile only) |
+    // offset of the copy inside its ring stage / 16 (bits 16-27) | bit 31.  A segment tile of four rows is ONE box.
     const uint4 *sched;
     const int *sched_count;
     int sched_stride;
+    const CUtensorMap *tmaps;  // device array of the tensor maps the schedule refers to (64-byte aligned)
     int l2_ahead;  // copies the producer's L2 prefetch runs ahead of the copy it issues (0 = off)
     // bit 0: stream no weight tiles (measures the exchange + prologue chain alone; results are wrong)
     // bit 2: wait for the weight tiles but skip the arithmetic on them
@@ -79,12 +92,19 @@ size_t decode_mega_exchange_words(const MegaParams &p);  // uint2 words of the f
 size_t decode_mega_x_words(const MegaParams &p);         // of which the x buffers, at the start (needs tp_size, H)
 int decode_mega_max_splits();
 constexpr int kMegaTileTrace = 512;
-inline size_t decode_mega_trace_words(size_t layers) { return 7 * (5 * layers + 1) + 1 + 2 * kMegaTileTrace; }
+constexpr int kMegaTraceCtas = 160;  // per-CTA part of the trace: [2][nph][kMegaTraceCtas] after the words above
+__host__ __device__ inline size_t decode_mega_trace_base_words(size_t layers) { return 7 * (5 * layers + 1) + 1 + 2 * kMegaTileTrace; }
+inline size_t decode_mega_trace_words(size_t layers) {
+    return decode_mega_trace_base_words(layers) + 2 * (5 * layers + 1) * kMegaTraceCtas;
+}
 int decode_mega_debug_flags();  // from the environment (LUMEN_MEGA_DEBUG), read once
 // Builds the producer schedule for `grid` CTAs from the shapes in p and the HOST copy of the layer table.
 // entries.size() == grid * stride afterwards.
+// tmaps receives the tensor maps of the matrices whose rows are cut into segments (two per matrix: a box of four
+// rows and a box of one row); it stays empty when the driver offers no tensor-map encoder, and segments then
+// arrive as one plain copy per row.
 void decode_mega_build_schedule(const MegaParams &p, const MegaLayer *host_layers, int grid, std::vector<uint4> &entries,
-                                std::vector<int> &counts, int &stride);
+                                std::vector<int> &counts, int &stride, std::vector<CUtensorMap> &tmaps);
 int launch_decode_mega(lumen_ctx *ctx, MegaParams &p, cudaStream_t s);
 
 }  // namespace lumen

@@ -42,21 +42,8 @@ class LlamaConfig:
 
     def param_shapes(self) -> dict:
         """Names and full shapes of `LlamaModel::named_parameters` (llama.rs:218-279)."""
-        H, I, V, D = self.hidden_size, self.intermediate_size, self.vocab_size, self.resolved_head_dim
-        qd, kvd = self.num_attention_heads * D, self.num_key_value_heads * D
-        shapes = {"model.embed_tokens.weight": (V, H), "model.norm.weight": (H,), "lm_head.weight": (V, H)}
-        for i in range(self.num_hidden_layers):
-            p = f"model.layers.{i}."
-            shapes.update({
-                p + "self_attn.q_proj.weight": (qd, H), p + "self_attn.k_proj.weight": (kvd, H),
-                p + "self_attn.v_proj.weight": (kvd, H), p + "self_attn.o_proj.weight": (H, qd),
-                p + "mlp.gate_proj.weight": (I, H), p + "mlp.up_proj.weight": (I, H),
-                p + "mlp.down_proj.weight": (H, I), p + "input_layernorm.weight": (H,),
-                p + "post_attention_layernorm.weight": (H,),
-            })
-            if self.qk_norm:
-                shapes.update({p + "self_attn.q_norm.weight": (D,), p + "self_attn.k_norm.weight": (D,)})
-        return shapes
+        from .synth import param_shapes
+        return param_shapes(self)
 
 
 def tp_param_slice(config: "LlamaConfig", tp_rank: int, tp_size: int, name: str) -> dict:
@@ -118,9 +105,11 @@ class LlamaModel:
         created).  With nph = 5 * layers + 1 phases (qkv, attention, o, gate/up, down per layer, then lm_head):
         `stamps` [nph, 3] ns at phase start / after its prologue / after its last tile, `end` ns,
         `producer` [nph] ns of the phase's first copy, `input_ready` [nph] ns, `wait_cycles` and
-        `busy_cycles` [nph] of consumer warp 0 on weight tiles, `tile_issue` and `tile_release` [512] ns."""
+        `busy_cycles` [nph] of consumer warp 0 on weight tiles, `tile_issue` and `tile_release` [512] ns;
+        `cta_input` and `cta_done` [nph, 160] ns per CTA (0 where a CTA has no part in the phase)."""
         nph = 5 * self.config.num_hidden_layers + 1
-        n = 7 * nph + 1 + 1024
+        base = 7 * nph + 1 + 1024
+        n = base + 2 * nph * 160
         buf = (C.c_uint64 * n)()
         got = C.c_size_t()
         self.ctx.check(self.ctx._lib.lumen_llama_decode_trace(self.h, buf, n, C.byref(got)))
@@ -128,7 +117,9 @@ class LlamaModel:
         return {"stamps": a[:3 * nph].reshape(nph, 3), "end": int(a[3 * nph]),
                 "producer": a[3 * nph + 1:4 * nph + 1], "input_ready": a[4 * nph + 1:5 * nph + 1],
                 "wait_cycles": a[5 * nph + 1:6 * nph + 1], "busy_cycles": a[6 * nph + 1:7 * nph + 1],
-                "tile_issue": a[7 * nph + 1:7 * nph + 513], "tile_release": a[7 * nph + 513:]}
+                "tile_issue": a[7 * nph + 1:7 * nph + 513], "tile_release": a[7 * nph + 513:base],
+                "cta_input": a[base:base + nph * 160].reshape(nph, 160),
+                "cta_done": a[base + nph * 160:base + 2 * nph * 160].reshape(nph, 160)}
 
     @property
     def weight_bytes_per_step(self) -> int:

@@ -16,6 +16,7 @@ import numpy as np
 
 from . import _lib
 from ._lib import BF16, F32, check
+from .synth import bf16_bits_to_f32, f32_to_bf16_bits  # noqa: F401  (numpy-only helpers, re-exported here)
 
 _NO_GRAD_DEPTH = 0
 _INFERENCE_MODE = False
@@ -100,17 +101,6 @@ def default_context() -> Context:
 
 def _shape_arr(shape):
     return (C.c_size_t * len(shape))(*shape)
-
-
-def f32_to_bf16_bits(a: np.ndarray) -> np.ndarray:
-    """Round-to-nearest-even f32 -> bf16 bit patterns (uint16)."""
-    u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
-    rounded = u + (np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1)))
-    return (rounded >> np.uint32(16)).astype(np.uint16)
-
-
-def bf16_bits_to_f32(b: np.ndarray) -> np.ndarray:
-    return (np.ascontiguousarray(b, dtype=np.uint16).astype(np.uint32) << np.uint32(16)).view(np.float32)
 
 
 class Tensor:

@@ -74,6 +74,20 @@ def num_threads() -> int:
     return int(lib().lo_num_threads())
 
 
+def host_cores() -> int:
+    """Cores this process may run on (its affinity mask; the machine's count where that is unknown)."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except (AttributeError, OSError):
+        return os.cpu_count() or 1
+
+
+def set_num_threads(n: int | None = None) -> int:
+    """Use `n` threads (default: every core of this process) whatever OMP_NUM_THREADS says; returns the count in use."""
+    lib().lo_set_num_threads(C.c_int(int(n) if n else host_cores()))
+    return num_threads()
+
+
 def matmul(a, w, prec="f32"):
     """a[..., K] @ w[N, K]^T (src/ops/matmul.rs:10-103)."""
     a, w = _f32(a), _f32(w)

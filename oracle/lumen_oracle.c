@@ -151,3 +151,13 @@ int lo_num_threads(void) {
 #endif
     return n;
 }
+
+/* Thread count of every later parallel loop, independent of OMP_NUM_THREADS (launchers such as
+ * torchrun export OMP_NUM_THREADS=1 to their children); n <= 0 leaves it unchanged. */
+void lo_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}

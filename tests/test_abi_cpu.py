@@ -85,3 +85,30 @@ def test_no_grad_switches(L):
     assert L.is_no_grad()
     L.set_inference_mode(False)
     assert not L.is_no_grad()
+
+
+def test_cpu_arm_of_the_benchmark_does_not_load_the_cuda_library():
+    """`bench.py --impl reference` times the CPU restatement and must not map liblumen_b200.so: its helpers take the
+    seeded generators from lumen_b200/synth.py by file path, without importing the package."""
+    import subprocess
+    import sys
+    code = (
+        "import sys, importlib.util\n"
+        f"spec = importlib.util.spec_from_file_location('bench', r'{ROOT / 'bench.py'}')\n"
+        "b = importlib.util.module_from_spec(spec); spec.loader.exec_module(b)\n"
+        "cfg = b.tinyllama_cfg('f32', 2048)\n"
+        "small = dict(cfg, num_hidden_layers=1, vocab_size=64, hidden_size=64, intermediate_size=128, num_attention_heads=4, num_key_value_heads=2)\n"
+        "params = dict(b.gen_params(small, 'f32'))\n"
+        "ids = b.load_synth().token_ids(1, 40, 64)\n"
+        "b.PROMPT_LEN = 8\n"
+        "tps, steps, threads, lg = b.cpu_decode(small, params, ids, 5.0, 3, 2)\n"
+        "assert steps == 3 and lg.shape == (5, 64) and threads >= 1\n"
+        "assert 'lumen_b200' not in sys.modules, 'the package was imported'\n"
+        "maps = open('/proc/self/maps').read()\n"
+        "assert 'liblumen_b200' not in maps, 'the CUDA library was mapped'\n"
+        "assert 'liblumen_oracle' in maps\n"
+        "assert b.stream_bytes(cfg, 'f32') == 4 * 1034512384, b.stream_bytes(cfg, 'f32')\n"
+        "print('ok')\n")
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300,
+                       env=dict(__import__("os").environ, OMP_NUM_THREADS="1"))
+    assert r.returncode == 0 and r.stdout.strip().endswith("ok"), r.stdout + r.stderr

@@ -217,19 +217,144 @@ def test_error_conditions(L):
         assert e.value.code == L._lib.ERR_SHAPE
 
 
-@pytest.mark.parametrize("wdt,prompt,steps", [("f32", 32, 128), ("bf16", 32, 24)])
-def test_tinyllama_config1_teacher_forced(L, oracle, wdt, prompt, steps):
-    """Benchmark configuration 1 at full size: TinyLlama-1.1B shape, weights N(0,0.02) seed 0 (gains 1.0), 32
-    prompt ids from seed 1 and teacher-forced decode steps at batch 1, cache sized to 2048.  The bf16
-    variant rounds the same weights to bf16 and runs fewer steps to bound the CPU oracle's time."""
+@pytest.fixture(scope="module")
+def tinyllama_f32(L, oracle):
+    """Benchmark configuration 1 at full size (f32 weights N(0,0.02) from seed 0, gains 1.0) on both sides."""
     from lumen_b200 import synth
     cfg = dict(synth.TINYLLAMA)
-    params = make_params(L, cfg, 0, std=0.02, round_bf16=(wdt == "bf16"))
+    params = make_params(L, cfg, 0, std=0.02)
+    model = L.LlamaModel(cfg_obj(L, cfg, "f32"))
+    model.load_state(params)
+    return cfg, params, model, oracle.Llama(cfg, params, "f32")
+
+
+def _teacher_forced(L, model, ref, ids, prompt, caches=None, rcaches=None):
+    caches = caches or model.init_kv_caches(1)
+    rcaches = rcaches or ref.init_kv_caches(1)
+    got, want = [], []
+    with L.no_grad():
+        if prompt:
+            got.append(model.forward(ids[:, :prompt], caches)[:, -1:])
+            want.append(ref.forward(ids[:, :prompt], rcaches)[:, -1:])
+        for t in range(prompt, ids.shape[1]):
+            got.append(model.forward(ids[:, t:t + 1], caches))
+            want.append(ref.forward(ids[:, t:t + 1], rcaches))
+    return np.concatenate(got, axis=1), np.concatenate(want, axis=1)
+
+
+def test_tinyllama_config1_teacher_forced_f32(L, tinyllama_f32):
+    """Benchmark configuration 1 at full size: TinyLlama-1.1B shape, 32 prompt ids from seed 1 and 128
+    teacher-forced decode steps at batch 1, cache sized to 2048."""
+    from lumen_b200 import synth
+    cfg, _, model, ref = tinyllama_f32
+    prompt, steps = 32, 128
     ids = synth.token_ids(1, prompt + steps, cfg["vocab_size"])[None, :]
-    got, _, _ = _gpu_run(L, cfg, params, ids, prompt, wdt)
+    got, want = _teacher_forced(L, model, ref, ids, prompt)
+    errs = [rel_err(got[0, t], want[0, t]) for t in range(got.shape[1])]
+    print(f"\nconfig1 f32: max rel err over {len(errs)} steps = {max(errs):.3e}")
+    assert max(errs) < TOL_F32
+    assert np.array_equal(got[0].argmax(-1), want[0].argmax(-1))
+
+
+def test_tinyllama_last_positions_of_the_cache(L, tinyllama_f32):
+    """The same full-size model decoding across positions 2030..2047, the end of the static cache and of the
+    RoPE table: both sides start from the same random cache contents of length 2030.  Covers the merge of the
+    context splits and the f32 rotation angles at the far end of the table, then the overflow status."""
+    cfg, _, model, ref = tinyllama_f32
+    rng = np.random.default_rng(2030)
+    start, max_seq = 2030, cfg["max_seq_len"]
+    caches, rcaches = model.init_kv_caches(1), ref.init_kv_caches(1)
+    shape = (1, cfg["num_key_value_heads"], max_seq, cfg["hidden_size"] // cfg["num_attention_heads"])
+    for c, rc in zip(caches, rcaches):
+        k = np.zeros(shape, np.float32)
+        v = np.zeros(shape, np.float32)
+        k[:, :, :start] = 0.5 * rng.standard_normal((shape[0], shape[1], start, shape[3]), dtype=np.float32)
+        v[:, :, :start] = 0.5 * rng.standard_normal((shape[0], shape[1], start, shape[3]), dtype=np.float32)
+        c.write(k, v, start)
+        rc.k[...] = k
+        rc.v[...] = v
+        rc.len = start
+    ids = rng.integers(0, cfg["vocab_size"], size=(1, max_seq - start)).astype(np.float32)
+    got, want = _teacher_forced(L, model, ref, ids, 0, caches, rcaches)
+    errs = [rel_err(got[0, t], want[0, t]) for t in range(got.shape[1])]
+    print(f"\nconfig1 f32, positions {start}..{max_seq - 1}: max rel err = {max(errs):.3e}")
+    assert max(errs) < TOL_F32
+    assert np.array_equal(got[0].argmax(-1), want[0].argmax(-1))
+    assert all(c.len == max_seq for c in caches)
+    with L.no_grad(), pytest.raises(L.LumenError) as e:  # self_attention.rs:144-149
+        model.forward(ids[:, :1], caches)
+    assert e.value.code == L._lib.ERR_KV_OVERFLOW
+
+
+def test_tinyllama_config1_teacher_forced_bf16(L, oracle):
+    """Configuration 1 with the same weights rounded to bf16 (f32 accumulation); fewer steps to bound the CPU
+    oracle's time."""
+    from lumen_b200 import synth
+    cfg = dict(synth.TINYLLAMA)
+    prompt, steps = 32, 24
+    params = make_params(L, cfg, 0, std=0.02, round_bf16=True)
+    ids = synth.token_ids(1, prompt + steps, cfg["vocab_size"])[None, :]
+    got, _, _ = _gpu_run(L, cfg, params, ids, prompt, "bf16")
     want, _ = _oracle_run(oracle, cfg, params, ids, prompt, "f32")
-    tol = TOL_BF16 if wdt == "bf16" else TOL_F32
     errs = [rel_err(got[0, t], want[0, t]) for t in range(prompt - 1, prompt + steps)]
-    print(f"\nconfig1 {wdt}: max rel err over {len(errs)} steps = {max(errs):.3e}")
-    assert max(errs) < tol
+    print(f"\nconfig1 bf16: max rel err over {len(errs)} steps = {max(errs):.3e}")
+    assert max(errs) < TOL_BF16
     assert np.array_equal(got[0, prompt - 1:].argmax(-1), want[0, prompt - 1:].argmax(-1))
+
+
+def _tiled_params(L, cfg, seed, random_norms=False):
+    """bf16-representable N(0, 0.02) weights for the multi-billion-parameter geometries: every matrix repeats one
+    seeded block of draws whose length is not a multiple of any row length, so no two rows are equal (drawing
+    1.6 G values one by one would take minutes)."""
+    from lumen_b200 import synth
+    params = dict(synth.iter_params_tiled(L.LlamaConfig(**cfg), seed, std=0.02, round_bf16=True, block=(1 << 22) + 7))
+    if random_norms:
+        rng = np.random.default_rng(seed + 1000)
+        for k in params:
+            if params[k].ndim == 1:
+                params[k] = (1.0 + 0.1 * rng.standard_normal(params[k].shape)).astype(np.float32)
+    return params
+
+
+def test_llama2_7b_geometry_two_layers(L, oracle):
+    """Benchmark configuration 4's geometry (hidden 4096, 32 heads of 128 without grouping, intermediate 11008,
+    vocabulary 32000, bf16 weights with f32 accumulation) cut to two layers: a 64-token prompt (tensor-core GEMMs
+    and prefill attention) and 8 teacher-forced decode steps through the persistent kernel."""
+    from lumen_b200 import synth
+    cfg = dict(synth.LLAMA2_7B, num_hidden_layers=2, max_seq_len=128)
+    params = _tiled_params(L, cfg, 4)
+    prompt, steps = 64, 8
+    ids = synth.token_ids(4, prompt + steps, cfg["vocab_size"])[None, :]
+    got, _, _ = _gpu_run(L, cfg, params, ids, prompt, "bf16")
+    want, _ = _oracle_run(oracle, cfg, params, ids, prompt, "f32")
+    errs = [rel_err(got[0, t], want[0, t]) for t in range(prompt + steps)]
+    print(f"\nLlama-2-7B geometry, 2 layers, bf16: max rel err over {len(errs)} positions = {max(errs):.3e}")
+    assert max(errs) < TOL_BF16
+    assert np.array_equal(got[0].argmax(-1), want[0].argmax(-1))
+
+
+def test_qwen3_8b_geometry_two_layers_batched(L, oracle):
+    """Benchmark configuration 5's geometry (32 query heads and 8 KV heads of 128, per-head q/k RMSNorm, intermediate
+    12288, vocabulary 151936, theta 1e6, bf16 weights) cut to two layers and two sequences: a 128-token prefix in two
+    slices of 64 (the second into a partly filled cache), then 4 batched decode steps."""
+    from lumen_b200 import synth
+    cfg = dict(synth.QWEN3_8B, num_hidden_layers=2, max_seq_len=192)
+    params = _tiled_params(L, cfg, 5, random_norms=True)
+    b, prefix, steps = 2, 128, 4
+    ids = synth.token_ids(5, b * (prefix + steps), cfg["vocab_size"]).reshape(b, prefix + steps)
+    model = L.LlamaModel(cfg_obj(L, cfg, "bf16"))
+    model.load_state(params)
+    caches = model.init_kv_caches(b)
+    ref = oracle.Llama(cfg, params, "f32")
+    rcaches = ref.init_kv_caches(b)
+    worst = 0.0
+    with L.no_grad():
+        for lo, hi in [(0, 64), (64, 128)] + [(t, t + 1) for t in range(prefix, prefix + steps)]:
+            got = model.forward(ids[:, lo:hi], caches)
+            want = ref.forward(ids[:, lo:hi], rcaches)
+            for t in range(hi - lo):
+                worst = max(worst, rel_err(got[:, t], want[:, t]))
+            assert np.array_equal(got.argmax(-1), want.argmax(-1)), (lo, hi)
+    print(f"\nQwen3-8B geometry, 2 layers, batch {b}, bf16: max rel err = {worst:.3e}")
+    assert worst < TOL_BF16
+    assert all(c.len == prefix + steps for c in caches)

@@ -33,6 +33,9 @@ CHILD = textwrap.dedent("""
             print("NO_ERROR")
         except L.LumenError as e:
             print("ERROR", e.code, round(time.perf_counter() - t0, 2))
+        # the step that gave up appended nothing: the cache length the host reports is the device's (4), not
+        # the value the host had bumped when it enqueued the step
+        print("LEN_AFTER", caches[0].len, caches[-1].len)
         # the context is still usable: operators and a fresh prefill run and give finite results
         a = L.Tensor.from_array_no_grad(np.ones((3, 16), np.float32))
         w = L.Tensor.from_array_no_grad(np.ones((5, 16), np.float32))
@@ -52,5 +55,6 @@ def test_unanswered_wait_times_out_and_context_survives():
     code_s, secs = lines["ERROR"].split()
     assert int(code_s) == 9            # LUMEN_ERR_TIMEOUT
     assert float(secs) < 5.0           # a bounded wait, not a hang
+    assert lines["LEN_AFTER"].split() == ["4", "4"]
     assert float(lines["MATMUL"]) == 3 * 5 * 16.0
     assert lines["PREFILL_FINITE"] == "True"
