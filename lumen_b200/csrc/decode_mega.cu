@@ -14,7 +14,7 @@
 // (weight-free) attention.
 //
 // Consumers: a phase's input vector is staged in shared memory (multiplied by the RMSNorm gains on the
-// way in; the 1/rms factor is a scalar and is applied to the row sums).  Tiles go round-robin to the six
+// way in; the 1/rms factor is a scalar and is applied to the row sums).  Tiles go round-robin to the seven
 // consumer warps and a warp works through a tile alone: per 16-byte step a lane reads one vector of x and the
 // matching vector of four weight rows with conflict-free 128-bit shared loads, the four row sums are folded
 // across lanes by one butterfly and land in the row's column (one per segment) of a table of partial sums.
@@ -43,10 +43,11 @@
 namespace lumen {
 namespace {
 
-// 6 consumer warps + 1 producer warp: at most two warps per SM sub-partition, so every thread may use up to 255
-// registers (with three warps on a sub-partition the limit is 168).  The kernel must not spill: the L1 is squeezed by
-// ~220 KB of shared memory, and a spill reload inside the tile loop is a round trip through L2.
-constexpr int kConsumers = 192;
+// 7 consumer warps + 1 producer warp: two warps per SM sub-partition, so every thread may use up to 255 registers
+// (with three warps on a sub-partition the limit is 168) and each scheduler has a second warp to cover the
+// shared-memory and shuffle latencies of the first.  The kernel must not spill: the L1 is squeezed by ~220 KB of
+// shared memory, and a spill reload inside the tile loop is a round trip through L2.
+constexpr int kConsumers = 224;
 constexpr int kConsumerWarps = kConsumers / 32;
 constexpr int kThreads = kConsumers + 32;   // + producer warp
 constexpr int kMaxRowsPerTile = 8;
