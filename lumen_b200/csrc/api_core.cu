@@ -166,6 +166,10 @@ int lumen_ctx_destroy(lumen_ctx *ctx) {
     if (!ctx) return LUMEN_ERR_INVALID;
     cudaSetDevice(ctx->device);
     if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+    if (ctx->d_exchange) {
+        tp_unshare_buffer(ctx, ctx->x_peers);
+        cudaFree(ctx->d_exchange);
+    }
     if (ctx->nccl_comm) {
         tp_shutdown(ctx);
     }

@@ -89,8 +89,6 @@ struct lumen_llama {
     size_t tmaps_capacity = 0;
     const void *mega_key = nullptr;  // first cache's k pointer the layer table was built for
     unsigned long long *d_trace = nullptr;  // phase timestamps of the last persistent step (LUMEN_DECODE_TRACE=1)
-    uint2 *d_exchange = nullptr;            // tagged activation exchange buffers of the persistent kernel
-    void *x_peers[8] = {nullptr};           // every rank's d_exchange as seen from this device (tensor parallelism)
 };
 
 namespace {
@@ -369,24 +367,35 @@ int run_mega(lumen_llama *m, lumen_kv_cache **caches) {
     p.x_slot_words = (p.H + 1) & ~1;
     // A rank computes its slice of the vocabulary; the slices are gathered after the kernel.
     p.ids = w.ids;
-    p.logits = tp ? w.logits_local + (size_t)ctx->tp_rank * m->vocab_l : w.logits;
+    p.logits = w.logits;  // (tensor parallel: set below, once the exchange buffer exists)
     // Exchange buffers of tagged words (zeroed once; tag 0 is never used).  With tensor parallelism the x
     // buffers at their start are written by every rank: the ranks map each other's buffer once.
     const size_t words = decode_mega_exchange_words(p);
-    if (!m->d_exchange) {
-        LUMEN_CUDA(ctx, cudaMalloc(&m->d_exchange, words * sizeof(uint2)));
-        LUMEN_CUDA(ctx, cudaMemsetAsync(m->d_exchange, 0, words * sizeof(uint2), ctx->stream));
-        LUMEN_TRY(tp_share_buffer(ctx, m->d_exchange, m->x_peers));  // (collective: also orders the memsets)
-    }
+    LUMEN_TRY(ensure_exchange(ctx, words * sizeof(uint2)));
     const unsigned int per_launch = decode_mega_epochs_per_launch(p.L);
     if (ctx->mega_epoch > 0xf0000000u - per_launch) {  // tags are about to wrap: start over from clean buffers
-        LUMEN_CUDA(ctx, cudaMemsetAsync(m->d_exchange, 0, words * sizeof(uint2), ctx->stream));
+        LUMEN_CUDA(ctx, cudaMemsetAsync(ctx->d_exchange, 0, ctx->exchange_bytes, ctx->stream));
         // no rank may write into a peer's buffer before that peer has cleared it
         if (tp) LUMEN_TRY(tp_allreduce_sum(ctx, w.logits_local, 1, ctx->stream));
         ctx->mega_epoch = 1;
     }
-    p.xT = m->d_exchange;
-    for (int r = 0; r < ctx->tp_size; ++r) p.x_peer[r] = static_cast<uint2 *>(m->x_peers[r]);
+    p.xT = static_cast<uint2 *>(ctx->d_exchange);
+    for (int r = 0; r < ctx->tp_size; ++r) p.x_peer[r] = static_cast<uint2 *>(ctx->x_peers[r]);
+    p.xrT = nullptr;
+    if (tp) {
+        // LUMEN_MEGA_TP_REDUCE=1: the row owners sum the ranks' partial values and publish the sums (two hops, one
+        // staging pass) instead of every CTA summing all slots while it stages x (one hop, several passes).  Measured on
+        // TinyLlama f32 the single hop wins at 2 ranks (1353 against 1272 tok/s) and at 4 (1604 against 1405).
+        static const int reduce_env = [] { const char *e = getenv("LUMEN_MEGA_TP_REDUCE"); return e ? atoi(e) : 0; }();
+        const size_t lo = decode_mega_logits_offset_words(p);
+        if (reduce_env == 1) p.xrT = p.xT + lo - 2 * (size_t)p.x_slot_words;
+        for (int r = 0; r < ctx->tp_size; ++r) {
+            p.logits_peer[r] = reinterpret_cast<float *>(static_cast<uint2 *>(ctx->x_peers[r]) + lo);
+            p.flag_peer[r] = reinterpret_cast<unsigned int *>(p.logits_peer[r] + ((p.vocab + 1) & ~1));
+        }
+        p.logits = p.logits_peer[ctx->tp_rank];
+        p.done_count = reinterpret_cast<unsigned int *>(ctx->d_mega_sync);
+    }
     p.qkvT = p.xT + decode_mega_x_words(p);
     p.actT = p.qkvT + ((p.qkv_rows + 1) & ~1);
     p.partT = p.actT + ((p.I + 1) & ~1);
@@ -401,12 +410,8 @@ int run_mega(lumen_llama *m, lumen_kv_cache **caches) {
     p.trace = m->d_trace;
     LUMEN_TRY(launch_decode_mega(ctx, p, ctx->stream));
     ctx->mega_epoch += per_launch;
-    if (tp) {
-        // Gather the vocabulary slices.  This collective also keeps the ranks within one token of each other,
-        // which the alternating x buffers rely on.
-        LUMEN_TRY(tp_allgather(ctx, p.logits, w.logits_local, m->vocab_l, ctx->stream));
-        LUMEN_CUDA(ctx, cudaMemcpyAsync(w.logits, w.logits_local, m->V * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
-    }
+    if (tp)  // the kernel gathered the vocabulary slices of all ranks into this rank's exchange buffer
+        LUMEN_CUDA(ctx, cudaMemcpyAsync(w.logits, p.logits, m->V * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
     return LUMEN_OK;
 }
 
@@ -756,7 +761,6 @@ int lumen_llama_free(lumen_llama *m) {
     if (m->d_sched_count) cudaFree(m->d_sched_count);
     if (m->d_tmaps) cudaFree(m->d_tmaps);
     if (m->d_trace) cudaFree(m->d_trace);
-    if (m->d_exchange) cudaFree(m->d_exchange);
     if (m->ws.base) cudaFree(m->ws.base);
     if (m->ws.h_ids) cudaFreeHost(m->ws.h_ids);
     if (m->ws.h_logits) cudaFreeHost(m->ws.h_logits);

@@ -47,6 +47,12 @@ struct lumen_ctx {
     // advance the device copy of the cache lengths although the host mirror was bumped at enqueue time, so
     // every cache re-reads its device length the first time it is used after an abort (kv_resync_len).
     unsigned int abort_gen = 0;
+    // Tagged activation exchange buffers of the persistent kernel.  They belong to the context, not to a model: with
+    // tensor parallelism every rank maps every other rank's buffer (CUDA IPC), and a mapping outlives the model that
+    // asked for it.  Models on one context run one after the other on its stream and share the buffer.
+    void *d_exchange = nullptr;
+    size_t exchange_bytes = 0;
+    void *x_peers[8] = {nullptr};  // every rank's d_exchange as seen from this device (x_peers[tp_rank] == d_exchange)
 };
 
 struct lumen_storage {
@@ -135,6 +141,11 @@ int tp_allgather(lumen_ctx *ctx, const float *send, float *recv, size_t n_per_ra
 // Maps a cudaMalloc'ed buffer of every rank into every rank (CUDA IPC, handles traded over NCCL):
 // peers_out[r] = rank r's buffer as seen from this device.
 int tp_share_buffer(lumen_ctx *ctx, void *local, void **peers_out);
+// Closes the mappings of the other ranks' buffers made by tp_share_buffer.
+void tp_unshare_buffer(lumen_ctx *ctx, void **peers);
+// The context's exchange buffer with room for `bytes` (zeroed when (re)allocated; collective when tp_size > 1: every
+// rank must ask for the same size at the same point).
+int ensure_exchange(lumen_ctx *ctx, size_t bytes);
 
 // Stream-ordered allocation from the device's default memory pool.
 int dev_alloc(lumen_ctx *ctx, size_t bytes, void **out);

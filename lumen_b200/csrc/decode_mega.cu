@@ -554,6 +554,39 @@ __device__ __forceinline__ void poll_x_sum_pass(const MegaParams &p, Shared &sh,
     }
 }
 
+// Two-step form of the same exchange: the threads that own rows [r0, r1) of the residual stream wait for the ranks'
+// partial values of their row, add them in rank order and publish the sum in `dst` (this GPU's xrT buffer); then
+// every thread stages dst like a single-GPU vector.
+__device__ __forceinline__ bool reduce_then_poll_x(const MegaParams &p, Shared &sh, const uint2 *src, uint2 *dst, int n, uint32_t tag,
+                                                   float *xs, int tid, int &bk, int r0, int r1, const StageOpts o) {
+    if (tid < r1 - r0) {
+        const int row = r0 + tid;
+        const long long t0 = clock64();
+        int spins = 0;
+        float sum = 0.f;
+        bool done = false, alive = true;
+        while (!done && alive) {
+            done = true;
+            unsigned long long w[8];
+#pragma unroll
+            for (int r = 0; r < 8; ++r)
+                if (r < p.tp_size) asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(w[r]) : "l"(src + (size_t)r * p.x_slot_words + row) : "memory");
+            sum = 0.f;
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                if (r < p.tp_size) {
+                    done = done && (uint32_t)(w[r] >> 32) == tag;
+                    const float v = __uint_as_float((uint32_t)w[r]);
+                    sum = r == 0 ? v : __fadd_rn(sum, v);
+                }
+            }
+            if (!done) alive = poll_continue(p, sh.abort, spins, t0, 355, row);
+        }
+        if (done) st_tagged(dst + row, sum, tag);
+    }
+    return poll_vector(p, sh, dst, n, tag, xs, tid, bk, 356, o);
+}
+
 __device__ __forceinline__ bool poll_x_sum(const MegaParams &p, Shared &sh, const uint2 *src, int n, uint32_t tag, float *xs, int tid,
                                            int &bk, const StageOpts o) {
     const int npairs = n / 2, sw = p.x_slot_words;
@@ -812,7 +845,10 @@ __device__ __forceinline__ bool gemv_phase(const MegaParams &p, Shared &sh, cons
     // the residual stream also refresh the residual value this thread carries for the o_proj / down epilogues.
     const bool has_rows = ti.r0 != ti.r1;
     const bool stages_x = g.kind == PH_QKV || g.kind == PH_GATEUP;
-    if (!has_rows && !stages_x) return true;
+    // (with the two-step tensor-parallel exchange every CTA owes the others the sums of its rows of the residual
+    // stream, also in the lm_head phase, where it may have no rows of the matrix)
+    const bool owes_sums = p.xrT != nullptr && g.kind == PH_LMHEAD;
+    if (!has_rows && !stages_x && !owes_sums) return true;
     const int njl = ti.njl;  // steps of a lane through a whole row
 
     // ---- prologue: the input vector, in shared memory ---------------------------------------------------
@@ -847,6 +883,9 @@ __device__ __forceinline__ bool gemv_phase(const MegaParams &p, Shared &sh, cons
         if (g.kind == PH_O) ok = poll_attention(p, sh, tag, xs, tid, bk);
         else if (g.kind == PH_DOWN) ok = poll_vector(p, sh, p.actT, g.K, tag, xs, tid, bk, 330 + g.kind);
         else if (p.tp_size == 1) ok = poll_vector(p, sh, xsrc, g.K, tag, xs, tid, bk, 330 + g.kind, so);
+        else if (p.xrT)
+            ok = reduce_then_poll_x(p, sh, xsrc, p.xrT + (size_t)(g.kind == PH_GATEUP ? 0 : 1) * p.x_slot_words, g.K, tag, xs, tid, bk, (int)r0h,
+                                    (int)r1h, so);
         else ok = poll_x_sum(p, sh, xsrc, g.K, tag, xs, tid, bk, so);
         if (!ok) return false;
         if (p.trace && cta == 0 && tid == 0) p.trace[4 * (5 * p.L + 1) + 1 + ph] = globaltimer_ns();
@@ -860,9 +899,9 @@ __device__ __forceinline__ bool gemv_phase(const MegaParams &p, Shared &sh, cons
         for (int w = 0; w < kConsumerWarps; ++w) tot += sh.red[w];
         inv = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(tot, (float)g.K), p.eps)));
     }
-    if (stages_x) {
+    if (stages_x || owes_sums) {
         // keep this thread's row of the residual stream (all ranks' partial sums added, before the gains)
-        if (tid < r1h - r0h) xres = sh.xraw[tid];
+        if (stages_x && tid < r1h - r0h) xres = sh.xraw[tid];
         if (!has_rows) {
             trace_stamp(p, cta, tid, 3 * ph + 1);
             trace_stamp(p, cta, tid, 3 * ph + 2);
@@ -966,7 +1005,14 @@ __device__ __forceinline__ bool gemv_phase(const MegaParams &p, Shared &sh, cons
                     st_tagged(p.actT + row, __fmul_rn(__fmul_rn(tot, sig), up), tag);
                     break;
                 }
-                default: p.logits[row] = tot; break;
+                default:  // lm_head: this rank's rows of the logits, stored into every rank's gathered copy
+                    if (p.tp_size == 1) {
+                        p.logits[row] = tot;
+                    } else {
+                        const size_t grow = (size_t)p.tp_rank * p.V + row;
+                        for (int r = 0; r < p.tp_size; ++r) p.logits_peer[r][grow] = tot;
+                    }
+                    break;
             }
         }
         if (cend < chunks) consumer_bar();  // the table is rewritten by the next block
@@ -1095,6 +1141,31 @@ __device__ __forceinline__ void consumer_loop(const MegaParams &p, Shared &sh, i
         }
     }
     trace_stamp(p, cta, tid, 3 * nphases);
+    if (p.tp_size > 1) {
+        // The logits rows of this CTA are on their way to every rank.  The last CTA of the rank to get here tells
+        // every rank that this rank's slice is complete, and waits (bounded) for the slices of the others.
+        consumer_bar();
+        if (tid == 0) {
+            __threadfence_system();
+            if (atomicAdd(p.done_count, 1u) == (unsigned)nctas - 1u) {
+                atomicExch(p.done_count, 0u);
+                const uint32_t tag = phase_tag(p, nphases - 1);
+                for (int r = 0; r < p.tp_size; ++r)
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.flag_peer[r] + p.tp_rank), "r"(tag) : "memory");
+                const long long t0 = clock64();
+                for (int r = 0; r < p.tp_size; ++r) {
+                    uint32_t v;
+                    do {
+                        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.flag_peer[p.tp_rank] + r) : "memory");
+                    } while (v != tag && !*sh.abort && clock64() - t0 < kWaitCycles);
+                    if (v != tag) {
+                        raise_abort(p, sh.abort, 360, r);
+                        break;
+                    }
+                }
+            }
+        }
+    }
     // c.len = new_len (self_attention.rs:179) for every layer's cache.  Every CTA read `past` before it did
     // anything else, and the next launch starts only after this one has ended.
     for (int l = tid; cta == 0 && l < p.L; l += kConsumers) *p.layers[l].d_len = past + 1;
@@ -1288,8 +1359,15 @@ unsigned int decode_mega_epochs_per_launch(int layers) { return 5u * (unsigned)l
 
 size_t decode_mega_x_words(const MegaParams &p) { return 2 * (size_t)p.tp_size * (size_t)((p.H + 1) & ~1); }
 
+size_t decode_mega_logits_offset_words(const MegaParams &p) {
+    size_t w = decode_mega_x_words(p) + p.qkv_rows + p.I + (size_t)p.Hq * kMaxSplit * (2 + p.D) + 8;
+    if (p.tp_size > 1) w = ((w + 1) & ~(size_t)1) + 2 * (size_t)((p.H + 1) & ~1);  // + the summed residual stream (xrT)
+    return (w + 15) & ~(size_t)15;  // 128-byte aligned
+}
 size_t decode_mega_exchange_words(const MegaParams &p) {
-    return decode_mega_x_words(p) + p.qkv_rows + p.I + (size_t)p.Hq * kMaxSplit * (2 + p.D) + 8;
+    // tensor parallel: + the gathered logits (f32 [vocab]) and one flag word per rank
+    const size_t extra = p.tp_size > 1 ? ((size_t)p.vocab + 1) / 2 + 8 : 0;
+    return decode_mega_logits_offset_words(p) + extra;
 }
 
 int decode_mega_supported(const MegaParams &p, char *why, size_t why_len) {

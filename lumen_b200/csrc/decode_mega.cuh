@@ -30,7 +30,13 @@ struct MegaParams {
     const float *cos_t, *sin_t;
     float eps, scale;
     const float *ids;         // [1] f32 token id
-    float *logits;            // [V]
+    float *logits;            // [V] (one GPU), or this rank's view of its own gathered logits [vocab] (tensor parallel)
+    // Tensor parallelism: a rank stores its slice of the logits straight into every rank's gathered-logits area
+    // (plain peer stores over NVLink), then raises its flag (the launch's tag) in every rank; the last CTA of a rank
+    // to finish waits for all flags, so that when the kernel ends the rank's logits are complete.
+    float *logits_peer[8];    // rank r's gathered logits [vocab] as seen from this device
+    unsigned int *flag_peer[8];  // rank r's flag array [tp_size] as seen from this device
+    unsigned int *done_count; // CTAs of this rank that have stored their logits rows (reset by the last one)
     // Activations that cross CTAs are exchanged as 8-byte {f32 bits, epoch tag} words: a consumer polls the
     // words it needs until they carry the tag of the producing phase, so the data is its own signal and no
     // grid barrier is needed.  tag(phase) = epoch_base + phase + 1; epoch_base grows with every launch.
@@ -44,6 +50,11 @@ struct MegaParams {
     uint2 *x_peer[8];         // x_peer[r] = rank r's xT as seen from this device (x_peer[tp_rank] == xT)
     int x_slot_words;         // words per slot: H rounded up to even
     uint2 *xT;                // [2][tp_size][x_slot_words]  residual stream (o_proj -> buffer 0, down -> buffer 1)
+    // Tensor parallelism with many ranks: summing tp_size slots while staging x takes tp_size times the loads of a
+    // plain staging pass, in several passes (each a round trip through L2).  Instead the CTA that owns a row of the
+    // residual stream sums the ranks' partial values of that row (in rank order, so every rank gets the same bits) and
+    // publishes the sum in xrT; everybody then stages xrT in one pass like on a single GPU.
+    uint2 *xrT;               // [2][x_slot_words] the summed residual stream (null: sum while staging)
     uint2 *qkvT;              // [qkv_rows]   q | k | v projections
     uint2 *actT;              // [I]          SiLU(gate) * up
     uint2 *partT;             // [Hq, nsplit, 2 + D]: {max}, {sum}, ctx[D] of every attention work item
@@ -88,7 +99,8 @@ struct MegaParams {
 size_t decode_mega_smem_bytes(int stages, int stage_bytes, int head_dim, int kmax);
 int decode_mega_supported(const MegaParams &p, char *why, size_t why_len);
 unsigned int decode_mega_epochs_per_launch(int layers);
-size_t decode_mega_exchange_words(const MegaParams &p);  // uint2 words of the four exchange buffers
+size_t decode_mega_exchange_words(const MegaParams &p);  // uint2 words of the four exchange buffers (+ gathered logits and flags)
+size_t decode_mega_logits_offset_words(const MegaParams &p);  // where the gathered logits start (then tp_size flags)
 size_t decode_mega_x_words(const MegaParams &p);         // of which the x buffers, at the start (needs tp_size, H)
 int decode_mega_max_splits();
 constexpr int kMegaTileTrace = 512;

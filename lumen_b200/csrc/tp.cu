@@ -129,6 +129,34 @@ int tp_share_buffer(lumen_ctx *ctx, void *local, void **peers_out) {
     return LUMEN_OK;
 }
 
+void tp_unshare_buffer(lumen_ctx *ctx, void **peers) {
+    for (int r = 0; r < ctx->tp_size && r < 8; ++r) {
+        if (r != ctx->tp_rank && peers[r]) cudaIpcCloseMemHandle(peers[r]);
+        peers[r] = nullptr;
+    }
+}
+
+int ensure_exchange(lumen_ctx *ctx, size_t bytes) {
+    if (ctx->d_exchange && ctx->exchange_bytes >= bytes) return LUMEN_OK;
+    LUMEN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (ctx->d_exchange) {
+        // every rank drops its mappings of the old buffers before anybody frees one
+        tp_unshare_buffer(ctx, ctx->x_peers);
+        if (ctx->tp_size > 1) {
+            LUMEN_TRY(tp_allreduce_sum(ctx, static_cast<float *>(ctx->d_exchange), 1, ctx->stream));
+            LUMEN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        }
+        cudaFree(ctx->d_exchange);
+        ctx->d_exchange = nullptr;
+        ctx->exchange_bytes = 0;
+    }
+    LUMEN_CUDA(ctx, cudaMalloc(&ctx->d_exchange, bytes));
+    ctx->exchange_bytes = bytes;
+    LUMEN_CUDA(ctx, cudaMemsetAsync(ctx->d_exchange, 0, bytes, ctx->stream));
+    ctx->mega_epoch = 1;  // clean buffers: the tags start over
+    return tp_share_buffer(ctx, ctx->d_exchange, ctx->x_peers);  // (collective: also orders the memsets)
+}
+
 }  // namespace lumen
 
 extern "C" int lumen_nccl_unique_id(void *id_out_128_bytes) {
