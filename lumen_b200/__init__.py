@@ -13,12 +13,13 @@ from .layers import (Embedding, KVCache, KVCacheInner, Linear, LlamaKVCache, Mod
                      RotaryEmbedding, SelfAttention, SiLU, attention_decode, fused_softmax, gemv, gemv_kn_static, matmul, reshape, sample_top_p)
 from .llama import LlamaConfig, LlamaModel  # noqa: E402
 from .loader import load_llama_weights  # noqa: E402
+from .tokenizer import LlamaTokenizer  # noqa: E402
 from .tensor import (Context, Tensor, default_context, is_inference_mode, is_no_grad, no_grad,  # noqa: E402
                      set_inference_mode)
 
 __all__ = [
     "BF16", "F32", "LumenError", "Context", "Tensor", "default_context", "is_inference_mode", "is_no_grad",
     "no_grad", "set_inference_mode", "Module", "Linear", "Embedding", "RMSNorm", "SiLU", "RotaryEmbedding",
-    "SelfAttention", "KVCache", "KVCacheInner", "LlamaKVCache", "LlamaConfig", "LlamaModel", "load_llama_weights", "matmul", "reshape",
+    "SelfAttention", "KVCache", "KVCacheInner", "LlamaKVCache", "LlamaConfig", "LlamaModel", "LlamaTokenizer", "load_llama_weights", "matmul", "reshape",
     "fused_softmax", "gemv", "gemv_kn_static", "attention_decode", "sample_top_p",
 ]

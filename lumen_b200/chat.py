@@ -7,6 +7,8 @@ runs on the device (`LlamaModel.forward_sample`), so one token id per step cross
 The caller supplies what the tokenizer did there: `encode_first(user_msg)` and `encode_next(user_msg)` return
 the token ids of a first-turn / follow-up prompt (main.rs:36-58 build the texts), and an optional
 `text_stop(generated_ids)` reproduces the check for role markers in the decoded text (main.rs:301-305).
+`LlamaTokenizer` (tokenizer.py, the mirror of src/tokenizer.rs) provides `encode` / `decode` / `eos_id` / `eot_id`
+for these over a tokenizer.json.
 """
 from __future__ import annotations
 
