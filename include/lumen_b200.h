@@ -257,6 +257,18 @@ size_t lumen_llama_weight_bytes(const lumen_llama *m);
  * Copies up to `capacity` stamps of the last step to the host. */
 int lumen_llama_decode_trace(lumen_llama *m, uint64_t *out, size_t capacity, size_t *n_out);
 
+/* ---- measurement helpers (no counterpart in the reference) ----------------------------------
+ * A kernel timed as a kernel: `iters` calls of lumen_gemv (src/ops/matmul.rs:42-69) / lumen_attention_decode
+ * (self_attention.rs:141-297) enqueued back to back from compiled code between two CUDA events on the context's
+ * stream, after three untimed calls, rotating over the n_w weight matrices / n_caches caches given (a working set
+ * larger than L2).  *us_per_call_out = microseconds per call.  Every attention call appends one row to the cache
+ * it uses, so each cache needs room for (iters + 3) / n_caches + 1 more rows.  Synchronises. */
+int lumen_gemv_repeat(lumen_ctx *ctx, const float *x_dev, const void *const *w_devs, size_t n_w, lumen_dtype w_dtype, int layout_kn,
+                      size_t k, size_t n, float *y_dev, size_t iters, float *us_per_call_out);
+int lumen_attention_decode_repeat(lumen_ctx *ctx, const float *q_dev, const float *k_new_dev, const float *v_new_dev, size_t n_head,
+                                  lumen_kv_cache *const *caches, size_t n_caches, lumen_rope *rope, float *out_dev, size_t iters,
+                                  float *us_per_call_out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -75,6 +75,8 @@ PROTOTYPES = {
     "lumen_embedding": (_I, [_P, _P, _P, _PP]),
     "lumen_fused_softmax": (_I, [_P, _P, _F, _I, _PP]),
     "lumen_gemv": (_I, [_P, _FP, _P, _I, _I, _SZ, _SZ, _FP]),
+    "lumen_gemv_repeat": (_I, [_P, _FP, _P, _SZ, _I, _I, _SZ, _SZ, _FP, _SZ, C.POINTER(C.c_float)]),
+    "lumen_attention_decode_repeat": (_I, [_P, _FP, _FP, _FP, _SZ, _P, _SZ, _P, _FP, _SZ, C.POINTER(C.c_float)]),
     "lumen_gemv_kn_static": (_I, [_P, _FP, _P, _I, _SZ, _SZ, _FP]),
     "lumen_rope_new": (_I, [_P, _SZ, _SZ, _F, _PP]),
     "lumen_rope_forward": (_I, [_P, _P, _SZ, _PP]),

@@ -166,6 +166,7 @@ int lumen_ctx_destroy(lumen_ctx *ctx) {
     if (!ctx) return LUMEN_ERR_INVALID;
     cudaSetDevice(ctx->device);
     if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+    if (ctx->sampler_ws) cudaFree(ctx->sampler_ws);
     if (ctx->d_exchange) {
         tp_unshare_buffer(ctx, ctx->x_peers);
         cudaFree(ctx->d_exchange);

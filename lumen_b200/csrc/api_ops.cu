@@ -70,6 +70,35 @@ int require_f32(lumen_ctx *ctx, const lumen_tensor *t, const char *what) {
 
 }  // namespace
 
+namespace {
+template <typename F>
+int timed_repeat(lumen_ctx *ctx, size_t iters, float *us_per_call_out, F call) {
+    if (iters == 0) return set_error(ctx, LUMEN_ERR_INVALID, "repeat: iters == 0");
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    LUMEN_CUDA(ctx, cudaEventCreate(&e0));
+    cudaError_t ce = cudaEventCreate(&e1);
+    if (ce != cudaSuccess) {
+        cudaEventDestroy(e0);
+        return cuda_fail(ctx, ce, "cudaEventCreate");
+    }
+    int rc = LUMEN_OK;
+    size_t i = 0;
+    for (; i < 3 && rc == LUMEN_OK; ++i) rc = call(i);
+    if (rc == LUMEN_OK) rc = check_device_status(ctx);
+    if (rc == LUMEN_OK && cudaEventRecord(e0, ctx->stream) != cudaSuccess) rc = LUMEN_ERR_CUDA;
+    for (size_t j = 0; j < iters && rc == LUMEN_OK; ++j) rc = call(i + j);
+    if (rc == LUMEN_OK && cudaEventRecord(e1, ctx->stream) != cudaSuccess) rc = LUMEN_ERR_CUDA;
+    if (rc == LUMEN_OK) rc = check_device_status(ctx);
+    float ms = 0.f;
+    if (rc == LUMEN_OK && cudaEventElapsedTime(&ms, e0, e1) != cudaSuccess) rc = LUMEN_ERR_CUDA;
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    if (rc == LUMEN_OK) *us_per_call_out = ms * 1000.0f / (float)iters;
+    return rc;
+}
+}  // namespace
+
+
 extern "C" {
 
 int lumen_matmul(lumen_ctx *ctx, const lumen_tensor *a, const lumen_tensor *w, lumen_tensor **out) {
@@ -186,6 +215,27 @@ int lumen_gemv(lumen_ctx *ctx, const float *x_dev, const void *w_dev, lumen_dtyp
     int rc = launch_gemv_kn(ctx, x_dev, w_dev, w_dtype, y_dev, k, n, static_cast<float *>(scratch), ctx->stream);
     int rc2 = dev_free(ctx, scratch);
     return rc != LUMEN_OK ? rc : rc2;
+}
+
+// ---- measurement helpers: a kernel timed as a kernel ----------------------------------------------------------
+// `iters` calls enqueued back to back from compiled code between two CUDA events on the context's stream (after
+// three untimed calls), rotating over the given operands so that a working set larger than L2 can be used: the
+// per-call cost of an interpreted host and its launch rate stay out of the number.
+int lumen_gemv_repeat(lumen_ctx *ctx, const float *x_dev, const void *const *w_devs, size_t n_w, lumen_dtype w_dtype, int layout_kn,
+                      size_t k, size_t n, float *y_dev, size_t iters, float *us_per_call_out) {
+    if (!ctx || !w_devs || n_w == 0 || !us_per_call_out) return set_error(ctx, LUMEN_ERR_INVALID, "gemv_repeat: null argument");
+    return timed_repeat(ctx, iters, us_per_call_out,
+                        [&](size_t i) { return lumen_gemv(ctx, x_dev, w_devs[i % n_w], w_dtype, layout_kn, k, n, y_dev); });
+}
+
+int lumen_attention_decode_repeat(lumen_ctx *ctx, const float *q_dev, const float *k_new_dev, const float *v_new_dev, size_t n_head,
+                                  lumen_kv_cache *const *caches, size_t n_caches, lumen_rope *rope, float *out_dev, size_t iters,
+                                  float *us_per_call_out) {
+    if (!ctx || !caches || n_caches == 0 || !us_per_call_out)
+        return set_error(ctx, LUMEN_ERR_INVALID, "attention_decode_repeat: null argument");
+    return timed_repeat(ctx, iters, us_per_call_out, [&](size_t i) {
+        return lumen_attention_decode(ctx, q_dev, k_new_dev, v_new_dev, n_head, caches[i % n_caches], rope, 1, out_dev);
+    });
 }
 
 int lumen_sample_top_p(lumen_ctx *ctx, const float *logits_dev, size_t vocab, const lumen_sample_params *sp, int32_t *token_out) {

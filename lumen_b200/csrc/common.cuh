@@ -53,6 +53,8 @@ struct lumen_ctx {
     void *d_exchange = nullptr;
     size_t exchange_bytes = 0;
     void *x_peers[8] = {nullptr};  // every rank's d_exchange as seen from this device (x_peers[tp_rank] == d_exchange)
+    void *sampler_ws = nullptr;    // scratch of the device sampler (probabilities, indices, sort space)
+    size_t sampler_ws_bytes = 0;
 };
 
 struct lumen_storage {
@@ -179,7 +181,8 @@ int launch_gemv_gate_up(lumen_ctx *ctx, const float *x, const void *w_gate, cons
 
 // y[n] = sum_k w[k, n] * x[k]; w is [K,N] row-major.  Uses `scratch` (>= gemv_kn_scratch_bytes) for
 // split-K partial sums.
-size_t gemv_kn_scratch_bytes(size_t K, size_t N, int num_sms);
+size_t gemv_kn_scratch_bytes(size_t K, size_t N, int num_sms);                           // either weight type
+size_t gemv_kn_scratch_bytes_for(size_t K, size_t N, lumen_dtype wdt, int num_sms);    // the plan of this weight type
 int launch_gemv_kn(lumen_ctx *ctx, const float *x, const void *w, lumen_dtype wdt, float *y, size_t K, size_t N,
                    float *scratch, cudaStream_t s);
 

@@ -89,7 +89,8 @@ struct MegaParams {
     const int *sched_count;
     int sched_stride;
     const CUtensorMap *tmaps;  // device array of the tensor maps the schedule refers to (64-byte aligned)
-    int l2_ahead;  // copies the producer's L2 prefetch runs ahead of the copy it issues (0 = off)
+    int l2_ahead;  // tiles the producer hands to the L2, one at a time, while the ring is full (0 = off)
+    int pf_pace, pf_grace;  // cycles between two such prefetches, and how long the ring must have been full before the first
     // bit 0: stream no weight tiles (measures the exchange + prologue chain alone; results are wrong)
     // bit 2: wait for the weight tiles but skip the arithmetic on them
     // bit 3: the first phase publishes nothing: every wait on it gives up after its limit (time-out test)

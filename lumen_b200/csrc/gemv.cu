@@ -481,6 +481,10 @@ int launch_gemv_gate_up(lumen_ctx *ctx, const float *x, const void *w_gate, cons
 #undef GU
 }
 
+size_t gemv_kn_scratch_bytes_for(size_t K, size_t N, lumen_dtype wdt, int num_sms) {
+    return (size_t)plan_kn(K, N, wdt == LUMEN_F32 ? 4 : 8, num_sms).splits * N * sizeof(float);
+}
+
 size_t gemv_kn_scratch_bytes(size_t K, size_t N, int num_sms) {
     KnPlan p4 = plan_kn(K, N, 4, num_sms), p8 = plan_kn(K, N, 8, num_sms);
     return (size_t)std::max(p4.splits, p8.splits) * N * sizeof(float);

@@ -30,7 +30,7 @@ int lumen_gemv_kn_static(lumen_ctx *ctx, const float *x_dev, const void *w_dev, 
     if (w_dtype != LUMEN_F32 && w_dtype != LUMEN_BF16)
         return set_error(ctx, LUMEN_ERR_DTYPE, "gemv_kn_static: dtype %d", (int)w_dtype);
     if (k == 0 || n == 0) return LUMEN_OK;
-    const size_t need = gemv_kn_scratch_bytes(k, n, ctx->num_sms);
+    const size_t need = gemv_kn_scratch_bytes_for(k, n, w_dtype, ctx->num_sms);  // what this launch will write
     if (need > kStaticScratchBytes)
         return set_error(ctx, LUMEN_ERR_UNSUPPORTED,
                          "gemv_kn_static: k=%zu n=%zu needs %zu bytes of partial sums, the fixed scratch holds %zu; "

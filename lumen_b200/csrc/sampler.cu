@@ -91,8 +91,8 @@ sample_prep_kernel(const float *__restrict__ logits, int n, float temperature, f
 // running sum reaches a threshold (main.rs:113-121 and :126-134).  With a flat distribution the rounding of
 // that sequential sum decides the index, so the order of the additions is kept: the warp stages 1024 values at a
 // time in shared memory (dividing by `scale` on the way: 1 for the cumulative probability, the nucleus mass
-// for the inverse-CDF walk) and lane 0 adds them in order, eight per test of the threshold; the block of
-// eight that crosses is then walked value by value.  Returns the first index < n whose running sum is >=
+// for the inverse-CDF walk) and lane 0 adds them in order, 32 per test of the threshold; the block of
+// 32 that crosses is then walked value by value.  Returns the first index < n whose running sum is >=
 // threshold (n if none) and that running sum (the total if none).
 __device__ __forceinline__ int first_reaching(const float *__restrict__ vals, int n, float scale, float threshold, float *buf,
                                               float *sum_out) {
@@ -105,12 +105,22 @@ __device__ __forceinline__ int first_reaching(const float *__restrict__ vals, in
         for (int i = lane; i < kChunk; i += 32) buf[i] = i < m ? __fdiv_rn(vals[c0 + i], scale) : 0.f;  // zeros change no sum
         __syncwarp();
         if (lane == 0) {
-            for (int i = 0; i < m; i += 8) {
+            // 32 values per test of the threshold: eight 128-bit loads, then the dependent chain of 32 additions
+            // (the chain is what the walk costs; nothing else is on it)
+            for (int i = 0; i < m; i += 32) {
+                float4 v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = *reinterpret_cast<const float4 *>(buf + i + 4 * j);
                 float t = run;
 #pragma unroll
-                for (int j = 0; j < 8; ++j) t = __fadd_rn(t, buf[i + j]);
-                if (t >= threshold) {  // the sums only grow: the crossing is inside these eight
-                    for (int j = 0; j < 8 && i + j < m; ++j) {
+                for (int j = 0; j < 8; ++j) {
+                    t = __fadd_rn(t, v[j].x);
+                    t = __fadd_rn(t, v[j].y);
+                    t = __fadd_rn(t, v[j].z);
+                    t = __fadd_rn(t, v[j].w);
+                }
+                if (t >= threshold) {  // the sums only grow: the crossing is inside these 32 (or in their zero padding)
+                    for (int j = 0; j < 32 && i + j < m; ++j) {
                         run = __fadd_rn(run, buf[i + j]);
                         if (run >= threshold) {
                             found = c0 + i + j;
@@ -118,7 +128,7 @@ __device__ __forceinline__ int first_reaching(const float *__restrict__ vals, in
                         }
                     }
                     if (found != n) break;
-                    continue;  // (only the zero padding pushed t over the line: cannot happen, t == run then)
+                    continue;  // (only zero padding was left: t == run, and that was below the threshold)
                 }
                 run = t;
             }
@@ -133,7 +143,7 @@ __device__ __forceinline__ int first_reaching(const float *__restrict__ vals, in
 __global__ void __launch_bounds__(32)
 sample_pick_kernel(const float *__restrict__ sorted_p, const int *__restrict__ sorted_i, int n, float top_p, float r,
                    int *__restrict__ token_out) {
-    __shared__ float buf[1024];
+    __shared__ __align__(16) float buf[1024];
     const float target = fmaxf(fminf(fmaxf(top_p, 0.f), 1.f), 1e-6f);
     float cumulative;
     const int at = first_reaching(sorted_p, n, 1.0f, target, buf, &cumulative);  // main.rs:113-121
@@ -157,8 +167,16 @@ int launch_sample_top_p(lumen_ctx *ctx, const float *logits_dev, size_t vocab, f
                                               (int *)nullptr, n, 0, 32, s);
     const size_t nf = ((size_t)n + 63) & ~(size_t)63;
     const size_t bytes = 4 * nf * 4 + kMaxRecent * sizeof(int) + ((sort_bytes + 255) & ~(size_t)255);
-    void *ws = nullptr;
-    LUMEN_TRY(dev_alloc(ctx, bytes, &ws));
+    // scratch kept with the context (grown when a larger vocabulary comes along): no allocation per token
+    if (ctx->sampler_ws_bytes < bytes) {
+        LUMEN_CUDA(ctx, cudaStreamSynchronize(s));
+        if (ctx->sampler_ws) cudaFree(ctx->sampler_ws);
+        ctx->sampler_ws = nullptr;
+        ctx->sampler_ws_bytes = 0;
+        LUMEN_CUDA(ctx, cudaMalloc(&ctx->sampler_ws, bytes));
+        ctx->sampler_ws_bytes = bytes;
+    }
+    void *ws = ctx->sampler_ws;
     float *probs = static_cast<float *>(ws), *probs_sorted = probs + nf;
     int *idx = reinterpret_cast<int *>(probs_sorted + nf), *idx_sorted = idx + nf;
     int *recent_dev = idx_sorted + nf;
@@ -179,8 +197,7 @@ int launch_sample_top_p(lumen_ctx *ctx, const float *logits_dev, size_t vocab, f
         if (e == cudaSuccess) ctx->launches += 1;
     }
     if (e != cudaSuccess) rc = cuda_fail(ctx, e, "sample_top_p");
-    int rc2 = dev_free(ctx, ws);
-    return rc != LUMEN_OK ? rc : rc2;
+    return rc;
 }
 
 }  // namespace lumen

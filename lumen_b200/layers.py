@@ -36,6 +36,24 @@ def fused_softmax(x: Tensor, scale: float, is_causal: bool) -> Tensor:
     return _unary_out(x.ctx, x.ctx._lib.lumen_fused_softmax, x.h, C.c_float(scale), int(is_causal))
 
 
+def gemv_repeat(ctx, x_ptr: int, w_ptrs, w_dtype: int, layout_kn: bool, k: int, n: int, y_ptr: int, iters: int) -> float:
+    """`lumen_gemv_repeat`: microseconds per call of `iters` back-to-back products rotating over the matrices `w_ptrs`."""
+    arr = (C.c_void_p * len(w_ptrs))(*w_ptrs)
+    us = C.c_float()
+    ctx.check(ctx._lib.lumen_gemv_repeat(ctx.h, x_ptr, arr, len(w_ptrs), w_dtype, int(layout_kn), k, n, y_ptr, iters, C.byref(us)))
+    return float(us.value)
+
+
+def attention_decode_repeat(ctx, q_ptr: int, k_ptr: int, v_ptr: int, n_head: int, caches, rope, out_ptr: int, iters: int) -> float:
+    """`lumen_attention_decode_repeat`: microseconds per call of `iters` back-to-back decode-attention steps rotating over
+    `caches` (each call appends one row to the cache it uses)."""
+    arr = (C.c_void_p * len(caches))(*[c.h for c in caches])
+    us = C.c_float()
+    ctx.check(ctx._lib.lumen_attention_decode_repeat(ctx.h, q_ptr, k_ptr, v_ptr, n_head, arr, len(caches), rope.h if rope else None,
+                                                     out_ptr, iters, C.byref(us)))
+    return float(us.value)
+
+
 def gemv(ctx: Context, x_ptr: int, w_ptr: int, w_dtype: int, layout_kn: bool, k: int, n: int, y_ptr: int) -> None:
     """Vector-matrix product on raw device pointers (`lumen_gemv`)."""
     ctx.check(ctx._lib.lumen_gemv(ctx.h, x_ptr, w_ptr, w_dtype, int(layout_kn), k, n, y_ptr))
