@@ -525,11 +525,13 @@ __device__ __forceinline__ bool poll_vector(const MegaParams &p, Shared &sh, con
     const int npairs = n / 2;
     const int per_thread = (npairs + kConsumers - 1) / kConsumers;
     float ss = 0.f;
-    // At most 8 loads per thread and pass: more words in flight would push the kernel's hot loops into spilling,
-    // and with the L1 squeezed by the shared-memory ring a spill costs a round trip through L2.
+    // At most 13 loads per thread and pass (a 5632-element vector in one pass of 224 threads): more words in flight
+    // would push the kernel's hot loops into spilling, and with the L1 squeezed by the shared-memory ring a spill
+    // costs a round trip through L2.  Every pass is such a round trip too.
     if (per_thread <= 4) poll_vector_pass<4>(p, sh, s4, npairs, 0, tag, xs, tid, site, o, ss);
+    else if (per_thread <= 8) poll_vector_pass<8>(p, sh, s4, npairs, 0, tag, xs, tid, site, o, ss);
     else
-        for (int base = 0; base < npairs; base += kConsumers * 8) poll_vector_pass<8>(p, sh, s4, npairs, base, tag, xs, tid, site, o, ss);
+        for (int base = 0; base < npairs; base += kConsumers * 13) poll_vector_pass<13>(p, sh, s4, npairs, base, tag, xs, tid, site, o, ss);
     publish_ss(sh, ss, tid);
     return consumer_bar_ok(sh.abort, sh.decision, tid, bk);
 }
