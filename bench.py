@@ -14,12 +14,15 @@ Own arm (default): prints ONE JSON line with
   roofline  algorithmic HBM bytes per step / measured step time against the measured copy bandwidth
   cpu_baseline  the CPU restatement of the reference's Rayon path, timed on this box's host cores on a
             bounded sample of the same workload (rank 0, N = 1 only)
-With N > 1 (launched by torchrun, one rank per GPU) the model is tensor-parallel over the N GPUs with an
-NCCL allreduce after the o/down projections ("scaling": "strong": the work per token is fixed).
+With N > 1 (launched by torchrun, one rank per GPU) the model is tensor-parallel over the N GPUs; the all-reduce after
+the o/down projections and the gather of the logits happen inside the persistent kernel over NVLink peer stores
+("scaling": "strong": the work per token is fixed).  Rank 0 also compares its logits with the CPU restatement
+(`parity_vs_cpu`) and the line carries a short Llama-2-7B run (`extra`).  The timed region is exactly --steps steps; it
+is repeated (fresh prompt and warm-up each time) and the median repetition is reported, with the spread beside it.
 
 Reference arm (--impl reference): the reference is Rust and cannot be built on this box, so the arm
 times its CPU restatement (oracle/) with all host threads on the same workload and prints the same
-line with "impl": "reference".
+line with "impl": "reference".  It loads neither the package nor the CUDA library.
 """
 from __future__ import annotations
 
@@ -100,9 +103,9 @@ class ClockSampler(threading.Thread):
 
 
 # dram__bytes_read + dram__bytes_write of one persistent-kernel launch divided by its algorithmic bytes,
-# from an ncu capture of a 4-layer truncation of the same model (973.6 MB / 967.3 MB); its summary is committed
-# with the other profiler summaries.
-MEGA_TRAFFIC_RATIO = 1.0065
+# from an ncu capture of a 4-layer truncation of the same model (973.0 MB / 967.3 MB; f32 weights, one GPU); its
+# summary is committed with the other profiler summaries.
+MEGA_TRAFFIC_RATIO = 1.0058
 
 
 WORKLOADS = {  # name -> (synth config, label, default weight dtype)
