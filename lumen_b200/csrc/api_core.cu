@@ -171,6 +171,10 @@ int lumen_ctx_destroy(lumen_ctx *ctx) {
         tp_unshare_buffer(ctx, ctx->x_peers);
         cudaFree(ctx->d_exchange);
     }
+    if (ctx->d_tp_sum) {
+        tp_unshare_buffer(ctx, ctx->tp_sum_peers);
+        cudaFree(ctx->d_tp_sum);
+    }
     if (ctx->nccl_comm) {
         tp_shutdown(ctx);
     }

@@ -101,8 +101,9 @@ void drop_graphs(lumen_llama *m) {
 
 int ensure_workspace(lumen_llama *m, size_t M) {
     Workspace &w = m->ws;
-    if (M <= w.M) return LUMEN_OK;
     lumen_ctx *ctx = m->ctx;
+    LUMEN_TRY(ensure_tp_sum(ctx));  // (every rank passes here at the same points; no-op after the first time)
+    if (M <= w.M) return LUMEN_OK;
     LUMEN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     drop_graphs(m);
     if (w.base) cudaFree(w.base);
@@ -195,6 +196,7 @@ int enqueue_forward(lumen_llama *m, const StepPlan &p, lumen_kv_cache **caches, 
     const float *res_x = (!tp || ctx->tp_rank == 0) ? w.x : nullptr;
 
     LUMEN_TRY(launch_embedding(ctx, w.ids, m->embed, wdt, w.x, M, m->V, H, s));
+    bool nx_ready = false;  // w.nx already holds Norm(x) of the block about to run
     for (size_t l = 0; l < m->L; ++l) {
         const LayerW &lw = m->layers[l];
         lumen_kv_cache *c = caches[l];
@@ -205,7 +207,7 @@ int enqueue_forward(lumen_llama *m, const StepPlan &p, lumen_kv_cache **caches, 
             g.norm_w = lw.norm1; g.norm_eps = eps;
             LUMEN_TRY(launch_gemv_nk(ctx, g, s));
         } else {
-            LUMEN_TRY(launch_rmsnorm(ctx, w.x, lw.norm1, eps, w.nx, M, H, s));
+            if (!nx_ready) LUMEN_TRY(launch_rmsnorm(ctx, w.x, lw.norm1, eps, w.nx, M, H, s));
             LUMEN_TRY(launch_gemm_nk(ctx, w.nx, lw.wqkv, wdt, w.qkv, M, H, qkvd, nullptr, s));
         }
         if (p.decode) {
@@ -230,19 +232,26 @@ int enqueue_forward(lumen_llama *m, const StepPlan &p, lumen_kv_cache **caches, 
             LUMEN_TRY(launch_attn_prefill(ctx, a, s));
             LUMEN_TRY(launch_bump_len(ctx, c->d_len, (int)p.S, s));
         }
-        LUMEN_TRY(matmul_dispatch(ctx, w.att, lw.wo, wdt, w.x, M, m->qd_l, H, res_x, s));
-        if (tp) LUMEN_TRY(tp_allreduce_sum(ctx, w.x, M * H, s));
+        // With tensor parallelism the sum over the ranks follows the product in the same call, and (outside the
+        // vector path, which folds the norm into its next product) leaves Norm(x) for the next product in w.nx.
+        TpSumArgs sum_o;
+        sum_o.out = w.x;
+        if (tp && !vec) { sum_o.norm_w = lw.norm2; sum_o.normed = w.nx; sum_o.eps = eps; }
+        LUMEN_TRY(matmul_dispatch(ctx, w.att, lw.wo, wdt, w.x, M, m->qd_l, H, res_x, s, tp ? &sum_o : nullptr));
         // out = h + MLP(Norm(h))                                       llama.rs:113-115, :59-65
         if (vec) {
             LUMEN_TRY(launch_gemv_gate_up(ctx, w.x, lw.wgate, lw.wup, wdt, w.act, (int)M, H, m->inter_l, lw.norm2, eps, s));
         } else {
-            LUMEN_TRY(launch_rmsnorm(ctx, w.x, lw.norm2, eps, w.nx, M, H, s));
+            if (!tp) LUMEN_TRY(launch_rmsnorm(ctx, w.x, lw.norm2, eps, w.nx, M, H, s));
             LUMEN_TRY(launch_gemm_nk(ctx, w.nx, lw.wgate, wdt, w.gate, M, H, m->inter_l, nullptr, s));
             LUMEN_TRY(launch_gemm_nk(ctx, w.nx, lw.wup, wdt, w.up, M, H, m->inter_l, nullptr, s));
             LUMEN_TRY(launch_silu_mul(ctx, w.gate, w.up, w.act, M * m->inter_l, s));
         }
-        LUMEN_TRY(matmul_dispatch(ctx, w.act, lw.wdown, wdt, w.x, M, m->inter_l, H, res_x, s));
-        if (tp) LUMEN_TRY(tp_allreduce_sum(ctx, w.x, M * H, s));
+        TpSumArgs sum_d;
+        sum_d.out = w.x;
+        nx_ready = tp && !vec && l + 1 < m->L;
+        if (nx_ready) { sum_d.norm_w = m->layers[l + 1].norm1; sum_d.normed = w.nx; sum_d.eps = eps; }
+        LUMEN_TRY(matmul_dispatch(ctx, w.act, lw.wdown, wdt, w.x, M, m->inter_l, H, res_x, s, tp ? &sum_d : nullptr));
     }
     // Final norm + lm_head                                             llama.rs:202-205
     const float *xin = w.x;
@@ -383,12 +392,14 @@ int run_mega(lumen_llama *m, lumen_kv_cache **caches) {
     for (int r = 0; r < ctx->tp_size; ++r) p.x_peer[r] = static_cast<uint2 *>(ctx->x_peers[r]);
     p.xrT = nullptr;
     if (tp) {
-        // LUMEN_MEGA_TP_REDUCE=1: the row owners sum the ranks' partial values and publish the sums (two hops, one
-        // staging pass) instead of every CTA summing all slots while it stages x (one hop, several passes).  Measured on
-        // TinyLlama f32 the single hop wins at 2 ranks (1353 against 1272 tok/s) and at 4 (1604 against 1405).
-        static const int reduce_env = [] { const char *e = getenv("LUMEN_MEGA_TP_REDUCE"); return e ? atoi(e) : 0; }();
+        // Two forms of the exchange.  One hop: every CTA sums the ranks' slots while it stages x (tp_size times the loads
+        // of a plain staging pass, in several passes of what fits the registers).  Two hops: the row owners sum the
+        // ranks' partial values and publish the sums, then everybody stages them in one pass.  Measured on TinyLlama f32
+        // the single hop wins at 2 ranks (1353 against 1272 tok/s) and at 4 (1604 against 1405); at 8 ranks the single hop
+        // needs 5 passes (10 at hidden size 4096), so the two hops are the default there.  LUMEN_MEGA_TP_REDUCE=0/1 forces one.
+        static const int reduce_env = [] { const char *e = getenv("LUMEN_MEGA_TP_REDUCE"); return e ? atoi(e) : -1; }();
         const size_t lo = decode_mega_logits_offset_words(p);
-        if (reduce_env == 1) p.xrT = p.xT + lo - 2 * (size_t)p.x_slot_words;
+        if (reduce_env == 1 || (reduce_env < 0 && ctx->tp_size >= 8)) p.xrT = p.xT + lo - 2 * (size_t)p.x_slot_words;
         for (int r = 0; r < ctx->tp_size; ++r) {
             p.logits_peer[r] = reinterpret_cast<float *>(static_cast<uint2 *>(ctx->x_peers[r]) + lo);
             p.flag_peer[r] = reinterpret_cast<unsigned int *>(p.logits_peer[r] + ((p.vocab + 1) & ~1));

@@ -27,17 +27,28 @@ namespace lumen {
 
 // Shared by the op-level API and the model: y[M,N] = a[M,K] . w[N,K]^T (+ residual).
 int matmul_dispatch(lumen_ctx *ctx, const float *a, const void *w, lumen_dtype wdt, float *y, size_t M, size_t K,
-                    size_t N, const float *residual, cudaStream_t s) {
+                    size_t N, const float *residual, cudaStream_t s, const TpSumArgs *tp) {
     if (M == 0 || N == 0) return LUMEN_OK;
+    if (ctx->tp_size == 1) tp = nullptr;
+    const bool fused = tp && tp_sum_usable(ctx, M, N);
     // The streaming vector-matrix kernel takes up to 8 rows over f32 weights; over bf16 weights only a single row
     // (from two rows on, the tensor-core kernel with split K is faster).
     const size_t vec_rows = (wdt == LUMEN_BF16 && gemm_tc_usable(wdt, M, K, N, w)) ? 1 : 8;
     if (M <= vec_rows && M * K * 4 <= 200 * 1024) {
         GemvArgs g;
         g.x = a; g.w = w; g.wdt = wdt; g.y = y; g.M = (int)M; g.K = K; g.N = N; g.ldy = N; g.residual = residual;
-        return launch_gemv_nk(ctx, g, s);
+        LUMEN_TRY(launch_gemv_nk(ctx, g, s));
+        if (fused) return launch_tp_sum(ctx, y, 1, nullptr, M, N, *tp, s);
+    } else {
+        LUMEN_TRY(launch_gemm_nk(ctx, a, w, wdt, y, M, K, N, residual, s, fused ? tp : nullptr));
+        if (fused) return LUMEN_OK;
     }
-    return launch_gemm_nk(ctx, a, w, wdt, y, M, K, N, residual, s);
+    if (tp) {
+        // too many rows for the fused exchange (long prefill slices are bandwidth-bound): NCCL, then the norm
+        LUMEN_TRY(tp_allreduce_sum(ctx, y, M * N, s));
+        if (tp->norm_w) LUMEN_TRY(launch_rmsnorm(ctx, y, tp->norm_w, tp->eps, tp->normed, M, N, s));
+    }
+    return LUMEN_OK;
 }
 
 int rope_tables_host(size_t dim, size_t max_seq, float theta, std::vector<float> &cos_h, std::vector<float> &sin_h) {

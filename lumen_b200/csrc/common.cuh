@@ -53,6 +53,10 @@ struct lumen_ctx {
     void *d_exchange = nullptr;
     size_t exchange_bytes = 0;
     void *x_peers[8] = {nullptr};  // every rank's d_exchange as seen from this device (x_peers[tp_rank] == d_exchange)
+    // Buffer of the fused tensor-parallel row sum (control words, flags, two sets of per-rank slots), mapped by every
+    // rank like d_exchange; fixed size, allocated once per context.
+    void *d_tp_sum = nullptr;
+    void *tp_sum_peers[8] = {nullptr};
     void *sampler_ws = nullptr;    // scratch of the device sampler (probabilities, indices, sort space)
     size_t sampler_ws_bytes = 0;
 };
@@ -129,9 +133,21 @@ int check_device_status(lumen_ctx *ctx);
 // (one 4-byte synchronising read, only on the first use after the abort).
 int kv_resync_len(lumen_kv_cache *c);
 
-// y[M,N] = a[M,K] . w[N,K]^T (+ residual): vector-matrix kernel for M <= 8, tiled GEMM otherwise.
+// What a row-parallel product (o_proj, down) of a tensor-parallel rank asks for behind its own sum: the sum over the
+// ranks, in rank order, of (product + residual), written to `out` on every rank, and optionally the RMSNorm of the summed
+// rows (gains norm_w) written to `normed`.
+struct TpSumArgs {
+    float *out = nullptr;
+    const float *norm_w = nullptr;
+    float *normed = nullptr;
+    float eps = 0.f;
+};
+
+// y[M,N] = a[M,K] . w[N,K]^T (+ residual): vector-matrix kernel for M <= 8, tiled GEMM otherwise.  With `tp` (and
+// tp_size > 1) y becomes the sum over the ranks: fused into one kernel over peer memory when the rows fit its buffer
+// (launch_tp_sum), through NCCL otherwise; tp->out must be y.
 int matmul_dispatch(lumen_ctx *ctx, const float *a, const void *w, lumen_dtype wdt, float *y, size_t M, size_t K,
-                    size_t N, const float *residual, cudaStream_t s);
+                    size_t N, const float *residual, cudaStream_t s, const TpSumArgs *tp = nullptr);
 // cos/sin tables [max_seq, dim/2] computed on the host in f32.
 int rope_tables_host(size_t dim, size_t max_seq, float theta, std::vector<float> &cos_h, std::vector<float> &sin_h);
 
@@ -148,6 +164,17 @@ void tp_unshare_buffer(lumen_ctx *ctx, void **peers);
 // The context's exchange buffer with room for `bytes` (zeroed when (re)allocated; collective when tp_size > 1: every
 // rank must ask for the same size at the same point).
 int ensure_exchange(lumen_ctx *ctx, size_t bytes);
+
+// Fused tensor-parallel row sum (tp_sum.cu).  Limits of one call: kTpSumMaxRows rows, kTpSumSlotFloats elements.
+constexpr size_t kTpSumMaxRows = 512;
+constexpr size_t kTpSumSlotFloats = (size_t)512 * 1024;  // 2 MB per rank and buffer
+constexpr size_t kTpSumCtlBytes = 256;
+// Allocates and shares the buffer (collective, synchronises; not inside a stream capture).  No-op when tp_size == 1.
+int ensure_tp_sum(lumen_ctx *ctx);
+bool tp_sum_usable(const lumen_ctx *ctx, size_t rows, size_t dim);
+// out = sum over ranks of (sum over `splits` slices of part (+ residual)); see TpSumArgs.  part and residual may alias out.
+int launch_tp_sum(lumen_ctx *ctx, const float *part, int splits, const float *residual, size_t rows, size_t dim,
+                  const TpSumArgs &a, cudaStream_t s);
 
 // Stream-ordered allocation from the device's default memory pool.
 int dev_alloc(lumen_ctx *ctx, size_t bytes, void **out);
@@ -187,14 +214,15 @@ int launch_gemv_kn(lumen_ctx *ctx, const float *x, const void *w, lumen_dtype wd
                    float *scratch, cudaStream_t s);
 
 // C[M,N] = A[M,K] . W[N,K]^T, any M (f32 SIMT tiles; bf16 weights are widened on load).
+// With `tp` usable for M x N the product leaves its result to launch_tp_sum (split-K slices included).
 int launch_gemm_nk(lumen_ctx *ctx, const float *a, const void *w, lumen_dtype wdt, float *c, size_t M, size_t K,
-                   size_t N, const float *residual, cudaStream_t s);
+                   size_t N, const float *residual, cudaStream_t s, const TpSumArgs *tp = nullptr);
 // The same product on the tensor cores (tcgen05, accumulator in tensor memory) for M >= 2 (callers keep up to 8
 // rows over f32 weights on the streaming kernel);
 // launch_gemm_nk takes this path whenever gemm_tc_usable says so.
 bool gemm_tc_usable(lumen_dtype wdt, size_t M, size_t K, size_t N, const void *w);
 int launch_gemm_tc(lumen_ctx *ctx, const float *a, const void *w, lumen_dtype wdt, float *c, size_t M, size_t K, size_t N,
-                   const float *residual, cudaStream_t s);
+                   const float *residual, cudaStream_t s, const TpSumArgs *tp = nullptr);
 
 int launch_rmsnorm(lumen_ctx *ctx, const float *x, const float *w, float eps, float *out, size_t rows, size_t dim,
                    cudaStream_t s);

@@ -617,9 +617,9 @@ __device__ __forceinline__ bool poll_x_sum(const MegaParams &p, Shared &sh, cons
     const int npairs = n / 2, sw = p.x_slot_words;
     float ss = 0.f;
     if (p.tp_size == 2)
-        for (int base = 0; base < npairs; base += kConsumers * 4) poll_x_sum_pass<2, 4>(p, sh, src, sw, npairs, base, tag, xs, tid, o, ss);
+        for (int base = 0; base < npairs; base += kConsumers * 5) poll_x_sum_pass<2, 5>(p, sh, src, sw, npairs, base, tag, xs, tid, o, ss);
     else if (p.tp_size == 4)
-        for (int base = 0; base < npairs; base += kConsumers * 2) poll_x_sum_pass<4, 2>(p, sh, src, sw, npairs, base, tag, xs, tid, o, ss);
+        for (int base = 0; base < npairs; base += kConsumers * 3) poll_x_sum_pass<4, 3>(p, sh, src, sw, npairs, base, tag, xs, tid, o, ss);
     else  // 8 ranks (the launcher admits 1, 2, 4 and 8)
         for (int base = 0; base < npairs; base += kConsumers) poll_x_sum_pass<8, 1>(p, sh, src, sw, npairs, base, tag, xs, tid, o, ss);
     publish_ss(sh, ss, tid);

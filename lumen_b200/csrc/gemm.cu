@@ -76,9 +76,9 @@ gemm_nk_kernel(const float *__restrict__ a, const WT *__restrict__ w, float *__r
 }  // namespace
 
 int launch_gemm_nk(lumen_ctx *ctx, const float *a, const void *w, lumen_dtype wdt, float *c, size_t M, size_t K,
-                   size_t N, const float *residual, cudaStream_t s) {
+                   size_t N, const float *residual, cudaStream_t s, const TpSumArgs *tp) {
     if (M == 0 || N == 0) return LUMEN_OK;
-    if (gemm_tc_usable(wdt, M, K, N, w)) return launch_gemm_tc(ctx, a, w, wdt, c, M, K, N, residual, s);
+    if (gemm_tc_usable(wdt, M, K, N, w)) return launch_gemm_tc(ctx, a, w, wdt, c, M, K, N, residual, s, tp);
     dim3 grid((unsigned)((N + BN - 1) / BN), (unsigned)((M + BM - 1) / BM));
     if (wdt == LUMEN_F32)
         gemm_nk_kernel<float><<<grid, kThreads, 0, s>>>(a, static_cast<const float *>(w), c, M, K, N, residual);
@@ -86,6 +86,7 @@ int launch_gemm_nk(lumen_ctx *ctx, const float *a, const void *w, lumen_dtype wd
         gemm_nk_kernel<__nv_bfloat16>
             <<<grid, kThreads, 0, s>>>(a, static_cast<const __nv_bfloat16 *>(w), c, M, K, N, residual);
     LUMEN_LAUNCHED(ctx);
+    if (tp) return launch_tp_sum(ctx, c, 1, nullptr, M, N, *tp, s);
     return LUMEN_OK;
 }
 

@@ -249,7 +249,7 @@ int pick_bn(size_t M, size_t N, int num_sms) {
 // wdt == LUMEN_F32: the weights are split into hi + lo bf16 matrices on the fly as well (one streaming pass
 // over W per call) and three of the four cross products are accumulated.
 int launch_gemm_tc(lumen_ctx *ctx, const float *a, const void *w, lumen_dtype wdt, float *c, size_t M, size_t K, size_t N,
-                   const float *residual, cudaStream_t s) {
+                   const float *residual, cudaStream_t s, const TpSumArgs *tp) {
     const bool wsplit = wdt == LUMEN_F32;
     void *split = nullptr;
     const size_t na = M * K, nap = (na + 7) & ~(size_t)7, nw = wsplit ? N * K : 0, nwp = (nw + 7) & ~(size_t)7;
@@ -309,7 +309,11 @@ int launch_gemm_tc(lumen_ctx *ctx, const float *a, const void *w, lumen_dtype wd
         else if (wsplit) rc = bn == 128 ? LUMEN_TC(2, 2, 128, false) : bn == 64 ? LUMEN_TC(2, 2, 64, false) : LUMEN_TC(2, 2, 32, false);
         else rc = bn == 128 ? LUMEN_TC(2, 1, 128, false) : bn == 64 ? LUMEN_TC(2, 1, 64, false) : LUMEN_TC(2, 1, 32, false);
 #undef LUMEN_TC
-        if (rc == LUMEN_OK && splits > 1) {
+        if (rc == LUMEN_OK && tp) {
+            // the sum over the ranks takes the slices (or the finished product) from here
+            rc = splits > 1 ? launch_tp_sum(ctx, static_cast<const float *>(partial), splits, residual, M, N, *tp, s)
+                            : launch_tp_sum(ctx, c, 1, nullptr, M, N, *tp, s);
+        } else if (rc == LUMEN_OK && splits > 1) {
             const size_t mn = M * N;
             splitk_reduce_kernel<<<(unsigned)((mn + 255) / 256), 256, 0, s>>>(static_cast<const float *>(partial), residual, c, mn, splits);
             cudaError_t e = cudaGetLastError();

@@ -30,25 +30,26 @@ def main():
     for n, w in params.items():
         model.set_param(n, w)  # every rank passes the full tensor; the library keeps its slice
     prompt, steps = int(os.environ.get("TP_TEST_PROMPT", "7")), 6
-    ids = synth.token_ids(5, prompt + steps, cfg["vocab_size"])
-    caches = model.init_kv_caches(1)
+    batch = int(os.environ.get("TP_TEST_BATCH", "1"))
+    ids = synth.token_ids(5, batch * (prompt + steps), cfg["vocab_size"]).reshape(batch, prompt + steps)
+    caches = model.init_kv_caches(batch)
     got = []
     with L.no_grad():
-        got.append(model.forward(ids[None, :prompt], caches)[0, -1])
+        got.append(model.forward(ids[:, :prompt], caches)[:, -1])
         for t in range(steps):
-            got.append(model.forward(ids[None, prompt + t:prompt + t + 1], caches)[0, 0])
-    got = np.stack(got)
+            got.append(model.forward(ids[:, prompt + t:prompt + t + 1], caches)[:, 0])
+    got = np.stack(got)  # [1 + steps, batch, vocab]
     ctx.synchronize()
     if rank == 0:
         from oracle import binding as O
         O.build()
         om = O.Llama(cfg, params, "f64")
-        oc = om.init_kv_caches(1)
-        want = [om.forward(ids[None, :prompt], oc)[0, -1]]
+        oc = om.init_kv_caches(batch)
+        want = [om.forward(ids[:, :prompt], oc)[:, -1]]
         for t in range(steps):
-            want.append(om.forward(ids[None, prompt + t:prompt + t + 1], oc)[0, 0])
+            want.append(om.forward(ids[:, prompt + t:prompt + t + 1], oc)[:, 0])
         want = np.stack(want)
-        errs = [float(np.abs(g - w).max() / np.abs(w).max()) for g, w in zip(got, want)]
+        errs = [float(np.abs(g - w).max() / np.abs(w).max()) for g, w in zip(got.reshape(-1, got.shape[-1]), want.reshape(-1, want.shape[-1]))]
         print(json.dumps({"world": world, "max_rel_err": max(errs),
                           "argmax_equal": bool((got.argmax(-1) == want.argmax(-1)).all())}), flush=True)
     dist.barrier()
