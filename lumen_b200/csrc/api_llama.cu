@@ -36,6 +36,9 @@ struct Workspace {
     char *base = nullptr;
     float *x = nullptr, *nx = nullptr, *qkv = nullptr, *att = nullptr, *act = nullptr, *gate = nullptr, *up = nullptr;
     float *logits = nullptr, *logits_local = nullptr, *last_x = nullptr, *part = nullptr, *ids = nullptr;
+    // bf16 hi/lo split of the activations the next tensor-core product reads (written by the kernel that finishes the
+    // previous product): [M, max(H, I_l)] each
+    __nv_bfloat16 *p_hi = nullptr, *p_lo = nullptr;
     size_t part_bytes = 0;
     float *h_ids = nullptr;     // pinned
     float *h_logits = nullptr;  // pinned
@@ -121,13 +124,17 @@ int ensure_workspace(lumen_llama *m, size_t M) {
         return o;
     };
     size_t o_x = take(M * m->H), o_nx = take(M * m->H), o_qkv = take(M * qkvd), o_att = take(M * m->qd_l);
-    size_t o_act = take(M * m->inter_l), o_gate = take(M * m->inter_l), o_up = take(M * m->inter_l);
+    // gate and up are adjacent: the fused step runs them as one product into [M, 2 * I_l]
+    size_t o_act = take(M * m->inter_l), o_gate = take(2 * M * m->inter_l);
+    const size_t pair_floats = (M * std::max(m->H, m->inter_l) + 1) / 2 + 8;
+    size_t o_phi = take(pair_floats), o_plo = take(pair_floats);
     size_t o_logits = take(M * m->V), o_ll = take(T > 1 ? T * M * m->vocab_l : 0), o_last = take(M * m->H);
     size_t o_part = take(w.part_bytes / sizeof(float)), o_ids = take(M);
     LUMEN_CUDA(ctx, cudaMalloc(&w.base, off));
     auto at = [&](size_t o) { return reinterpret_cast<float *>(w.base + o); };
     w.x = at(o_x); w.nx = at(o_nx); w.qkv = at(o_qkv); w.att = at(o_att); w.act = at(o_act); w.gate = at(o_gate);
-    w.up = at(o_up); w.logits = at(o_logits); w.logits_local = at(o_ll); w.last_x = at(o_last); w.part = at(o_part);
+    w.up = w.gate + M * m->inter_l; w.p_hi = reinterpret_cast<__nv_bfloat16 *>(at(o_phi)); w.p_lo = reinterpret_cast<__nv_bfloat16 *>(at(o_plo));
+    w.logits = at(o_logits); w.logits_local = at(o_ll); w.last_x = at(o_last); w.part = at(o_part);
     w.ids = at(o_ids);
     LUMEN_CUDA(ctx, cudaMallocHost(&w.h_ids, std::max<size_t>(M, 1) * sizeof(float)));
     w.h_logits_elems = std::min<size_t>(M * m->V, (size_t)16 << 20);  // pinned staging up to 64 MB
@@ -195,11 +202,86 @@ int enqueue_forward(lumen_llama *m, const StepPlan &p, lumen_kv_cache **caches, 
     const float scale = 1.0f / sqrtf((float)m->D);  // (head_dim as f32).sqrt().recip(), self_attention.rs:89
     const float *res_x = (!tp || ctx->tp_rank == 0) ? w.x : nullptr;
 
+    // Fused step (tiled products only): every product's finishing kernel writes what the next product reads, as the bf16
+    // hi/lo pair in w.p_hi / w.p_lo, and gate and up run as one product over their adjacent weights.  Per block:
+    // qkv product + split-K sum, attention, o_proj (split + product + finisher), gate/up (product + finisher),
+    // down (product + finisher) = 11 launches instead of 20.
+    static const bool no_fuse = [] {
+        const char *e = getenv("LUMEN_NO_STEP_FUSE");
+        return e && e[0] == '1';
+    }();
+    bool fuse = !vec && !no_fuse && row_finish_usable(H) && m->inter_l % 8 == 0 && m->qd_l % 8 == 0 && m->L > 0;
+    for (size_t l = 0; fuse && l < m->L; ++l) {
+        const LayerW &lw = m->layers[l];
+        fuse = lw.wup == lw.wgate + m->inter_l * H * m->esz && gemm_tc_usable(wdt, M, H, qkvd, lw.wqkv) &&
+               gemm_tc_usable(wdt, M, m->qd_l, H, lw.wo) && gemm_tc_usable(wdt, M, H, 2 * m->inter_l, lw.wgate) &&
+               gemm_tc_usable(wdt, M, m->inter_l, H, lw.wdown);
+    }
+
+    auto attend = [&](const LayerW &lw, lumen_kv_cache *c) -> int {
+        if (p.decode) {
+            AttnDecodeArgs a;
+            a.q = w.qkv; a.k_new = w.qkv + m->qd_l; a.v_new = w.qkv + m->qd_l + m->kvd_l;
+            a.q_stride = qkvd; a.kv_stride = qkvd;
+            a.k_cache = c->k; a.v_cache = c->v; a.d_len = c->d_len;
+            a.B = p.B; a.Hq = m->hq_l; a.Hkv = m->hkv_l; a.D = m->D; a.max_seq = c->max_seq;
+            a.cos_t = m->cos_t; a.sin_t = m->sin_t;
+            a.q_norm = lw.qn; a.k_norm = lw.kn; a.norm_eps = eps;
+            a.scale = scale; a.out = w.att; a.part = w.part; a.max_splits = p.nsplit; a.len_hint = c->len;
+            return launch_attn_decode(ctx, a, s);
+        }
+        AttnPrefillArgs a;
+        a.q = w.qkv; a.k = w.qkv + m->qd_l; a.v = w.qkv + m->qd_l + m->kvd_l;
+        a.q_stride = qkvd; a.kv_stride = qkvd;
+        a.k_cache = c->k; a.v_cache = c->v;
+        a.past = c->len; a.S = p.S; a.B = p.B; a.Hq = m->hq_l; a.Hkv = m->hkv_l; a.D = m->D; a.max_seq = c->max_seq;
+        a.cos_t = m->cos_t; a.sin_t = m->sin_t;
+        a.q_norm = lw.qn; a.k_norm = lw.kn; a.norm_eps = eps;
+        a.scale = scale; a.causal = 1; a.out = w.att;
+        LUMEN_TRY(launch_attn_prefill(ctx, a, s));
+        return launch_bump_len(ctx, c->d_len, (int)p.S, s);
+    };
+    // Row-parallel product of the fused step: x = x + a . W^T summed over the ranks, and the split of RMSNorm(x) * norm_w
+    // for the next product (norm_w null after the last block).  `a` null: the activations are the pair already.
+    auto row_parallel = [&](const float *a, const void *wmat, size_t K, const float *norm_w) -> int {
+        GemmFuse f;
+        if (!a) { f.a_hi = w.p_hi; f.a_lo = w.p_lo; }
+        if (!tp) {
+            f.post = GemmFuse::kPostNorm; f.norm_w = norm_w; f.eps = eps; f.next_hi = w.p_hi; f.next_lo = w.p_lo;
+            return launch_gemm_tc(ctx, a, wmat, wdt, w.x, M, K, H, res_x, s, nullptr, &f);
+        }
+        if (tp_sum_usable(ctx, M, H)) {
+            TpSumArgs t;
+            t.out = w.x; t.norm_w = norm_w; t.eps = eps;
+            if (norm_w) { t.next_hi = w.p_hi; t.next_lo = w.p_lo; }
+            return launch_gemm_tc(ctx, a, wmat, wdt, w.x, M, K, H, res_x, s, &t, &f);
+        }
+        // too many rows for the fused exchange (long prefill slices are bandwidth-bound): NCCL, then the norm + split
+        LUMEN_TRY(launch_gemm_tc(ctx, a, wmat, wdt, w.x, M, K, H, res_x, s, nullptr, &f));
+        LUMEN_TRY(tp_allreduce_sum(ctx, w.x, M * H, s));
+        if (norm_w) return launch_sum_norm_split(ctx, w.x, 1, nullptr, M, H, nullptr, norm_w, eps, w.p_hi, w.p_lo, s);
+        return LUMEN_OK;
+    };
+
     LUMEN_TRY(launch_embedding(ctx, w.ids, m->embed, wdt, w.x, M, m->V, H, s));
-    bool nx_ready = false;  // w.nx already holds Norm(x) of the block about to run
+    bool nx_ready = false;  // w.nx (or, fused, the pair) already holds Norm(x) of the block about to run
     for (size_t l = 0; l < m->L; ++l) {
         const LayerW &lw = m->layers[l];
         lumen_kv_cache *c = caches[l];
+        if (fuse) {
+            if (!nx_ready) LUMEN_TRY(launch_sum_norm_split(ctx, w.x, 1, nullptr, M, H, nullptr, lw.norm1, eps, w.p_hi, w.p_lo, s));
+            GemmFuse fq;
+            fq.a_hi = w.p_hi; fq.a_lo = w.p_lo;
+            LUMEN_TRY(launch_gemm_tc(ctx, nullptr, lw.wqkv, wdt, w.qkv, M, H, qkvd, nullptr, s, nullptr, &fq));
+            LUMEN_TRY(attend(lw, c));
+            LUMEN_TRY(row_parallel(w.att, lw.wo, m->qd_l, lw.norm2));
+            GemmFuse fg;
+            fg.a_hi = w.p_hi; fg.a_lo = w.p_lo; fg.post = GemmFuse::kPostSwiglu; fg.next_hi = w.p_hi; fg.next_lo = w.p_lo;
+            LUMEN_TRY(launch_gemm_tc(ctx, nullptr, lw.wgate, wdt, w.gate, M, H, 2 * m->inter_l, nullptr, s, nullptr, &fg));
+            nx_ready = l + 1 < m->L;
+            LUMEN_TRY(row_parallel(nullptr, lw.wdown, m->inter_l, nx_ready ? m->layers[l + 1].norm1 : nullptr));
+            continue;
+        }
         // h = x + Attention(Norm(x))                                   llama.rs:107-110
         if (vec) {
             GemvArgs g;
@@ -210,28 +292,7 @@ int enqueue_forward(lumen_llama *m, const StepPlan &p, lumen_kv_cache **caches, 
             if (!nx_ready) LUMEN_TRY(launch_rmsnorm(ctx, w.x, lw.norm1, eps, w.nx, M, H, s));
             LUMEN_TRY(launch_gemm_nk(ctx, w.nx, lw.wqkv, wdt, w.qkv, M, H, qkvd, nullptr, s));
         }
-        if (p.decode) {
-            AttnDecodeArgs a;
-            a.q = w.qkv; a.k_new = w.qkv + m->qd_l; a.v_new = w.qkv + m->qd_l + m->kvd_l;
-            a.q_stride = qkvd; a.kv_stride = qkvd;
-            a.k_cache = c->k; a.v_cache = c->v; a.d_len = c->d_len;
-            a.B = p.B; a.Hq = m->hq_l; a.Hkv = m->hkv_l; a.D = m->D; a.max_seq = c->max_seq;
-            a.cos_t = m->cos_t; a.sin_t = m->sin_t;
-            a.q_norm = lw.qn; a.k_norm = lw.kn; a.norm_eps = eps;
-            a.scale = scale; a.out = w.att; a.part = w.part; a.max_splits = p.nsplit; a.len_hint = c->len;
-            LUMEN_TRY(launch_attn_decode(ctx, a, s));
-        } else {
-            AttnPrefillArgs a;
-            a.q = w.qkv; a.k = w.qkv + m->qd_l; a.v = w.qkv + m->qd_l + m->kvd_l;
-            a.q_stride = qkvd; a.kv_stride = qkvd;
-            a.k_cache = c->k; a.v_cache = c->v;
-            a.past = c->len; a.S = p.S; a.B = p.B; a.Hq = m->hq_l; a.Hkv = m->hkv_l; a.D = m->D; a.max_seq = c->max_seq;
-            a.cos_t = m->cos_t; a.sin_t = m->sin_t;
-            a.q_norm = lw.qn; a.k_norm = lw.kn; a.norm_eps = eps;
-            a.scale = scale; a.causal = 1; a.out = w.att;
-            LUMEN_TRY(launch_attn_prefill(ctx, a, s));
-            LUMEN_TRY(launch_bump_len(ctx, c->d_len, (int)p.S, s));
-        }
+        LUMEN_TRY(attend(lw, c));
         // With tensor parallelism the sum over the ranks follows the product in the same call, and (outside the
         // vector path, which folds the norm into its next product) leaves Norm(x) for the next product in w.nx.
         TpSumArgs sum_o;

@@ -141,6 +141,7 @@ struct TpSumArgs {
     const float *norm_w = nullptr;
     float *normed = nullptr;
     float eps = 0.f;
+    __nv_bfloat16 *next_hi = nullptr, *next_lo = nullptr;  // bf16 hi/lo split of RMSNorm(sum) for a tensor-core product that follows
 };
 
 // y[M,N] = a[M,K] . w[N,K]^T (+ residual): vector-matrix kernel for M <= 8, tiled GEMM otherwise.  With `tp` (and
@@ -221,8 +222,31 @@ int launch_gemm_nk(lumen_ctx *ctx, const float *a, const void *w, lumen_dtype wd
 // rows over f32 weights on the streaming kernel);
 // launch_gemm_nk takes this path whenever gemm_tc_usable says so.
 bool gemm_tc_usable(lumen_dtype wdt, size_t M, size_t K, size_t N, const void *w);
+// Fusions around the tensor-core product inside a model step.  Input side: the activations arrive already split into
+// bf16 hi + lo by the kernel that produced them (then `a` is not read).  Output side: the kernel that adds the split-K
+// slices also produces what the next product reads (gemm_finish.cu):
+//   kPostNorm    c = sum (+ residual); (next_hi, next_lo) = split of RMSNorm(c) * norm_w  (norm_w null: c only)
+//   kPostSwiglu  the product ran over the concatenated gate and up weights (N = 2 * intermediate):
+//                (next_hi, next_lo) = split of silu(c[:, :N/2]) * c[:, N/2:]; c is scratch for [M, N] floats
+struct GemmFuse {
+    enum Post { kPostNone = 0, kPostNorm = 1, kPostSwiglu = 2 };
+    const __nv_bfloat16 *a_hi = nullptr, *a_lo = nullptr;
+    Post post = kPostNone;
+    const float *norm_w = nullptr;
+    float eps = 0.f;
+    __nv_bfloat16 *next_hi = nullptr, *next_lo = nullptr;
+};
 int launch_gemm_tc(lumen_ctx *ctx, const float *a, const void *w, lumen_dtype wdt, float *c, size_t M, size_t K, size_t N,
-                   const float *residual, cudaStream_t s, const TpSumArgs *tp = nullptr);
+                   const float *residual, cudaStream_t s, const TpSumArgs *tp = nullptr, const GemmFuse *fuse = nullptr);
+// Row finishers (gemm_finish.cu).  Rows of up to 8192 elements, a multiple of 8.
+bool row_finish_usable(size_t dim);
+// out = sum over `splits` slices of part (+ residual) (out may be null or alias part / residual); with gains also the bf16
+// hi/lo split of RMSNorm(out).
+int launch_sum_norm_split(lumen_ctx *ctx, const float *part, int splits, const float *residual, size_t rows, size_t dim, float *out,
+                          const float *norm_w, float eps, __nv_bfloat16 *hi, __nv_bfloat16 *lo, cudaStream_t s);
+// part: [splits][rows][2 * inter] (gate columns, then up columns) -> bf16 hi/lo split of silu(gate) * up, [rows, inter].
+int launch_sum_swiglu_split(lumen_ctx *ctx, const float *part, int splits, size_t rows, size_t inter, __nv_bfloat16 *hi,
+                            __nv_bfloat16 *lo, cudaStream_t s);
 
 int launch_rmsnorm(lumen_ctx *ctx, const float *x, const float *w, float eps, float *out, size_t rows, size_t dim,
                    cudaStream_t s);

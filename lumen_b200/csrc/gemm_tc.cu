@@ -249,17 +249,21 @@ int pick_bn(size_t M, size_t N, int num_sms) {
 // wdt == LUMEN_F32: the weights are split into hi + lo bf16 matrices on the fly as well (one streaming pass
 // over W per call) and three of the four cross products are accumulated.
 int launch_gemm_tc(lumen_ctx *ctx, const float *a, const void *w, lumen_dtype wdt, float *c, size_t M, size_t K, size_t N,
-                   const float *residual, cudaStream_t s, const TpSumArgs *tp) {
+                   const float *residual, cudaStream_t s, const TpSumArgs *tp, const GemmFuse *fuse) {
     const bool wsplit = wdt == LUMEN_F32;
+    const bool presplit = fuse && fuse->a_hi && fuse->a_lo;  // the producer of the activations split them already
     void *split = nullptr;
-    const size_t na = M * K, nap = (na + 7) & ~(size_t)7, nw = wsplit ? N * K : 0, nwp = (nw + 7) & ~(size_t)7;
+    const size_t na = presplit ? 0 : M * K, nap = (na + 7) & ~(size_t)7, nw = wsplit ? N * K : 0, nwp = (nw + 7) & ~(size_t)7;
     LUMEN_TRY(dev_alloc(ctx, (2 * nap + 2 * nwp) * sizeof(__nv_bfloat16) + 32, &split));
     __nv_bfloat16 *hi = static_cast<__nv_bfloat16 *>(split);
     __nv_bfloat16 *lo = hi + nap;  // every matrix stays 16-byte aligned
     __nv_bfloat16 *whi = lo + nap, *wlo = whi + nwp;
-    split_bf16_kernel<<<(unsigned)((na + 255) / 256), 256, 0, s>>>(a, hi, lo, na);
     int rc = LUMEN_OK;
-    {
+    if (presplit) {
+        hi = const_cast<__nv_bfloat16 *>(fuse->a_hi);
+        lo = const_cast<__nv_bfloat16 *>(fuse->a_lo);
+    } else {
+        split_bf16_kernel<<<(unsigned)((na + 255) / 256), 256, 0, s>>>(a, hi, lo, na);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) rc = cuda_fail(ctx, e, "split_bf16_kernel launch");
         else ctx->launches += 1;
@@ -313,6 +317,15 @@ int launch_gemm_tc(lumen_ctx *ctx, const float *a, const void *w, lumen_dtype wd
             // the sum over the ranks takes the slices (or the finished product) from here
             rc = splits > 1 ? launch_tp_sum(ctx, static_cast<const float *>(partial), splits, residual, M, N, *tp, s)
                             : launch_tp_sum(ctx, c, 1, nullptr, M, N, *tp, s);
+        } else if (rc == LUMEN_OK && fuse && fuse->post == GemmFuse::kPostNorm) {
+            if (splits > 1)
+                rc = launch_sum_norm_split(ctx, static_cast<const float *>(partial), splits, residual, M, N, c, fuse->norm_w, fuse->eps,
+                                           fuse->next_hi, fuse->next_lo, s);
+            else if (fuse->norm_w)  // c is complete (the product's epilogue added the residual): only the norm outputs are missing
+                rc = launch_sum_norm_split(ctx, c, 1, nullptr, M, N, nullptr, fuse->norm_w, fuse->eps, fuse->next_hi, fuse->next_lo, s);
+        } else if (rc == LUMEN_OK && fuse && fuse->post == GemmFuse::kPostSwiglu) {
+            rc = launch_sum_swiglu_split(ctx, splits > 1 ? static_cast<const float *>(partial) : c, splits, M, N / 2, fuse->next_hi,
+                                         fuse->next_lo, s);
         } else if (rc == LUMEN_OK && splits > 1) {
             const size_t mn = M * N;
             splitk_reduce_kernel<<<(unsigned)((mn + 255) / 256), 256, 0, s>>>(static_cast<const float *>(partial), residual, c, mn, splits);

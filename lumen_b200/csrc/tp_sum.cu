@@ -16,7 +16,7 @@
 #include <algorithm>
 #include <cstdlib>
 
-#include "common.cuh"
+#include "row_finish.cuh"
 
 namespace lumen {
 namespace {
@@ -26,10 +26,7 @@ constexpr long long kTpSumWaitCycles = 4000000000LL;  // ~2 s: ranks are launche
 struct TpSumParams {
     const float *part;      // [splits][rows*dim] partial products of this rank
     const float *residual;  // added once (rank 0 passes the residual stream) or null
-    float *out;             // [rows, dim] sum over ranks
-    const float *norm_w;    // RMSNorm gains applied to the summed rows into `normed`, or null
-    float *normed;
-    float eps;
+    RowFinish fin;          // where the sum over the ranks goes: the row, and optionally RMSNorm of it (f32 and/or bf16 hi/lo)
     int splits, rows, dim, rank;
     float *slots[8];
     unsigned *flags[8];
@@ -46,19 +43,6 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *p) {
     return v;
 }
 
-__device__ __forceinline__ float warp_sum(float v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    return v;
-}
-__device__ __forceinline__ float4 add4(float4 a, float4 b) {
-    return make_float4(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y), __fadd_rn(a.z, b.z), __fadd_rn(a.w, b.w));
-}
-
-// One CTA per row; a thread holds up to kVecs float4 of the row (dim <= 8192) in registers, so that every pass over the
-// row is one batch of independent loads (the kernel is a chain of memory round trips, not of bytes).
-constexpr int kVecs = 8;
-
 template <int T>
 __global__ void __launch_bounds__(256) tp_sum_kernel(TpSumParams p) {
     __shared__ float red[8];
@@ -73,39 +57,13 @@ __global__ void __launch_bounds__(256) tp_sum_kernel(TpSumParams p) {
     // 1. this rank's partial rows (split-K slices added in order, residual last) into everybody's slot `rank`
     for (int row = blockIdx.x; row < p.rows; row += gridDim.x) {
         const size_t base = (size_t)row * p.dim;
-        float4 acc[kVecs];
-        {
-            const float4 *p0 = reinterpret_cast<const float4 *>(p.part + base);
-#pragma unroll
-            for (int k = 0; k < kVecs; ++k)
-                if (tid + 256 * k < nvec) acc[k] = p0[tid + 256 * k];
-        }
-#pragma unroll 4
-        for (int sl = 1; sl < p.splits; ++sl) {
-            const float4 *ps = reinterpret_cast<const float4 *>(p.part + (size_t)sl * mn + base);
-            float4 t[kVecs];
-#pragma unroll
-            for (int k = 0; k < kVecs; ++k)
-                if (tid + 256 * k < nvec) t[k] = ps[tid + 256 * k];
-#pragma unroll
-            for (int k = 0; k < kVecs; ++k)
-                if (tid + 256 * k < nvec) acc[k] = add4(acc[k], t[k]);
-        }
-        if (p.residual) {
-            const float4 *pr = reinterpret_cast<const float4 *>(p.residual + base);
-            float4 t[kVecs];
-#pragma unroll
-            for (int k = 0; k < kVecs; ++k)
-                if (tid + 256 * k < nvec) t[k] = pr[tid + 256 * k];
-#pragma unroll
-            for (int k = 0; k < kVecs; ++k)
-                if (tid + 256 * k < nvec) acc[k] = add4(t[k], acc[k]);
-        }
+        float4 acc[kRowVecs];
+        row_load_sum(acc, p.part, p.splits, mn, p.residual, base, nvec, tid);
 #pragma unroll
         for (int r = 0; r < T; ++r) {
             float4 *dst = reinterpret_cast<float4 *>(p.slots[r] + my_slot + base);
 #pragma unroll
-            for (int k = 0; k < kVecs; ++k)
+            for (int k = 0; k < kRowVecs; ++k)
                 if (tid + 256 * k < nvec) dst[tid + 256 * k] = acc[k];
         }
         __syncthreads();
@@ -134,56 +92,25 @@ __global__ void __launch_bounds__(256) tp_sum_kernel(TpSumParams p) {
         }
         __syncthreads();
         const size_t base = (size_t)row * p.dim;
-        float4 v[kVecs];
+        float4 v[kRowVecs];
         {
             const float4 *s0 = reinterpret_cast<const float4 *>(mine + base);
 #pragma unroll
-            for (int k = 0; k < kVecs; ++k)
+            for (int k = 0; k < kRowVecs; ++k)
                 if (tid + 256 * k < nvec) v[k] = __ldcg(s0 + tid + 256 * k);
         }
 #pragma unroll
         for (int t = 1; t < T; ++t) {
             const float4 *st = reinterpret_cast<const float4 *>(mine + (size_t)t * kTpSumSlotFloats + base);
-            float4 u[kVecs];
+            float4 u[kRowVecs];
 #pragma unroll
-            for (int k = 0; k < kVecs; ++k)
+            for (int k = 0; k < kRowVecs; ++k)
                 if (tid + 256 * k < nvec) u[k] = __ldcg(st + tid + 256 * k);
 #pragma unroll
-            for (int k = 0; k < kVecs; ++k)
+            for (int k = 0; k < kRowVecs; ++k)
                 if (tid + 256 * k < nvec) v[k] = add4(v[k], u[k]);
         }
-        float4 *o4 = reinterpret_cast<float4 *>(p.out + base);
-        float ss = 0.f;
-#pragma unroll
-        for (int k = 0; k < kVecs; ++k)
-            if (tid + 256 * k < nvec) {
-                o4[tid + 256 * k] = v[k];
-                ss = fmaf(v[k].x, v[k].x, ss);
-                ss = fmaf(v[k].y, v[k].y, ss);
-                ss = fmaf(v[k].z, v[k].z, ss);
-                ss = fmaf(v[k].w, v[k].w, ss);
-            }
-        if (p.norm_w) {
-            // RMSNorm::forward (src/layers/norm/rms_norm.rs:49-56): rms = sqrt(ss/dim + eps); o = (x * (1/rms)) * w
-            ss = warp_sum(ss);
-            if ((tid & 31) == 0) red[tid >> 5] = ss;
-            __syncthreads();
-            float t = 0.f;
-#pragma unroll
-            for (int w = 0; w < 8; ++w) t += red[w];
-            __syncthreads();
-            const float rms = sqrtf(__fadd_rn(__fdiv_rn(t, (float)p.dim), p.eps));
-            const float inv = __fdiv_rn(1.0f, rms);
-            const float4 *g4 = reinterpret_cast<const float4 *>(p.norm_w);
-            float4 *n4 = reinterpret_cast<float4 *>(p.normed + base);
-#pragma unroll
-            for (int k = 0; k < kVecs; ++k)
-                if (tid + 256 * k < nvec) {
-                    const float4 g = g4[tid + 256 * k];
-                    n4[tid + 256 * k] = make_float4(__fmul_rn(__fmul_rn(v[k].x, inv), g.x), __fmul_rn(__fmul_rn(v[k].y, inv), g.y),
-                                                    __fmul_rn(__fmul_rn(v[k].z, inv), g.z), __fmul_rn(__fmul_rn(v[k].w, inv), g.w));
-                }
-        }
+        row_finish(v, p.fin, base, p.dim, nvec, tid, red);
     }
 
     // 3. the last CTA advances the epoch for the next launch on this stream
@@ -211,7 +138,7 @@ bool tp_sum_usable(const lumen_ctx *ctx, size_t rows, size_t dim) {
     }();
     const int T = ctx->tp_size;
     return !off && (T == 2 || T == 4 || T == 8) && ctx->d_tp_sum && rows >= 1 && rows <= kTpSumMaxRows && dim % 4 == 0 &&
-           dim <= (size_t)kVecs * 1024 && rows * dim <= kTpSumSlotFloats;
+           dim % 8 == 0 && dim <= (size_t)kRowVecs * 1024 && rows * dim <= kTpSumSlotFloats;
 }
 
 int ensure_tp_sum(lumen_ctx *ctx) {
@@ -234,7 +161,8 @@ int launch_tp_sum(lumen_ctx *ctx, const float *part, int splits, const float *re
                   const TpSumArgs &a, cudaStream_t s) {
     if (!tp_sum_usable(ctx, rows, dim)) return set_error(ctx, LUMEN_ERR_UNSUPPORTED, "tensor-parallel sum: %zu x %zu does not fit the exchange buffer", rows, dim);
     TpSumParams p{};
-    p.part = part; p.residual = residual; p.out = a.out; p.norm_w = a.norm_w; p.normed = a.normed; p.eps = a.eps;
+    p.part = part; p.residual = residual;
+    p.fin = RowFinish{a.out, a.norm_w, a.eps, a.normed, a.next_hi, a.next_lo};
     p.splits = splits; p.rows = (int)rows; p.dim = (int)dim; p.rank = ctx->tp_rank;
     const size_t flag_words = (size_t)2 * ctx->tp_size * kTpSumMaxRows;
     for (int r = 0; r < ctx->tp_size; ++r) {
