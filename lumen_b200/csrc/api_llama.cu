@@ -68,6 +68,11 @@ struct lumen_llama {
     size_t kv_head0 = 0, q_head0 = 0;  // first global head owned by this rank
     size_t esz = 4;
     char *wslab = nullptr;
+    // f32 weights only: bf16 hi and lo halves of the whole slab (same layout at half the offsets), built before the first
+    // tensor-core product and dropped when a parameter changes, so that prefill and batched steps do not split the
+    // weights again on every call.  Costs as many bytes as the weights; absent (null) when that allocation fails.
+    __nv_bfloat16 *wsplit = nullptr;
+    bool wsplit_valid = false, wsplit_failed = false;
     size_t wbytes = 0, stream_bytes = 0;
     std::vector<LayerW> layers;
     char *embed = nullptr, *lm_head = nullptr;
@@ -179,6 +184,37 @@ int upload_block(lumen_ctx *ctx, void *dst, lumen_dtype dst_dt, const void *src_
     return rc;
 }
 
+int ensure_weight_split(lumen_llama *m) {
+    if (m->cfg.weight_dtype != LUMEN_F32 || m->wsplit_valid || m->wsplit_failed) return LUMEN_OK;
+    static const bool off = [] {
+        const char *e = getenv("LUMEN_NO_WEIGHT_SPLIT_CACHE");
+        return e && e[0] == '1';
+    }();
+    if (off) return LUMEN_OK;
+    lumen_ctx *ctx = m->ctx;
+    const size_t n = m->wbytes / 4;
+    if (!m->wsplit) {
+        void *p = nullptr;
+        if (cudaMalloc(&p, 2 * n * sizeof(__nv_bfloat16)) != cudaSuccess) {
+            cudaGetLastError();  // no room: the products keep splitting per call
+            m->wsplit_failed = true;
+            return LUMEN_OK;
+        }
+        m->wsplit = static_cast<__nv_bfloat16 *>(p);
+    }
+    LUMEN_TRY(launch_split_bf16(ctx, reinterpret_cast<const float *>(m->wslab), m->wsplit, m->wsplit + n, n, ctx->stream));
+    m->wsplit_valid = true;
+    return LUMEN_OK;
+}
+
+// Points a product's fusion record at the kept split of the f32 weight matrix `wp` (no-op without one).
+void use_weight_split(const lumen_llama *m, const void *wp, GemmFuse &f) {
+    if (!m->wsplit_valid) return;
+    const size_t at = (size_t)(static_cast<const char *>(wp) - m->wslab) / 4;
+    f.w_hi = m->wsplit + at;
+    f.w_lo = m->wsplit + m->wbytes / 4 + at;
+}
+
 struct StepPlan {
     size_t B, S, M;
     bool decode;
@@ -245,6 +281,7 @@ int enqueue_forward(lumen_llama *m, const StepPlan &p, lumen_kv_cache **caches, 
     // for the next product (norm_w null after the last block).  `a` null: the activations are the pair already.
     auto row_parallel = [&](const float *a, const void *wmat, size_t K, const float *norm_w) -> int {
         GemmFuse f;
+        use_weight_split(m, wmat, f);
         if (!a) { f.a_hi = w.p_hi; f.a_lo = w.p_lo; }
         if (!tp) {
             f.post = GemmFuse::kPostNorm; f.norm_w = norm_w; f.eps = eps; f.next_hi = w.p_hi; f.next_lo = w.p_lo;
@@ -272,11 +309,13 @@ int enqueue_forward(lumen_llama *m, const StepPlan &p, lumen_kv_cache **caches, 
             if (!nx_ready) LUMEN_TRY(launch_sum_norm_split(ctx, w.x, 1, nullptr, M, H, nullptr, lw.norm1, eps, w.p_hi, w.p_lo, s));
             GemmFuse fq;
             fq.a_hi = w.p_hi; fq.a_lo = w.p_lo;
+            use_weight_split(m, lw.wqkv, fq);
             LUMEN_TRY(launch_gemm_tc(ctx, nullptr, lw.wqkv, wdt, w.qkv, M, H, qkvd, nullptr, s, nullptr, &fq));
             LUMEN_TRY(attend(lw, c));
             LUMEN_TRY(row_parallel(w.att, lw.wo, m->qd_l, lw.norm2));
             GemmFuse fg;
             fg.a_hi = w.p_hi; fg.a_lo = w.p_lo; fg.post = GemmFuse::kPostSwiglu; fg.next_hi = w.p_hi; fg.next_lo = w.p_lo;
+            use_weight_split(m, lw.wgate, fg);
             LUMEN_TRY(launch_gemm_tc(ctx, nullptr, lw.wgate, wdt, w.gate, M, H, 2 * m->inter_l, nullptr, s, nullptr, &fg));
             nx_ready = l + 1 < m->L;
             LUMEN_TRY(row_parallel(nullptr, lw.wdown, m->inter_l, nx_ready ? m->layers[l + 1].norm1 : nullptr));
@@ -330,7 +369,13 @@ int enqueue_forward(lumen_llama *m, const StepPlan &p, lumen_kv_cache **caches, 
         LUMEN_TRY(launch_gemv_nk(ctx, g, s));
     } else {
         LUMEN_TRY(launch_rmsnorm(ctx, xin, m->final_norm, eps, w.nx, rows, H, s));
-        LUMEN_TRY(launch_gemm_nk(ctx, w.nx, m->lm_head, wdt, lg, rows, H, m->vocab_l, nullptr, s));
+        if (m->wsplit_valid && gemm_tc_usable(wdt, rows, H, m->vocab_l, m->lm_head)) {
+            GemmFuse fl;
+            use_weight_split(m, m->lm_head, fl);
+            LUMEN_TRY(launch_gemm_tc(ctx, w.nx, m->lm_head, wdt, lg, rows, H, m->vocab_l, nullptr, s, nullptr, &fl));
+        } else {
+            LUMEN_TRY(launch_gemm_nk(ctx, w.nx, m->lm_head, wdt, lg, rows, H, m->vocab_l, nullptr, s));
+        }
     }
     if (tp) {
         LUMEN_TRY(tp_allgather(ctx, lg, w.logits_local, rows * m->vocab_l, s));
@@ -510,6 +555,7 @@ int run_forward(lumen_llama *m, size_t b, size_t s, lumen_kv_cache **caches, boo
         return LUMEN_OK;
     }
     StepPlan p{b, s, b * s, s == 1, 1};
+    if (p.M > 8) LUMEN_TRY(ensure_weight_split(m));  // (outside any stream capture; the streaming kernels of <= 8 rows read f32)
     if (p.decode) p.nsplit = pick_decode_splits(m, b, caches[0]->len + 1);
     int rc = LUMEN_OK;
     if (p.decode && m->use_graph) {
@@ -677,6 +723,7 @@ int lumen_llama_set_param(lumen_llama *m, const char *name, const void *host_dat
     if (dtype != LUMEN_F32 && dtype != LUMEN_BF16) return set_error(ctx, LUMEN_ERR_DTYPE, "set_param: dtype %d", (int)dtype);
     const lumen_dtype wdt = m->cfg.weight_dtype;
     const size_t se = dtype == LUMEN_F32 ? 4 : 2, e = m->esz, H = m->H;
+    m->wsplit_valid = false;  // (the kept bf16 split of the f32 weights is rebuilt before its next use)
     // Which part of the tensor this rank keeps comes from the shard plan; what is left here is where it goes.
     TpSlice sl;
     long li = -1;
@@ -837,6 +884,7 @@ int lumen_llama_free(lumen_llama *m) {
     if (m->ws.h_ids) cudaFreeHost(m->ws.h_ids);
     if (m->ws.h_logits) cudaFreeHost(m->ws.h_logits);
     if (m->wslab) cudaFree(m->wslab);
+    if (m->wsplit) cudaFree(m->wsplit);
     delete m;
     return LUMEN_OK;
 }

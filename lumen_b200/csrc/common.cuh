@@ -231,6 +231,7 @@ bool gemm_tc_usable(lumen_dtype wdt, size_t M, size_t K, size_t N, const void *w
 struct GemmFuse {
     enum Post { kPostNone = 0, kPostNorm = 1, kPostSwiglu = 2 };
     const __nv_bfloat16 *a_hi = nullptr, *a_lo = nullptr;
+    const __nv_bfloat16 *w_hi = nullptr, *w_lo = nullptr;  // f32 weights split once by the model (else split on every call)
     Post post = kPostNone;
     const float *norm_w = nullptr;
     float eps = 0.f;
@@ -238,6 +239,8 @@ struct GemmFuse {
 };
 int launch_gemm_tc(lumen_ctx *ctx, const float *a, const void *w, lumen_dtype wdt, float *c, size_t M, size_t K, size_t N,
                    const float *residual, cudaStream_t s, const TpSumArgs *tp = nullptr, const GemmFuse *fuse = nullptr);
+// hi = bf16(a), lo = bf16(a - hi), n elements (the operand form of the tensor-core product).
+int launch_split_bf16(lumen_ctx *ctx, const float *a, __nv_bfloat16 *hi, __nv_bfloat16 *lo, size_t n, cudaStream_t s);
 // Row finishers (gemm_finish.cu).  Rows of up to 8192 elements, a multiple of 8.
 bool row_finish_usable(size_t dim);
 // out = sum over `splits` slices of part (+ residual) (out may be null or alias part / residual); with gains also the bf16

@@ -246,6 +246,13 @@ int pick_bn(size_t M, size_t N, int num_sms) {
 
 }  // namespace
 
+int launch_split_bf16(lumen_ctx *ctx, const float *a, __nv_bfloat16 *hi, __nv_bfloat16 *lo, size_t n, cudaStream_t s) {
+    if (n == 0) return LUMEN_OK;
+    split_bf16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(a, hi, lo, n);
+    LUMEN_LAUNCHED(ctx);
+    return LUMEN_OK;
+}
+
 // wdt == LUMEN_F32: the weights are split into hi + lo bf16 matrices on the fly as well (one streaming pass
 // over W per call) and three of the four cross products are accumulated.
 int launch_gemm_tc(lumen_ctx *ctx, const float *a, const void *w, lumen_dtype wdt, float *c, size_t M, size_t K, size_t N,
@@ -253,7 +260,8 @@ int launch_gemm_tc(lumen_ctx *ctx, const float *a, const void *w, lumen_dtype wd
     const bool wsplit = wdt == LUMEN_F32;
     const bool presplit = fuse && fuse->a_hi && fuse->a_lo;  // the producer of the activations split them already
     void *split = nullptr;
-    const size_t na = presplit ? 0 : M * K, nap = (na + 7) & ~(size_t)7, nw = wsplit ? N * K : 0, nwp = (nw + 7) & ~(size_t)7;
+    const bool wpre = wsplit && fuse && fuse->w_hi && fuse->w_lo;  // the model keeps the split of its f32 weights
+    const size_t na = presplit ? 0 : M * K, nap = (na + 7) & ~(size_t)7, nw = (wsplit && !wpre) ? N * K : 0, nwp = (nw + 7) & ~(size_t)7;
     LUMEN_TRY(dev_alloc(ctx, (2 * nap + 2 * nwp) * sizeof(__nv_bfloat16) + 32, &split));
     __nv_bfloat16 *hi = static_cast<__nv_bfloat16 *>(split);
     __nv_bfloat16 *lo = hi + nap;  // every matrix stays 16-byte aligned
@@ -268,7 +276,10 @@ int launch_gemm_tc(lumen_ctx *ctx, const float *a, const void *w, lumen_dtype wd
         if (e != cudaSuccess) rc = cuda_fail(ctx, e, "split_bf16_kernel launch");
         else ctx->launches += 1;
     }
-    if (rc == LUMEN_OK && wsplit) {
+    if (wpre) {
+        whi = const_cast<__nv_bfloat16 *>(fuse->w_hi);
+        wlo = const_cast<__nv_bfloat16 *>(fuse->w_lo);
+    } else if (rc == LUMEN_OK && wsplit) {
         split_bf16_kernel<<<(unsigned)((nw + 255) / 256), 256, 0, s>>>(static_cast<const float *>(w), whi, wlo, nw);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) rc = cuda_fail(ctx, e, "split_bf16_kernel launch");
