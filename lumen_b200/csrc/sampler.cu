@@ -89,24 +89,45 @@ sample_prep_kernel(const float *__restrict__ logits, int n, float temperature, f
 
 // The reference adds the sorted probabilities one by one in f32 and stops at the first index where the
 // running sum reaches a threshold (main.rs:113-121 and :126-134).  With a flat distribution the rounding of
-// that sequential sum decides the index, so the order of the additions is kept: the warp stages 1024 values at a
-// time in shared memory (dividing by `scale` on the way: 1 for the cumulative probability, the nucleus mass
-// for the inverse-CDF walk) and lane 0 adds them in order, 32 per test of the threshold; the block of
-// 32 that crosses is then walked value by value.  Returns the first index < n whose running sum is >=
-// threshold (n if none) and that running sum (the total if none).
-__device__ __forceinline__ int first_reaching(const float *__restrict__ vals, int n, float scale, float threshold, float *buf,
+// that sequential sum decides the index, so the order of the additions is kept: one thread adds the values in
+// order, 32 per test of the threshold (the block of 32 that crosses is then walked value by value), reading them
+// from shared memory, while the other three warps of the CTA stage the next 2048 values into the other half of a
+// double buffer (dividing by `scale` on the way: 1 for the cumulative probability, the nucleus mass for the
+// inverse-CDF walk).  What the walk costs is then the dependent chain of additions alone.  Returns the first
+// index < n whose running sum is >= threshold (n if none) and that running sum (the total if none).
+constexpr int kPickThreads = 128;
+constexpr int kPickChunk = 2048;
+
+struct PickShared {
+    __align__(16) float buf[2][kPickChunk];
+    int found;
+    float run;
+};
+
+__device__ __forceinline__ void stage_chunk(const float *__restrict__ vals, int n, int c0, float scale, float *dst, int first, int step) {
+    const int m = min(kPickChunk, n - c0);
+    for (int i = first; i < kPickChunk; i += step) dst[i] = i < m ? __fdiv_rn(vals[c0 + i], scale) : 0.f;  // zeros change no sum
+}
+
+__device__ __forceinline__ int first_reaching(const float *__restrict__ vals, int n, float scale, float threshold, PickShared &sh,
                                               float *sum_out) {
-    constexpr int kChunk = 1024;
-    const int lane = threadIdx.x;
-    float run = 0.f;
-    int found = n;
-    for (int c0 = 0; c0 < n && found == n; c0 += kChunk) {
-        const int m = min(kChunk, n - c0);
-        for (int i = lane; i < kChunk; i += 32) buf[i] = i < m ? __fdiv_rn(vals[c0 + i], scale) : 0.f;  // zeros change no sum
-        __syncwarp();
-        if (lane == 0) {
+    const int tid = threadIdx.x;
+    stage_chunk(vals, n, 0, scale, sh.buf[0], tid, kPickThreads);
+    if (tid == 0) {
+        sh.found = n;
+        sh.run = 0.f;
+    }
+    __syncthreads();
+    const int chunks = (n + kPickChunk - 1) / kPickChunk;
+    for (int c = 0; c < chunks; ++c) {
+        if (tid >= 32) {
+            if (c + 1 < chunks) stage_chunk(vals, n, (c + 1) * kPickChunk, scale, sh.buf[(c + 1) & 1], tid - 32, kPickThreads - 32);
+        } else if (tid == 0) {
+            const float *buf = sh.buf[c & 1];
+            const int c0 = c * kPickChunk, m = min(kPickChunk, n - c0);
+            float run = sh.run;
+            int found = n;
             // 32 values per test of the threshold: eight 128-bit loads, then the dependent chain of 32 additions
-            // (the chain is what the walk costs; nothing else is on it)
             for (int i = 0; i < m; i += 32) {
                 float4 v[8];
 #pragma unroll
@@ -132,25 +153,31 @@ __device__ __forceinline__ int first_reaching(const float *__restrict__ vals, in
                 }
                 run = t;
             }
+            sh.run = run;
+            sh.found = found;
         }
-        found = __shfl_sync(0xffffffffu, found, 0);
-        __syncwarp();
+        __syncthreads();
+        const int f = sh.found;
+        __syncthreads();  // everybody has read the word before the walker writes it again
+        if (f != n) break;
     }
-    *sum_out = __shfl_sync(0xffffffffu, run, 0);
+    const int found = sh.found;
+    *sum_out = sh.run;
+    __syncthreads();  // the buffers and the two words are reused by the next walk
     return found;
 }
 
-__global__ void __launch_bounds__(32)
+__global__ void __launch_bounds__(kPickThreads)
 sample_pick_kernel(const float *__restrict__ sorted_p, const int *__restrict__ sorted_i, int n, float top_p, float r,
                    int *__restrict__ token_out) {
-    __shared__ __align__(16) float buf[1024];
+    __shared__ PickShared sh;
     const float target = fmaxf(fminf(fmaxf(top_p, 0.f), 1.f), 1e-6f);
     float cumulative;
-    const int at = first_reaching(sorted_p, n, 1.0f, target, buf, &cumulative);  // main.rs:113-121
+    const int at = first_reaching(sorted_p, n, 1.0f, target, sh, &cumulative);  // main.rs:113-121
     const int cut = max(1, min(n, at + 1));
     float acc;
     // main.rs:126-134: acc += probs[i] / cumulative; the first i with r <= acc, else the last of the nucleus
-    const int pick = first_reaching(sorted_p, cut, cumulative, r, buf, &acc);
+    const int pick = first_reaching(sorted_p, cut, cumulative, r, sh, &acc);
     if (threadIdx.x == 0) *token_out = sorted_i[min(pick, cut - 1)];
 }
 
@@ -192,7 +219,7 @@ int launch_sample_top_p(lumen_ctx *ctx, const float *logits_dev, size_t vocab, f
     if (e == cudaSuccess)
         e = cub::DeviceRadixSort::SortPairsDescending(sort_ws, sort_bytes, probs, probs_sorted, idx, idx_sorted, n, 0, 32, s);
     if (e == cudaSuccess) {
-        sample_pick_kernel<<<1, 32, 0, s>>>(probs_sorted, idx_sorted, n, top_p, r, token_dev);
+        sample_pick_kernel<<<1, kPickThreads, 0, s>>>(probs_sorted, idx_sorted, n, top_p, r, token_dev);
         e = cudaGetLastError();
         if (e == cudaSuccess) ctx->launches += 1;
     }
