@@ -1438,7 +1438,9 @@ int launch_decode_mega(lumen_ctx *ctx, MegaParams &p, cudaStream_t s) {
     // Tiles handed to the L2, one at a time, while the ring is full (0: none; at most 64, the entries the producer
     // holds).  Measured on TinyLlama f32, 20 steps after a 32-token prompt: 0 -> 1040 tok/s, 24 -> 1076 (64 steps),
     // 48 -> 1115; a pace of 450 cycles instead of 600 loses again (the prefetches queue up in front of the polls).
-    p.l2_ahead = 48;
+    // With 4 or more tensor-parallel ranks the token is bound by the cross-GPU exchanges, a rank's share of the weights is
+    // small, and the prefetches only get in the way of the polls: 4 ranks 1466 tok/s with 48, 1599 with none.
+    p.l2_ahead = p.tp_size >= 4 ? 0 : 48;
     if (const char *e = getenv("LUMEN_MEGA_L2_AHEAD")) p.l2_ahead = std::max(0, std::min(64, atoi(e)));
     p.pf_pace = (int)kPrefetchPace;
     p.pf_grace = (int)kPrefetchGrace;
