@@ -1424,7 +1424,7 @@ int launch_decode_mega(lumen_ctx *ctx, MegaParams &p, cudaStream_t s) {
     const int grid = ctx->num_sms;
     if ((p.H + grid - 1) / grid + 1 > kRowBlock)
         return set_error(ctx, LUMEN_ERR_UNSUPPORTED, "hidden size %d needs more than %d rows per CTA", p.H, kRowBlock);
-    // Ring geometry: 32 KB stages (a row of every supported matrix fits), as many as fit beside the
+    // Ring geometry: 16 KB stages (four rows x 4 KB; longer rows arrive in segments), as many as fit beside the
     // scratch areas in the 227 KB a CTA may use.
     p.stage_bytes = kMegaStageBytes;
     const int kmax = std::max(p.H, std::max(p.qd, p.I));
@@ -1433,8 +1433,6 @@ int launch_decode_mega(lumen_ctx *ctx, MegaParams &p, cudaStream_t s) {
     while (stages > 2 && decode_mega_smem_bytes(stages, p.stage_bytes, p.D, kmax) > budget) --stages;
     p.stages = stages;
     p.debug_flags = decode_mega_debug_flags();
-    // L2 look-ahead of the producer in copies per CTA, counted from the copy being issued (the ring itself
-    // holds `stages` of them): 0 = off, at most 56.
     // Tiles handed to the L2, one at a time, while the ring is full (0: none; at most 64, the entries the producer
     // holds).  Measured on TinyLlama f32, 20 steps after a 32-token prompt: 0 -> 1040 tok/s, 24 -> 1076 (64 steps),
     // 48 -> 1115; a pace of 450 cycles instead of 600 loses again (the prefetches queue up in front of the polls).
