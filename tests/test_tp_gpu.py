@@ -1,5 +1,6 @@
-"""Tensor parallelism on real GPUs (one process per GPU, NCCL allreduce per block): TP=N logits against the
-CPU oracle.  Skipped on a box with a single GPU."""
+"""Tensor parallelism on real GPUs (one process per GPU; the sums over the ranks run inside the persistent decode kernel
+for batch 1, in the fused peer-memory sum kernel for batched steps and short prefills, through NCCL for long prefill
+slices): TP=N logits against the CPU oracle.  Skipped on a box with a single GPU."""
 import json
 import os
 import socket
